@@ -1,0 +1,85 @@
+// Library state and the C-ABI entry points that are not tied to one kernel file.
+#include <atomic>
+#include <mutex>
+
+#include "fvm_internal.h"
+
+namespace fvm {
+
+static constexpr int MAX_DEVICES = 64;
+static DeviceState g_state[MAX_DEVICES];
+static std::mutex g_mutex;
+static std::atomic<long long> g_launches{0};
+
+DeviceState* device_state() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    DeviceState* st = &g_state[dev];
+    return st->ready ? st : nullptr;
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+}  // namespace fvm
+
+using namespace fvm;
+
+extern "C" int fvm_init(void) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return FVM_ERR_SETUP;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState* st = &g_state[dev];
+    if (st->ready) return FVM_OK;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return FVM_ERR_SETUP;
+    if (prop.major != 10) return FVM_ERR_SETUP;   // tcgen05 / TMEM kernels: sm_100 family only
+    st->sms = prop.multiProcessorCount;
+    st->max_smem = static_cast<int>(prop.sharedMemPerBlockOptin);
+    // The status word lives in mapped pinned host memory: kernels write it through the device alias, the host reads
+    // it after a synchronise without a copy.
+    if (cudaHostAlloc(reinterpret_cast<void**>(&st->status_host), sizeof(int), cudaHostAllocMapped) != cudaSuccess)
+        return FVM_ERR_SETUP;
+    *st->status_host = 0;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&st->status_dev), st->status_host, 0) != cudaSuccess)
+        return FVM_ERR_SETUP;
+    const int rc = conv_host_init();
+    if (rc != FVM_OK) return rc;
+    st->ready = true;
+    return FVM_OK;
+}
+
+extern "C" long long fvm_query(int what) {
+    DeviceState* st = device_state();
+    switch (what) {
+        case 0: return 100;   // version 0.1.0
+        case 1: return st ? st->sms : -1;
+        case 2: return st ? st->max_smem : -1;
+        case 3: return g_launches.load(std::memory_order_relaxed);
+    }
+    return -1;
+}
+
+extern "C" int fvm_last_status(int* code) {
+    DeviceState* st = device_state();
+    if (!st || !code) return FVM_ERR_SETUP;
+    *code = *static_cast<volatile int*>(st->status_host);
+    *static_cast<volatile int*>(st->status_host) = 0;
+    return FVM_OK;
+}
+
+extern "C" int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* res, const float* scale,
+                              void* y, int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw,
+                              int dh, int dw, long long ldx, long long ldy, long long ldr, int act, void* stream) {
+    return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act, 0,
+                         static_cast<cudaStream_t>(stream));
+}
+
+// Same as fvm_conv2d_f16 with the output-channel tile forced (multiple of 16, <= 256): used by tests and tuning runs
+// to exercise every tile shape on one problem.
+extern "C" int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const void* res, const float* scale,
+                                   void* y, int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh,
+                                   int sw, int dh, int dw, long long ldx, long long ldy, long long ldr, int act,
+                                   int tile_n, void* stream) {
+    return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act,
+                         tile_n, static_cast<cudaStream_t>(stream));
+}

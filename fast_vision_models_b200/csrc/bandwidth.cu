@@ -1,0 +1,654 @@
+// HBM-bound NHWC fp16 kernels of the convolutional hot path: layout conversion, pooling, global average pool,
+// squeeze-excite gate and scale, channels-last LayerNorm, elementwise epilogues, bilinear resize and fused
+// upsample+argmax. All of them move 16 bytes (8 channels) per thread per access, accumulate in fp32 and round once.
+#include <cstdint>
+
+#include "fvm_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace fvm {
+
+union V8 {
+    uint4 u;
+    __half2 h2[4];
+    __half h[8];
+};
+
+__device__ __forceinline__ uint4 ldg16(const __half* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void stg16(__half* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+
+__device__ __forceinline__ void to_f8(const uint4& u, float (&f)[8]) {
+    V8 v;
+    v.u = u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(v.h2[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 from_f8(const float (&f)[8]) {
+    V8 v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v.h2[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return v.u;
+}
+
+static inline int blocks_for(long long items, int threads) {
+    long long b = (items + threads - 1) / threads;
+    if (b < 1) b = 1;
+    if (b > 0x7fffffffll) b = 0x7fffffffll;
+    return static_cast<int>(b);
+}
+
+// ------------------------------------------------------------------------------------------- input fp32 NCHW -> NHWC8
+// y[n,h,w,c] = c < C ? half(x[n,c,h,w]) : 0   (reference: classification/fast/csrc/fused_conv.cu:597-606)
+__global__ void input_nhwc8_kernel(const float* __restrict__ x, __half* __restrict__ y, int C, long long HW,
+                                   long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / HW;
+    const long long hw = i - n * HW;
+    const float* src = x + n * C * HW + hw;
+    float f[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) f[c] = c < C ? __ldg(src + c * HW) : 0.f;
+    stg16(y + i * 8, from_f8(f));
+}
+
+// ------------------------------------------------------------------------------------------- max / avg pool
+// reference: maxpool_nhwc8 (fused_conv.cu:338-356): -inf padding, half2 max over in-image taps only.
+__global__ void maxpool_kernel(const __half* __restrict__ x, __half* __restrict__ y, int H, int W, int C, int kh, int kw,
+                               int sh, int sw, int ph, int pw, int P, int Q, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    long long t = i / cv;
+    const int q = static_cast<int>(t % Q);
+    t /= Q;
+    const int pp = static_cast<int>(t % P);
+    const long long n = t / P;
+    V8 m;
+    const __half2 ninf = __half2half2(__ushort_as_half(0xfc00));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m.h2[j] = ninf;
+    const int h0 = pp * sh - ph, w0 = q * sw - pw;
+    for (int r = 0; r < kh; ++r) {
+        const int h = h0 + r;
+        if (h < 0 || h >= H) continue;
+        for (int s = 0; s < kw; ++s) {
+            const int w = w0 + s;
+            if (w < 0 || w >= W) continue;
+            V8 a;
+            a.u = ldg16(x + ((n * H + h) * W + w) * C + v * 8);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m.h2[j] = __hmax2(m.h2[j], a.h2[j]);
+        }
+    }
+    stg16(y + i * 8, m.u);
+}
+
+// reference: avgpool_nhwc8 (fused_conv.cu:556-582): fp32 sum over in-image taps, PyTorch divisor rule.
+__global__ void avgpool_kernel(const __half* __restrict__ x, __half* __restrict__ y, int H, int W, int C, int kh, int kw,
+                               int sh, int sw, int ph, int pw, int P, int Q, int include_pad, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    long long t = i / cv;
+    const int q = static_cast<int>(t % Q);
+    t /= Q;
+    const int pp = static_cast<int>(t % P);
+    const long long n = t / P;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int h0 = pp * sh - ph, w0 = q * sw - pw;
+    int cnt = 0;
+    for (int r = 0; r < kh; ++r) {
+        const int h = h0 + r;
+        if (h < 0 || h >= H) continue;
+        for (int s = 0; s < kw; ++s) {
+            const int w = w0 + s;
+            if (w < 0 || w >= W) continue;
+            float f[8];
+            to_f8(ldg16(x + ((n * H + h) * W + w) * C + v * 8), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            ++cnt;
+        }
+    }
+    int div;
+    if (include_pad) {
+        const int hend = min(h0 + kh, H + ph), wend = min(w0 + kw, W + pw);
+        div = (hend - h0) * (wend - w0);
+    } else {
+        div = max(cnt, 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = acc[j] / static_cast<float>(div);
+    stg16(y + i * 8, from_f8(acc));
+}
+
+// ------------------------------------------------------------------------------------------- global average pool
+// Stage 1: block (32 channel-vectors x 8 pixel rows); grid (ceil(cv/32), splits, N). Each thread sums its pixels of
+// one split in a fixed order, the 8 rows are combined in a fixed order in shared memory -> partial[n][split][c].
+// Stage 2 sums the splits in order and scales. Summation order is therefore fixed: results are deterministic.
+static constexpr int GAP_VX = 32, GAP_RY = 8;
+
+__global__ void gap_partial_kernel(const __half* __restrict__ x, float* __restrict__ partial, int HW, int C,
+                                   long long ldx, int splits, int chunk) {
+    __shared__ float red[GAP_RY][GAP_VX][8];
+    const int cv = C >> 3;
+    const int v = blockIdx.x * GAP_VX + threadIdx.x;
+    const int split = blockIdx.y;
+    const long long n = blockIdx.z;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (v < cv) {
+        const int p0 = split * chunk;
+        const int p1 = min(HW, p0 + chunk);
+        const __half* base = x + n * HW * ldx + v * 8;
+        for (int px = p0 + threadIdx.y; px < p1; px += GAP_RY) {
+            float f[8];
+            to_f8(ldg16(base + px * ldx), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[threadIdx.y][threadIdx.x][j] = acc[j];
+    __syncthreads();
+    if (threadIdx.y == 0 && v < cv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float s = red[0][threadIdx.x][j];
+            for (int r = 1; r < GAP_RY; ++r) s += red[r][threadIdx.x][j];
+            partial[(n * splits + split) * C + v * 8 + j] = s;
+        }
+    }
+}
+
+__global__ void gap_final_kernel(const float* __restrict__ partial, __half* __restrict__ y, int C, int splits,
+                                 float inv_hw, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / C;
+    const int c = static_cast<int>(i - n * C);
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partial[(n * splits + k) * C + c];
+    y[i] = __float2half_rn(s * inv_hw);
+}
+
+static int gap_splits(int N, int HW, int C, int sms) {
+    const int cvb = ((C >> 3) + GAP_VX - 1) / GAP_VX;
+    const long long base_blocks = static_cast<long long>(N) * cvb;
+    long long want = (4ll * sms + base_blocks - 1) / base_blocks;
+    long long max_splits = (HW + 63) / 64;   // at least 64 pixels (8 per thread) per split
+    if (want > max_splits) want = max_splits;
+    if (want < 1) want = 1;
+    if (want > 1024) want = 1024;
+    return static_cast<int>(want);
+}
+
+// ------------------------------------------------------------------------------------------- squeeze-excite gate
+// One block per image. h = half(act(W1 g + b1)) (warp per output, lanes stride over C); s = half(W2 h + b2)
+// (thread per output). Rounding points follow the two conv_fused calls the reference issues on [N,C,1,1] tensors.
+__global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __restrict__ w1,
+                               const __half* __restrict__ b1, const __half* __restrict__ w2,
+                               const __half* __restrict__ b2, __half* __restrict__ s_out, int C, int Cs, int act,
+                               float mean_scale) {
+    extern __shared__ float sm[];
+    float* g = sm;          // [C]
+    float* h = sm + C;      // [Cs]
+    const long long n = blockIdx.x;
+    if (mean_scale != 0.f) {
+        const float* gs = static_cast<const float*>(g_in) + n * C;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) g[c] = __half2float(__float2half_rn(gs[c] * mean_scale));
+    } else {
+        const __half* gh = static_cast<const __half*>(g_in) + n * C;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) g[c] = __half2float(gh[c]);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int cv = C >> 3;
+    for (int j = warp; j < Cs; j += nwarps) {
+        const __half* row = w1 + static_cast<long long>(j) * C;
+        float acc = 0.f;
+        for (int v = lane; v < cv; v += 32) {
+            float f[8];
+            to_f8(ldg16(row + v * 8), f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc = fmaf(f[k], g[v * 8 + k], acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            if (b1) acc += __half2float(b1[j]);
+            h[j] = __half2float(__float2half_rn(act_f(acc, act)));
+        }
+    }
+    __syncthreads();
+    const int sv = Cs >> 3;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const __half* row = w2 + static_cast<long long>(c) * Cs;
+        float acc = 0.f;
+        for (int v = 0; v < sv; ++v) {
+            float f[8];
+            to_f8(ldg16(row + v * 8), f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc = fmaf(f[k], h[v * 8 + k], acc);
+        }
+        if (b2) acc += __half2float(b2[c]);
+        s_out[n * C + c] = __float2half_rn(acc);
+    }
+}
+
+// y = x * sigmoid(s[n,c]) -- reference se_scale_k (classification/fast/csrc/r3.cu:302-317): sigmoid in fp32, rounded
+// to fp16, fp16 multiply.
+__global__ void se_scale_kernel(const __half* __restrict__ x, const __half* __restrict__ s, __half* __restrict__ y,
+                                int HW, int C, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    const long long n = i / (static_cast<long long>(cv) * HW);
+    V8 a, g, o;
+    a.u = ldg16(x + i * 8);
+    g.u = ldg16(s + n * C + v * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float2 t = __half22float2(g.h2[j]);
+        __half2 sg = __floats2half2_rn(1.f / (1.f + __expf(-t.x)), 1.f / (1.f + __expf(-t.y)));
+        o.h2[j] = __hmul2(a.h2[j], sg);
+    }
+    stg16(y + i * 8, o.u);
+}
+
+// ------------------------------------------------------------------------------------------- channels-last LayerNorm
+// G lanes cooperate on one row (G = 8, 16 or 32), each lane holds up to VPL 16-byte vectors of the row in registers;
+// two-pass fp32 statistics (mean, then sum of squared deviations), fp32 affine, one rounding.
+template <int G, int VPL>
+__global__ void layernorm_cl_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma,
+                                    const __half* __restrict__ beta, __half* __restrict__ y, long long rows, int C,
+                                    float eps, long long ldx, long long ldy) {
+    constexpr int ROWS_PER_WARP = 32 / G;
+    const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / G, gl = lane % G;
+    const long long row = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp_in_block) * ROWS_PER_WARP + sub;
+    const int cv = C >> 3;
+    const bool row_ok = row < rows;
+    float f[VPL][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int v = gl + k * G;
+        if (row_ok && v < cv) {
+            to_f8(ldg16(x + row * ldx + v * 8), f[k]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += f[k][j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[k][j] = 0.f;
+        }
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / static_cast<float>(C);
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int v = gl + k * G;
+        if (v < cv) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float d = f[k][j] - mean;
+                sq += d * d;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / static_cast<float>(C) + eps);
+    if (!row_ok) return;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int v = gl + k * G;
+        if (v < cv) {
+            float gm[8], bt[8], o[8];
+            if (gamma) to_f8(ldg16(gamma + v * 8), gm);
+            if (beta) to_f8(ldg16(beta + v * 8), bt);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float t = (f[k][j] - mean) * rstd;
+                if (gamma) t *= gm[j];
+                if (beta) t += bt[j];
+                o[j] = t;
+            }
+            stg16(y + row * ldy + v * 8, from_f8(o));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------- elementwise epilogues
+// reference: bias_act_h (segmentation/fast/csrc/seg_kernels.cu:107-119)
+__global__ void bias_act_kernel(__half* __restrict__ y, const __half* __restrict__ bias, const __half* __restrict__ res,
+                                int C, int relu, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    float f[8];
+    to_f8(*reinterpret_cast<const uint4*>(y + i * 8), f);
+    if (bias) {
+        float b[8];
+        to_f8(ldg16(bias + v * 8), b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += b[j];
+    }
+    if (res) {
+        float r[8];
+        to_f8(ldg16(res + i * 8), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += r[j];
+    }
+    if (relu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+    }
+    stg16(y + i * 8, from_f8(f));
+}
+
+// reference: affine_act_k (classification/fast/csrc/fused_conv.cu:310-321)
+__global__ void affine_act_kernel(const __half* __restrict__ x, const float* __restrict__ scale,
+                                  const float* __restrict__ shift, __half* __restrict__ y, int C, long long ldx,
+                                  long long ldy, int act, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    const long long px = i / cv;
+    float f[8];
+    to_f8(ldg16(x + px * ldx + v * 8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = act_f(f[j] * __ldg(scale + v * 8 + j) + __ldg(shift + v * 8 + j), act);
+    stg16(y + px * ldy + v * 8, from_f8(f));
+}
+
+__global__ void add_act_kernel(const __half* __restrict__ a, const __half* __restrict__ b, __half* __restrict__ y,
+                               int act, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float fa[8], fb[8];
+    to_f8(ldg16(a + i * 8), fa);
+    to_f8(ldg16(b + i * 8), fb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) fa[j] = act_f(fa[j] + fb[j], act);
+    stg16(y + i * 8, from_f8(fa));
+}
+
+// ------------------------------------------------------------------------------------------- bilinear resize
+// PyTorch index math (reference: bilin_k, segmentation/fast/csrc/segx_ops.cu:62-111).
+__device__ __forceinline__ void src_index(int i, float scale, int align, int in, int& i0, int& i1, float& l) {
+    float f = align ? i * scale : fmaxf((i + 0.5f) * scale - 0.5f, 0.f);
+    i0 = min(static_cast<int>(f), in - 1);
+    i1 = i0 + (i0 < in - 1 ? 1 : 0);
+    l = f - i0;
+}
+
+__global__ void bilinear_kernel(const __half* __restrict__ x, const __half* __restrict__ base, __half* __restrict__ y,
+                                int h, int w, int C, int H, int W, int align, float sch, float scw, int relu,
+                                long long ldx, long long ldy, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    long long t = i / cv;
+    const int ox = static_cast<int>(t % W);
+    t /= W;
+    const int oy = static_cast<int>(t % H);
+    const long long n = t / H;
+    int y0, y1, x0, x1;
+    float ly, lx;
+    src_index(oy, sch, align, h, y0, y1, ly);
+    src_index(ox, scw, align, w, x0, x1, lx);
+    const float hy = 1.f - ly, hx = 1.f - lx;
+    const __half* img = x + n * h * w * ldx + v * 8;
+    float a[8], b[8], c[8], d[8], o[8];
+    to_f8(ldg16(img + (static_cast<long long>(y0) * w + x0) * ldx), a);
+    to_f8(ldg16(img + (static_cast<long long>(y0) * w + x1) * ldx), b);
+    to_f8(ldg16(img + (static_cast<long long>(y1) * w + x0) * ldx), c);
+    to_f8(ldg16(img + (static_cast<long long>(y1) * w + x1) * ldx), d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = hy * (hx * a[j] + lx * b[j]) + ly * (hx * c[j] + lx * d[j]);
+    const long long opix = (n * H + oy) * W + ox;
+    if (base) {
+        // the interpolated value is rounded to fp16 first, then added in fp32 (segx_ops.cu:102-105)
+        float bb[8];
+        to_f8(ldg16(base + opix * ldy + v * 8), bb);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j] = __half2float(__float2half_rn(o[j])) + bb[j];
+            if (relu) o[j] = fmaxf(o[j], 0.f);
+        }
+    }
+    stg16(y + opix * ldy + v * 8, from_f8(o));
+}
+
+// Fused bilinear upsample + argmax over channels; first maximum wins; scores are not rounded between the lerp and
+// the comparison (reference: up_argmax_h, segmentation/fast/csrc/seg_kernels.cu:11-42).
+__global__ void up_argmax_kernel(const __half* __restrict__ s, int32_t* __restrict__ out, int h, int w, int C,
+                                 long long ld, int H, int W, int align, float sch, float scw, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int ox = static_cast<int>(i % W);
+    long long t = i / W;
+    const int oy = static_cast<int>(t % H);
+    const long long n = t / H;
+    int y0, y1, x0, x1;
+    float ly, lx;
+    src_index(oy, sch, align, h, y0, y1, ly);
+    src_index(ox, scw, align, w, x0, x1, lx);
+    const float hy = 1.f - ly, hx = 1.f - lx;
+    const __half* img = s + n * h * w * ld;
+    const __half* pa = img + (static_cast<long long>(y0) * w + x0) * ld;
+    const __half* pb = img + (static_cast<long long>(y0) * w + x1) * ld;
+    const __half* pc = img + (static_cast<long long>(y1) * w + x0) * ld;
+    const __half* pd = img + (static_cast<long long>(y1) * w + x1) * ld;
+    float best = -INFINITY;
+    int arg = 0;
+    for (int c0 = 0; c0 < C; c0 += 8) {
+        float a[8], b[8], c[8], d[8];
+        to_f8(ldg16(pa + c0), a);
+        to_f8(ldg16(pb + c0), b);
+        to_f8(ldg16(pc + c0), c);
+        to_f8(ldg16(pd + c0), d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float val = hy * (hx * a[j] + lx * b[j]) + ly * (hx * c[j] + lx * d[j]);
+            if (c0 + j < C && val > best) {
+                best = val;
+                arg = c0 + j;
+            }
+        }
+    }
+    out[i] = arg;
+}
+
+// ------------------------------------------------------------------------------------------- host wrappers
+#define FVM_LAUNCH_CHECK()                                                   \
+    do {                                                                     \
+        count_launch();                                                      \
+        return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;  \
+    } while (0)
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace fvm
+
+using namespace fvm;
+
+extern "C" int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
+    if (!x || !y || N <= 0 || C <= 0 || C > 8 || H <= 0 || W <= 0 || !aligned16(y)) return FVM_ERR_ARG;
+    const long long HW = static_cast<long long>(H) * W, total = HW * N;
+    input_nhwc8_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, static_cast<__half*>(y), C, HW, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_maxpool_f16(const void* x, void* y, int N, int H, int W, int C, int kh, int kw, int sh, int sw,
+                               int ph, int pw, int P, int Q, void* stream) {
+    if (!x || !y || N <= 0 || H <= 0 || W <= 0 || C <= 0 || (C & 7) || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
+        P <= 0 || Q <= 0 || !aligned16(x) || !aligned16(y))
+        return FVM_ERR_ARG;
+    const long long total = static_cast<long long>(N) * P * Q * (C >> 3);
+    maxpool_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), H, W, C, kh, kw, sh, sw, ph, pw, P, Q, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_avgpool_f16(const void* x, void* y, int N, int H, int W, int C, int kh, int kw, int sh, int sw,
+                               int ph, int pw, int P, int Q, int count_include_pad, void* stream) {
+    if (!x || !y || N <= 0 || H <= 0 || W <= 0 || C <= 0 || (C & 7) || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
+        P <= 0 || Q <= 0 || !aligned16(x) || !aligned16(y))
+        return FVM_ERR_ARG;
+    const long long total = static_cast<long long>(N) * P * Q * (C >> 3);
+    avgpool_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), H, W, C, kh, kw, sh, sw, ph, pw, P, Q,
+        count_include_pad, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" long long fvm_gap_scratch_floats(int N, int HW, int C) {
+    if (N <= 0 || HW <= 0 || C <= 0) return 0;
+    DeviceState* st = device_state();
+    const int sms = st ? st->sms : 148;
+    return static_cast<long long>(N) * gap_splits(N, HW, C, sms) * C;
+}
+
+extern "C" int fvm_global_avgpool_f16(const void* x, void* y, float* partial, int N, int HW, int C, long long ldx,
+                                      void* stream) {
+    DeviceState* st = device_state();
+    if (!st) return FVM_ERR_SETUP;
+    if (!x || !y || !partial || N <= 0 || HW <= 0 || C <= 0 || (C & 7) || (ldx & 7) || ldx < C || !aligned16(x))
+        return FVM_ERR_ARG;
+    if (N > 65535) return FVM_ERR_ARG;
+    const int splits = gap_splits(N, HW, C, st->sms);
+    const int chunk = (HW + splits - 1) / splits;
+    dim3 grid(((C >> 3) + GAP_VX - 1) / GAP_VX, splits, N), block(GAP_VX, GAP_RY);
+    gap_partial_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(x), partial,
+                                                                              HW, C, ldx, splits, chunk);
+    count_launch();
+    const long long total = static_cast<long long>(N) * C;
+    gap_final_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        partial, static_cast<__half*>(y), C, splits, 1.f / static_cast<float>(HW), total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, const void* w2, const void* b2, void* s,
+                               int N, int C, int Cs, int act, float mean_scale, void* stream) {
+    if (!g || !w1 || !w2 || !s || N <= 0 || C <= 0 || Cs <= 0 || (C & 7) || (Cs & 7) || act < 0 || act > 6 ||
+        !aligned16(w1) || !aligned16(w2))
+        return FVM_ERR_ARG;
+    const size_t smem = static_cast<size_t>(C + Cs) * sizeof(float);
+    if (smem > 48 * 1024) return FVM_ERR_ARG;
+    se_gate_kernel<<<N, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+        g, static_cast<const __half*>(w1), static_cast<const __half*>(b1), static_cast<const __half*>(w2),
+        static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C, void* stream) {
+    if (!x || !s || !y || N <= 0 || HW <= 0 || C <= 0 || (C & 7) || !aligned16(x) || !aligned16(y) || !aligned16(s))
+        return FVM_ERR_ARG;
+    const long long total = static_cast<long long>(N) * HW * (C >> 3);
+    se_scale_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(s), static_cast<__half*>(y), HW, C, total);
+    FVM_LAUNCH_CHECK();
+}
+
+template <int G, int VPL>
+static void launch_ln(const void* x, const void* gamma, const void* beta, void* y, long long rows, int C, float eps,
+                      long long ldx, long long ldy, cudaStream_t stream) {
+    constexpr int WARPS = 8;
+    const long long rows_per_block = static_cast<long long>(WARPS) * (32 / G);
+    layernorm_cl_kernel<G, VPL><<<blocks_for(rows, static_cast<int>(rows_per_block)), WARPS * 32, 0, stream>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(gamma), static_cast<const __half*>(beta),
+        static_cast<__half*>(y), rows, C, eps, ldx, ldy);
+}
+
+extern "C" int fvm_layernorm_cl_f16(const void* x, const void* gamma, const void* beta, void* y, long long rows, int C,
+                                    float eps, long long ldx, long long ldy, void* stream) {
+    if (!x || !y || rows <= 0 || C <= 0 || (C & 7) || (ldx & 7) || (ldy & 7) || ldx < C || ldy < C || !aligned16(x) ||
+        !aligned16(y) || !aligned16(gamma) || !aligned16(beta))
+        return FVM_ERR_ARG;
+    const int cv = C >> 3;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cv <= 8) launch_ln<8, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 16) launch_ln<16, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 32) launch_ln<32, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 64) launch_ln<32, 2>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 128) launch_ln<32, 4>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 256) launch_ln<32, 8>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else return FVM_ERR_ARG;
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_bias_act_f16(void* y, const void* bias, const void* res, long long pixels, int C, int relu,
+                                void* stream) {
+    if (!y || pixels <= 0 || C <= 0 || (C & 7) || !aligned16(y) || !aligned16(bias) || !aligned16(res))
+        return FVM_ERR_ARG;
+    const long long total = pixels * (C >> 3);
+    bias_act_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half*>(y), static_cast<const __half*>(bias), static_cast<const __half*>(res), C, relu, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_affine_act_f16(const void* x, const float* scale, const float* shift, void* y, long long pixels,
+                                  int C, long long ldx, long long ldy, int act, void* stream) {
+    if (!x || !y || !scale || !shift || pixels <= 0 || C <= 0 || (C & 7) || (ldx & 7) || (ldy & 7) || ldx < C ||
+        ldy < C || act < 0 || act > 6 || !aligned16(x) || !aligned16(y))
+        return FVM_ERR_ARG;
+    const long long total = pixels * (C >> 3);
+    affine_act_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), scale, shift, static_cast<__half*>(y), C, ldx, ldy, act, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_add_act_f16(const void* a, const void* b, void* y, long long n, int act, void* stream) {
+    if (!a || !b || !y || n <= 0 || (n & 7) || act < 0 || act > 6 || !aligned16(a) || !aligned16(b) || !aligned16(y))
+        return FVM_ERR_ARG;
+    const long long total = n >> 3;
+    add_act_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(a), static_cast<const __half*>(b), static_cast<__half*>(y), act, total);
+    FVM_LAUNCH_CHECK();
+}
+
+static float resize_scale(int in, int out, int align, float sf) {
+    if (align) return out > 1 ? static_cast<float>(in - 1) / static_cast<float>(out - 1) : 0.f;
+    if (sf > 0.f) return 1.f / sf;
+    return static_cast<float>(in) / static_cast<float>(out);
+}
+
+extern "C" int fvm_bilinear_f16(const void* x, const void* base, void* y, int N, int h, int w, int C, int H, int W,
+                                int align, float sf_h, float sf_w, int relu, long long ldx, long long ldy,
+                                void* stream) {
+    if (!x || !y || N <= 0 || h <= 0 || w <= 0 || H <= 0 || W <= 0 || C <= 0 || (C & 7) || (ldx & 7) || (ldy & 7) ||
+        ldx < C || ldy < C || !aligned16(x) || !aligned16(y) || !aligned16(base))
+        return FVM_ERR_ARG;
+    const long long total = static_cast<long long>(N) * H * W * (C >> 3);
+    bilinear_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(base), static_cast<__half*>(y), h, w, C, H, W, align,
+        resize_scale(h, H, align, sf_h), resize_scale(w, W, align, sf_w), relu, ldx, ldy, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_up_argmax_f16(const void* s, int32_t* out, int N, int h, int w, int C, long long ld, int H, int W,
+                                 int align, void* stream) {
+    if (!s || !out || N <= 0 || h <= 0 || w <= 0 || H <= 0 || W <= 0 || C <= 0 || (ld & 7) || ld < C || !aligned16(s))
+        return FVM_ERR_ARG;
+    if (((C + 7) & ~7) > ld) return FVM_ERR_ARG;   // whole 16-byte vectors are read
+    const long long total = static_cast<long long>(N) * H * W;
+    up_argmax_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(s), out, h, w, C, ld, H, W, align, resize_scale(h, H, align, 0.f),
+        resize_scale(w, W, align, 0.f), total);
+    FVM_LAUNCH_CHECK();
+}

@@ -1,0 +1,26 @@
+// Internal declarations shared by the translation units of libfvm_b200 (not part of the C ABI).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "../../include/fvm_b200.h"
+
+namespace fvm {
+
+struct DeviceState {
+    int sms = 0;
+    int max_smem = 0;
+    int* status_dev = nullptr;    // device-visible address of the status word (mapped pinned host memory)
+    int* status_host = nullptr;   // host address of the same word
+    bool ready = false;
+};
+
+// State of the current device, or nullptr if fvm_init() has not run for it.
+DeviceState* device_state();
+void count_launch();
+
+int conv_host_init();
+int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
+                  int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
+                  long long ldx, long long ldy, long long ldr, int act, int force_bn, cudaStream_t stream);
+
+}  // namespace fvm

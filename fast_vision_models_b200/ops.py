@@ -1,0 +1,437 @@
+"""Operator layer: torch tensors in, C-ABI calls out.
+
+Each function mirrors one op schema of the reference's `TORCH_LIBRARY` blocks (same name, argument order and meaning;
+classification/fast/csrc/fused_conv.cu:622-631, r3.cu:796-808, segmentation/fast/csrc/segx_conv.cu:619-629,
+segx_ops.cu:294-322) and forwards raw device pointers, sizes and the current CUDA stream to libfvm_b200.so.
+Activations are NCHW-shaped fp16 tensors in channels-last memory format (NHWC in memory), possibly a channel slice
+of a wider channels-last buffer. There is no CPU or aten fallback: a tensor that is not on a CUDA device, or a
+library that is missing, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+ACT_NONE, ACT_RELU, ACT_RELU6, ACT_SILU, ACT_HARDSWISH, ACT_GELU_ERF, ACT_GELU_TANH = range(7)
+
+_initialised_devices = set()
+
+
+class FvmError(RuntimeError):
+    pass
+
+
+_STATUS_TEXT = {1: "bad argument or unsupported shape", 2: "set-up failed (not an sm_100 device, or driver entry point missing)",
+                3: "kernel launch error", 4: "tensor-map encode error"}
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise FvmError(f"fvm_b200.{what}: status {rc} ({_STATUS_TEXT.get(rc, 'unknown')})")
+
+
+def lib() -> ctypes.CDLL:
+    return _lib.load()
+
+
+def init(device: Optional[torch.device] = None) -> None:
+    """Per-device set-up; must run before the first launch on a device and before any CUDA-graph capture."""
+    if not torch.cuda.is_available():
+        raise FvmError("fvm_b200 needs a CUDA device (sm_100a); there is no CPU path")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx in _initialised_devices:
+        return
+    with torch.cuda.device(idx):
+        _check(lib().fvm_init(), "init")
+    _initialised_devices.add(idx)
+
+
+def last_status() -> int:
+    """Asynchronous status word of the current device (0 = no fault); synchronises first."""
+    torch.cuda.synchronize()
+    code = ctypes.c_int(0)
+    _check(lib().fvm_last_status(ctypes.byref(code)), "last_status")
+    return code.value
+
+
+def launches() -> int:
+    """Number of kernels this library has launched since it was loaded."""
+    return int(lib().fvm_query(3))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda_half(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise FvmError(f"{name}: tensor is not on a CUDA device; fvm_b200 has no CPU path")
+    if t.dtype != torch.float16:
+        raise FvmError(f"{name}: expected fp16, got {t.dtype}")
+
+
+def nhwc_view(x: torch.Tensor, name: str = "x"):
+    """Returns (tensor, N, C, H, W, ld): `tensor` is NHWC in memory with pixel stride `ld` (a channels-last tensor or a
+    channel slice of one); anything else is made channels-last contiguous first (reference: fused_conv.cu:237-244)."""
+    _require_cuda_half(x, name)
+    if x.dim() != 4:
+        raise FvmError(f"{name}: expected a 4-D NCHW-shaped tensor")
+    N, C, H, W = x.shape
+    sN, sC, sH, sW = x.stride()
+    # pixel (n,h,w) must sit at ((n*H + h)*W + w) * ld; ld comes from the innermost dimension that has extent > 1
+    if W > 1:
+        ld = sW
+    elif H > 1:
+        ld = sH
+    elif N > 1:
+        ld = sN
+    else:
+        ld = C
+    ok = (C == 1 or sC == 1) and ld % 8 == 0 and ld >= C and x.data_ptr() % 16 == 0 \
+        and (H == 1 or sH == W * ld) and (N == 1 or sN == H * W * ld)
+    if not ok:
+        x = x.contiguous(memory_format=torch.channels_last)
+        if x.data_ptr() % 16 != 0 or C % 8 != 0:
+            raise FvmError(f"{name}: channels must be a multiple of 8 and the storage 16-byte aligned")
+        ld = C
+    return x, N, C, H, W, ld
+
+
+def empty_nhwc(N: int, C: int, H: int, W: int, device) -> torch.Tensor:
+    return torch.empty((N, C, H, W), dtype=torch.float16, device=device, memory_format=torch.channels_last)
+
+
+def _pair(v) -> tuple:
+    if isinstance(v, int):
+        return (v, v)
+    v = tuple(int(a) for a in v)
+    return (v[0], v[0]) if len(v) == 1 else (v[0], v[1])
+
+
+# ------------------------------------------------------------------------------------------------ dense conv / GEMM
+def _krsc(w: torch.Tensor) -> torch.Tensor:
+    """[K,C,R,S] weight -> KRSC in memory (a channels-last tensor), as the reference requires (fused_conv.cu:245)."""
+    _require_cuda_half(w, "w")
+    if w.dim() != 4:
+        raise FvmError("w: expected [K,C,R,S]")
+    return w.contiguous(memory_format=torch.channels_last)
+
+
+def conv_fused_into(x, w, bias, res, padding, stride, act: int, out: torch.Tensor, dilation=(1, 1),
+                    scale: Optional[torch.Tensor] = None, tile_n: int = 0) -> None:
+    """clf::conv_fused_into / segx::conv_fused_into: y = act((conv(x,w)+bias)*scale + res) written into `out`."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    w = _krsc(w)
+    K, Cw, R, S = w.shape
+    if Cw != C:
+        raise FvmError(f"conv_fused: weight has {Cw} input channels, input has {C}")
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    P = (H + 2 * ph - dh * (R - 1) - 1) // sh + 1
+    Q = (W + 2 * pw - dw * (S - 1) - 1) // sw + 1
+    out_v, No, Ko, Po, Qo, ldy = nhwc_view(out, "out")
+    if out_v is not out or (No, Ko, Po, Qo) != (N, K, P, Q):
+        raise FvmError(f"conv_fused_into: out must be a channels-last [N,K,P,Q]={N, K, P, Q} tensor or channel slice, "
+                       f"got {tuple(out.shape)} strides {out.stride()}")
+    ldr = 0
+    if res is not None:
+        res, Nr, Kr, Pr, Qr, ldr = nhwc_view(res, "res")
+        if (Nr, Kr, Pr, Qr) != (N, K, P, Q):
+            raise FvmError("conv_fused: residual shape does not match the output")
+    if bias is not None:
+        _require_cuda_half(bias, "bias")
+        bias = bias.contiguous()
+    if scale is not None:
+        if scale.dtype != torch.float32 or not scale.is_cuda:
+            raise FvmError("conv_fused: scale must be an fp32 CUDA tensor")
+        scale = scale.contiguous()
+    L = lib()
+    args = [x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(res), _ptr(scale), out.data_ptr(), N, H, W, C, K, R, S, ph, pw,
+            sh, sw, dh, dw, ldx, ldy, ldr, int(act)]
+    if tile_n:
+        rc = L.fvm_conv2d_f16_tile(*args, int(tile_n), _stream())
+    else:
+        rc = L.fvm_conv2d_f16(*args, _stream())
+    _check(rc, "conv2d_f16")
+
+
+def conv_fused(x, w, bias=None, res=None, padding=(0, 0), stride=(1, 1), act: int = 0, cfg: int = -1,
+               dilation=(1, 1), scale=None, tile_n: int = 0) -> torch.Tensor:
+    """clf::conv_fused(x, w, bias?, res?, padding, stride, act, cfg=-1) -> Tensor (fused_conv.cu:298-302, schema :624).
+    `cfg` (the reference's CUTLASS tile index) is accepted and ignored; `tile_n` forces this library's own N tile."""
+    N, C, H, W = x.shape
+    K, _, R, S = w.shape
+    ph, pw = _pair(padding)
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    P = (H + 2 * ph - dh * (R - 1) - 1) // sh + 1
+    Q = (W + 2 * pw - dw * (S - 1) - 1) // sw + 1
+    out = empty_nhwc(N, K, P, Q, x.device)
+    conv_fused_into(x, w, bias, res, padding, stride, act, out, dilation=dilation, scale=scale, tile_n=tile_n)
+    return out
+
+
+def conv_fused_d(x, w, bias, res, padding, stride, dilation, act: int) -> torch.Tensor:
+    """segx::conv_fused_d (segmentation/fast/csrc/segx_conv.cu:295-299)."""
+    return conv_fused(x, w, bias, res, padding, stride, act, dilation=dilation)
+
+
+def pw(x, w, bias, act: int) -> torch.Tensor:
+    """clfr3::pw (classification/fast/csrc/r3.cu:758-765): 1x1 stride-1 conv; here the same tcgen05 kernel."""
+    return conv_fused(x, w, bias, None, (0, 0), (1, 1), act)
+
+
+def linear(x2d: torch.Tensor, w: torch.Tensor, bias=None, res2d=None, act: int = 0, scale=None) -> torch.Tensor:
+    """Row-major GEMM y[M,K] = act((x[M,C] @ w[K,C]^T + bias)*scale + res): the reference's `_lin` view
+    (classification/fast/vit.py:56-64) without the permutes."""
+    _require_cuda_half(x2d, "x")
+    M, C = x2d.shape
+    K = w.shape[0]
+    x4 = x2d.contiguous().view(1, M, 1, C).permute(0, 3, 1, 2)
+    y = torch.empty((M, K), dtype=torch.float16, device=x2d.device)
+    y4 = y.view(1, M, 1, K).permute(0, 3, 1, 2)
+    r4 = None if res2d is None else res2d.contiguous().view(1, M, 1, K).permute(0, 3, 1, 2)
+    conv_fused_into(x4, w.reshape(K, C, 1, 1), bias, r4, (0, 0), (1, 1), act, y4, scale=scale)
+    return y
+
+
+# ------------------------------------------------------------------------------------------------ depthwise
+def dwconv(x, w_rsc, bias=None, stride=(1, 1), padding=(0, 0), act: int = 0, dilation=(1, 1),
+           pool_sums: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """clf::dwconv(x, w_rsc, bias?, stride, padding, act) (fused_conv.cu:480-502) / clfr3::dwconv2 (r3.cu:423-454) /
+    segx::dwconv with dilation (segx_ops.cu:45-57). w_rsc is [R,S,C] contiguous."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    _require_cuda_half(w_rsc, "w_rsc")
+    w_rsc = w_rsc.contiguous()
+    R, S, Cw = w_rsc.shape
+    if Cw != C:
+        raise FvmError("dwconv: weight channel count mismatch")
+    sh, sw = _pair(stride)
+    ph, pw_ = _pair(padding)
+    dh, dw = _pair(dilation)
+    P = (H + 2 * ph - dh * (R - 1) - 1) // sh + 1
+    Q = (W + 2 * pw_ - dw * (S - 1) - 1) // sw + 1
+    y = empty_nhwc(N, C, P, Q, x.device)
+    if bias is not None:
+        bias = bias.contiguous()
+    if pool_sums is not None and (pool_sums.dtype != torch.float32 or pool_sums.numel() != N * C):
+        raise FvmError("dwconv: pool_sums must be fp32 [N,C]")
+    _check(lib().fvm_dwconv_f16(x.data_ptr(), w_rsc.data_ptr(), _ptr(bias), y.data_ptr(), _ptr(pool_sums), N, H, W, C,
+                                R, S, ph, pw_, sh, sw, dh, dw, ldx, C, int(act), _stream()), "dwconv_f16")
+    return y
+
+
+dwconv2 = dwconv
+
+
+# ------------------------------------------------------------------------------------------------ pooling
+def _pool_out(L: int, k: int, s: int, p: int, ceil: bool) -> int:
+    """Output size rule of the reference (fused_conv.cu:363-367)."""
+    if not ceil:
+        return (L + 2 * p - k) // s + 1
+    o = (L + 2 * p - k + s - 1) // s + 1
+    if (o - 1) * s >= L + p:
+        o -= 1
+    return o
+
+
+def maxpool(x, k, stride, pad, ceil: bool = False) -> torch.Tensor:
+    """clf::maxpool(x, k, stride, pad, ceil=False) (fused_conv.cu:358-374)."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    if ldx != C:
+        x = x.contiguous(memory_format=torch.channels_last)
+    kh, kw = _pair(k)
+    sh, sw = _pair(stride)
+    ph, pw_ = _pair(pad)
+    P, Q = _pool_out(H, kh, sh, ph, ceil), _pool_out(W, kw, sw, pw_, ceil)
+    y = empty_nhwc(N, C, P, Q, x.device)
+    _check(lib().fvm_maxpool_f16(x.data_ptr(), y.data_ptr(), N, H, W, C, kh, kw, sh, sw, ph, pw_, P, Q, _stream()),
+           "maxpool_f16")
+    return y
+
+
+def avgpool(x, k, stride, pad, ceil: bool = False, count_include_pad: bool = True) -> torch.Tensor:
+    """clf::avgpool(x, k, stride, pad, ceil, count_include_pad) (fused_conv.cu:584-594)."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    if ldx != C:
+        x = x.contiguous(memory_format=torch.channels_last)
+    kh, kw = _pair(k)
+    sh, sw = _pair(stride)
+    ph, pw_ = _pair(pad)
+    P, Q = _pool_out(H, kh, sh, ph, ceil), _pool_out(W, kw, sw, pw_, ceil)
+    y = empty_nhwc(N, C, P, Q, x.device)
+    _check(lib().fvm_avgpool_f16(x.data_ptr(), y.data_ptr(), N, H, W, C, kh, kw, sh, sw, ph, pw_, P, Q,
+                                 int(count_include_pad), _stream()), "avgpool_f16")
+    return y
+
+
+def gap_scratch(N: int, HW: int, C: int, device) -> torch.Tensor:
+    init(device)
+    return torch.empty(int(lib().fvm_gap_scratch_floats(N, HW, C)), dtype=torch.float32, device=device)
+
+
+def global_avgpool(x, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """AdaptiveAvgPool2d(1) on NHWC fp16 -> [N,C,1,1] fp16; deterministic two-stage fp32 reduction."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    need = int(lib().fvm_gap_scratch_floats(N, H * W, C))
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=x.device)
+    elif scratch.numel() < need or scratch.dtype != torch.float32:
+        raise FvmError("global_avgpool: scratch too small")
+    y = torch.empty((N, C), dtype=torch.float16, device=x.device)
+    _check(lib().fvm_global_avgpool_f16(x.data_ptr(), y.data_ptr(), scratch.data_ptr(), N, H * W, C, ldx, _stream()),
+           "global_avgpool_f16")
+    return y.view(N, C, 1, 1)
+
+
+# ------------------------------------------------------------------------------------------------ squeeze-excite
+def se_gate(g, w1, b1, w2, b2, act: int = ACT_SILU, mean_scale: float = 0.0) -> torch.Tensor:
+    """s = W2 act(W1 g + b1) + b2 for g [N,C(,1,1)] -> s [N,C,1,1] fp16 (pre-sigmoid)."""
+    init(g.device)
+    N = g.shape[0]
+    C = g.shape[1]
+    w1 = w1.reshape(w1.shape[0], -1).contiguous()
+    w2 = w2.reshape(w2.shape[0], -1).contiguous()
+    Cs = w1.shape[0]
+    if w1.shape[1] != C or tuple(w2.shape) != (C, Cs):
+        raise FvmError("se_gate: weight shapes do not match")
+    g = g.reshape(N, C).contiguous()
+    if mean_scale == 0.0:
+        _require_cuda_half(g, "g")
+    elif g.dtype != torch.float32:
+        raise FvmError("se_gate: with mean_scale the squeeze input must be fp32 sums")
+    s = torch.empty((N, C), dtype=torch.float16, device=g.device)
+    _check(lib().fvm_se_gate_f16(g.data_ptr(), w1.data_ptr(), _ptr(b1), w2.data_ptr(), _ptr(b2), s.data_ptr(), N, C, Cs,
+                                 int(act), float(mean_scale), _stream()), "se_gate_f16")
+    return s.view(N, C, 1, 1)
+
+
+def se_scale(x, s) -> torch.Tensor:
+    """clfr3::se_scale(x, s) (classification/fast/csrc/r3.cu:319-329): y = x * sigmoid(s)."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    if ldx != C:
+        x = x.contiguous(memory_format=torch.channels_last)
+    _require_cuda_half(s, "s")
+    s = s.reshape(N, C).contiguous()
+    y = empty_nhwc(N, C, H, W, x.device)
+    _check(lib().fvm_se_scale_f16(x.data_ptr(), s.data_ptr(), y.data_ptr(), N, H * W, C, _stream()), "se_scale_f16")
+    return y
+
+
+# ------------------------------------------------------------------------------------------------ LayerNorm
+def layernorm_cl(x, weight, bias, eps: float = 1e-6) -> torch.Tensor:
+    """LayerNorm over the channel dimension of a channels-last tensor ([N,C,H,W] NHWC in memory) or over the last
+    dimension of a contiguous [..., C] tensor; same shape and layout out."""
+    init(x.device)
+    _require_cuda_half(x, "x")
+    if x.dim() == 4 and x.stride(1) == 1 and x.shape[1] > 1:
+        xv, N, C, H, W, ldx = nhwc_view(x, "x")
+        rows = N * H * W
+        y = empty_nhwc(N, C, H, W, x.device)
+        src = xv
+    else:
+        src = x.contiguous()
+        C = src.shape[-1]
+        rows = src.numel() // C
+        ldx = C
+        y = torch.empty_like(src)
+    _check(lib().fvm_layernorm_cl_f16(src.data_ptr(), _ptr(weight), _ptr(bias), y.data_ptr(), rows, C, float(eps), ldx,
+                                      C, _stream()), "layernorm_cl_f16")
+    return y
+
+
+# ------------------------------------------------------------------------------------------------ elementwise
+def input_nhwc8(x: torch.Tensor) -> torch.Tensor:
+    """clf::input_nhwc8(x) (fused_conv.cu:608-620): fp32 NCHW (C<=8) -> fp16 channels-last with C padded to 8."""
+    init(x.device)
+    if not x.is_cuda or x.dtype != torch.float32:
+        raise FvmError("input_nhwc8: expected an fp32 CUDA tensor")
+    x = x.contiguous()
+    N, C, H, W = x.shape
+    y = empty_nhwc(N, 8, H, W, x.device)
+    _check(lib().fvm_input_nhwc8_f32(x.data_ptr(), y.data_ptr(), N, C, H, W, _stream()), "input_nhwc8_f32")
+    return y
+
+
+def bias_act_(y, bias=None, res=None, relu: bool = False) -> torch.Tensor:
+    """segx::bias_act_(y, bias?, res?, relu) in place (segmentation/fast/csrc/segx_ops.cu:28-42)."""
+    init(y.device)
+    yv, N, C, H, W, ld = nhwc_view(y, "y")
+    if yv is not y or ld != C:
+        raise FvmError("bias_act_: y must be channels-last contiguous")
+    if res is not None:
+        res, *_r, ldr = nhwc_view(res, "res")
+        if ldr != C:
+            res = res.contiguous(memory_format=torch.channels_last)
+    _check(lib().fvm_bias_act_f16(y.data_ptr(), _ptr(bias), _ptr(res), N * H * W, C, int(relu), _stream()),
+           "bias_act_f16")
+    return y
+
+
+def affine_act(x, scale, shift, act: int) -> torch.Tensor:
+    """clf::affine_act(x, scale, shift, act) (fused_conv.cu:323-335)."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    y = empty_nhwc(N, C, H, W, x.device)
+    _check(lib().fvm_affine_act_f16(x.data_ptr(), scale.float().contiguous().data_ptr(),
+                                    shift.float().contiguous().data_ptr(), y.data_ptr(), N * H * W, C, ldx, C, int(act),
+                                    _stream()), "affine_act_f16")
+    return y
+
+
+def add_act(a, b, act: int = 0) -> torch.Tensor:
+    """y = act(a + b) for two channels-last tensors of the same shape."""
+    init(a.device)
+    a, N, C, H, W, lda = nhwc_view(a, "a")
+    b, *_s, ldb = nhwc_view(b, "b")
+    if lda != C:
+        a = a.contiguous(memory_format=torch.channels_last)
+    if ldb != C:
+        b = b.contiguous(memory_format=torch.channels_last)
+    y = empty_nhwc(N, C, H, W, a.device)
+    _check(lib().fvm_add_act_f16(a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), int(act), _stream()), "add_act_f16")
+    return y
+
+
+# ------------------------------------------------------------------------------------------------ resize / argmax
+def upsample_bilinear(x, H: int, W: int, sf_h: Optional[float] = None, sf_w: Optional[float] = None,
+                      align: bool = False, base=None, relu: bool = False) -> torch.Tensor:
+    """segx::upsample_bilinear(x, H, W, sf_h?, sf_w?, align) and upsample_add (segx_ops.cu:131-217)."""
+    init(x.device)
+    x, N, C, h, w, ldx = nhwc_view(x, "x")
+    y = empty_nhwc(N, C, H, W, x.device)
+    if base is not None:
+        base, *_s, ldb = nhwc_view(base, "base")
+        if ldb != C:
+            base = base.contiguous(memory_format=torch.channels_last)
+    _check(lib().fvm_bilinear_f16(x.data_ptr(), _ptr(base), y.data_ptr(), N, h, w, C, H, W, int(align),
+                                  float(sf_h or 0.0), float(sf_w or 0.0), int(relu), ldx, C, _stream()), "bilinear_f16")
+    return y
+
+
+def up_argmax(s, H: int, W: int, align: bool = False, num_classes: Optional[int] = None) -> torch.Tensor:
+    """segx::up_argmax(s, H, W, align) (segx_ops.cu:171-195): int32 class map [N,H,W]; first maximum wins.
+    `num_classes` restricts the argmax to the first channels of a zero-padded score tensor."""
+    init(s.device)
+    s, N, C, h, w, ld = nhwc_view(s, "s")
+    C_eff = C if num_classes is None else int(num_classes)
+    out = torch.empty((N, H, W), dtype=torch.int32, device=s.device)
+    _check(lib().fvm_up_argmax_f16(s.data_ptr(), out.data_ptr(), N, h, w, C_eff, ld, H, W, int(align), _stream()),
+           "up_argmax_f16")
+    return out

@@ -1,0 +1,130 @@
+/* fvm_b200 -- C ABI of the B200 (sm_100a) convolutional hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, i.e. a cudaStream_t),
+ * launches asynchronously on that stream and returns an int status at once:
+ *   0 ok, 1 bad argument / unsupported shape, 2 attribute or set-up failure, 3 launch error, 4 tensor-map encode error.
+ * The same convention as the reference's `run<F>` (classification/fast/csrc/fused_conv.cu:152-173: 0 ok, 1 cannot
+ * implement, 2 shared-memory attribute failed, 3 launch error). Asynchronous faults (a bounded device-side wait that
+ * ran out) are written to a per-device status word that fvm_last_status() reads after the stream has been synchronised.
+ *
+ * Tensors: activations are NHWC fp16 (a channels-last NCHW tensor in torch terms); `ld*` arguments are the pixel
+ * stride in elements (>= channels; a channel slice of a wider buffer is allowed, as in the reference's `ldx`/`ldy`,
+ * fused_conv.cu:24-31). Dense weights are KRSC fp16, depthwise weights RSC fp16, bias fp16 [K]. Base pointers and pixel
+ * strides must be 16-byte aligned (channels % 8 == 0), which is the reference's own contract (fused_conv.cu:7).
+ *
+ * Nothing here allocates device memory per call; fvm_init() sets up the per-device state and must be called once per
+ * device before the first launch (and before any stream capture).
+ */
+#ifndef FVM_B200_H
+#define FVM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FVM_OK 0
+#define FVM_ERR_ARG 1
+#define FVM_ERR_SETUP 2
+#define FVM_ERR_LAUNCH 3
+#define FVM_ERR_TMAP 4
+
+/* activation codes: reference act_f, classification/fast/csrc/fused_conv.cu:33-43 */
+#define FVM_ACT_NONE 0
+#define FVM_ACT_RELU 1
+#define FVM_ACT_RELU6 2
+#define FVM_ACT_SILU 3
+#define FVM_ACT_HARDSWISH 4
+#define FVM_ACT_GELU_ERF 5
+#define FVM_ACT_GELU_TANH 6
+
+/* Per-device set-up for the current device (SM count, kernel attributes, status word). Idempotent.
+ * Replaces the static initialisers of the reference extensions (fused_conv.cu:165-170, :205). */
+int fvm_init(void);
+
+/* what: 0 library version, 1 SM count of the current device, 2 max dynamic shared memory per block (bytes),
+ * 3 number of kernels launched by this library since load (all devices). */
+long long fvm_query(int what);
+
+/* Reads and clears the asynchronous status word of the current device (0 = no fault). Call after synchronising. */
+int fvm_last_status(int* code);
+
+/* Dense convolution / GEMM with fused epilogue -- replaces clf::conv_fused / conv_fused_into
+ * (classification/fast/csrc/fused_conv.cu:231-306), segx::conv_fused_d (segmentation/fast/csrc/segx_conv.cu:231-299)
+ * and clfr3::pw (classification/fast/csrc/r3.cu:633-765):
+ *   y[n,p,q,k] = act( (sum_{r,s,c} x[n, p*sh-ph+r*dh, q*sw-pw+s*dw, c] * w[k,r,s,c] + bias[k]) * scale[k] + res[n,p,q,k] )
+ * fp16 operands, fp32 accumulation (TMEM), fp32 epilogue, one rounding to fp16. bias, scale (fp32 [K], a LayerScale
+ * that was not folded into w) and res may be NULL. Requires C % 8 == 0 and K % 8 == 0. */
+int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y,
+                   int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
+                   long long ldx, long long ldy, long long ldr, int act, void* stream);
+
+/* Depthwise RxS convolution -- replaces clf::dwconv (fused_conv.cu:418-502), clfr3::dwconv2 (r3.cu:335-454) and
+ * segx::dwconv (segmentation/fast/csrc/seg_kernels.cu:124-158):
+ *   y[n,p,q,c] = act( bias[c] + sum_{r,s} x[n, p*sh-ph+r*dh, q*sw-pw+s*dw, c] * w[r,s,c] ), fp32 accumulation.
+ * If pool_sums != NULL (fp32 [N,C], zeroed by the caller) the per-(image,channel) sums of the fp16-rounded outputs
+ * are accumulated into it (the squeeze of a squeeze-excite block; cf. gconv2_pool, r3.cu:181-203). */
+int fvm_dwconv_f16(const void* x, const void* w_rsc, const void* bias, void* y, float* pool_sums, int N, int H, int W,
+                   int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw, long long ldx, long long ldy,
+                   int act, void* stream);
+
+/* NHWC max / average pooling -- replaces clf::maxpool (fused_conv.cu:338-374) and clf::avgpool (:556-594).
+ * P, Q are the output sizes (the caller applies the floor / ceil rule of fused_conv.cu:363-367). */
+int fvm_maxpool_f16(const void* x, void* y, int N, int H, int W, int C, int kh, int kw, int sh, int sw, int ph, int pw,
+                    int P, int Q, void* stream);
+int fvm_avgpool_f16(const void* x, void* y, int N, int H, int W, int C, int kh, int kw, int sh, int sw, int ph, int pw,
+                    int P, int Q, int count_include_pad, void* stream);
+
+/* Global average pool, NHWC fp16 [N,HW,C] (pixel stride ldx) -> fp16 [N,C], fp32 accumulation in a fixed order
+ * (deterministic). Stands where the reference leaves aten AdaptiveAvgPool2d(1) in the graph
+ * (classification/fast/r3.py:188-199) or fuses sums with atomics (r3.cu:181-203, :283-286).
+ * `partial` is caller-provided fp32 scratch of at least fvm_gap_scratch_floats(N, HW, C) floats. */
+long long fvm_gap_scratch_floats(int N, int HW, int C);
+int fvm_global_avgpool_f16(const void* x, void* y, float* partial, int N, int HW, int C, long long ldx, void* stream);
+
+/* Squeeze-excite gate: s[n,:] = W2 * act(W1 * g[n,:] + b1) + b2 with g fp16 [N,C], W1 fp16 [Cs,C], W2 fp16 [C,Cs];
+ * stands for the two clf::conv_fused calls on [N,C,1,1] tensors the reference issues (r3.py:188-199). Output fp16 [N,C]
+ * (pre-sigmoid). If mean_scale != 0, g is read as fp32 sums [N,C] and multiplied by mean_scale first (fused squeeze). */
+int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, const void* w2, const void* b2, void* s, int N,
+                    int C, int Cs, int act, float mean_scale, void* stream);
+
+/* y = x * sigmoid(s[n,c]) -- replaces clfr3::se_scale (r3.cu:302-329): sigmoid in fp32, rounded to fp16, fp16 multiply. */
+int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C, void* stream);
+
+/* Channels-last LayerNorm over the last dimension of [rows, C] fp16 (row stride ldx / ldy), fp32 two-pass statistics,
+ * fp32 affine, one rounding -- the torch nn.LayerNorm call of the reference's ConvNeXt block
+ * (classification/fast/convnext.py:55) and the ln_row pattern (segmentation/fast/csrc/seg_kernels.cu:192-210). */
+int fvm_layernorm_cl_f16(const void* x, const void* gamma, const void* beta, void* y, long long rows, int C, float eps,
+                         long long ldx, long long ldy, void* stream);
+
+/* fp32 NCHW [N,C,H,W] (C <= 8) -> fp16 NHWC with channels zero-padded to 8 -- replaces clf::input_nhwc8
+ * (fused_conv.cu:597-620). */
+int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H, int W, void* stream);
+
+/* In place: y = relu?(y + bias[c] + res) -- replaces segx::bias_act_ (segmentation/fast/csrc/segx_ops.cu:28-42). */
+int fvm_bias_act_f16(void* y, const void* bias, const void* res, long long pixels, int C, int relu, void* stream);
+
+/* y = act(x * scale[c] + shift[c]), fp32 scale/shift -- replaces clf::affine_act (fused_conv.cu:308-335). */
+int fvm_affine_act_f16(const void* x, const float* scale, const float* shift, void* y, long long pixels, int C,
+                       long long ldx, long long ldy, int act, void* stream);
+
+/* y = act(a + b) elementwise fp16 (fp32 math) -- the un-fused residual add the reference leaves to aten in MBConv
+ * blocks (no custom kernel there; SURVEY of the reference graph: 25 aten adds in EfficientNet-B4). */
+int fvm_add_act_f16(const void* a, const void* b, void* y, long long n, int act, void* stream);
+
+/* PyTorch-exact bilinear resize of NHWC fp16 [N,h,w,C] -> [N,H,W,C] (align_corners both ways; sf_* <= 0 means derive
+ * the scale from the sizes). If base != NULL: y = relu?(half(interp) + base) -- replaces segx::upsample_bilinear /
+ * upsample_add (segmentation/fast/csrc/segx_ops.cu:59-157). */
+int fvm_bilinear_f16(const void* x, const void* base, void* y, int N, int h, int w, int C, int H, int W, int align,
+                     float sf_h, float sf_w, int relu, long long ldx, long long ldy, void* stream);
+
+/* Fused bilinear upsample + channel argmax of NHWC fp16 scores [N,h,w,ld] (first C channels) -> int32 [N,H,W]; the
+ * first maximum wins -- replaces segx::up_argmax (segx_ops.cu:171-195; seg_kernels.cu:11-42). */
+int fvm_up_argmax_f16(const void* s, int32_t* out, int N, int h, int w, int C, long long ld, int H, int W, int align,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FVM_B200_H */
