@@ -1,0 +1,136 @@
+"""Building blocks of the compiled networks: each holds its prepared fp16 weights as buffers and runs one library op.
+
+They stand where the reference's fx passes insert `torch.ops.clf.*` calls (classification/fast/fused.py:163-203 for
+conv + add + activation chains, :206-236 for depthwise, r3.py:188-199 for squeeze-excite).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import fold, ops
+
+_ACT_CODES = {
+    nn.ReLU: ops.ACT_RELU, nn.ReLU6: ops.ACT_RELU6, nn.SiLU: ops.ACT_SILU, nn.Hardswish: ops.ACT_HARDSWISH,
+}
+
+
+def act_code(m: Optional[nn.Module]) -> int:
+    """Activation module -> op code; same table as the reference's `_act_of` (fused.py:22-44)."""
+    if m is None or isinstance(m, nn.Identity):
+        return ops.ACT_NONE
+    for cls, code in _ACT_CODES.items():
+        if isinstance(m, cls):
+            return code
+    if isinstance(m, nn.GELU):
+        return ops.ACT_GELU_TANH if getattr(m, "approximate", "none") == "tanh" else ops.ACT_GELU_ERF
+    raise ValueError(f"activation {type(m).__name__} has no fused code")
+
+
+class FusedConv(nn.Module):
+    """y = act((conv(x, w) + b) * scale + res): one launch of the tcgen05 implicit-GEMM kernel."""
+
+    def __init__(self, w: torch.Tensor, b: Optional[torch.Tensor], stride=(1, 1), padding=(0, 0), dilation=(1, 1),
+                 act: int = 0, scale: Optional[torch.Tensor] = None, out_channels: Optional[int] = None):
+        super().__init__()
+        K = w.shape[0]
+        self.out_channels = K if out_channels is None else out_channels   # channels that carry data (rest is padding)
+        Kp = fold.round_up(K, 8)
+        w, b = fold.pad_out_channels(w, b, Kp)
+        w = fold.pad_in_channels(w, fold.round_up(w.shape[1], 8))
+        self.register_buffer("w", fold.to_krsc_half(w))
+        self.register_buffer("b", None if b is None else b.half().contiguous())
+        self.register_buffer("scale", None if scale is None else scale.float().contiguous())
+        self.stride, self.padding, self.dilation, self.act = tuple(stride), tuple(padding), tuple(dilation), int(act)
+
+    @classmethod
+    def from_conv_bn(cls, conv: nn.Conv2d, bn: Optional[nn.Module] = None, act: int = 0, **kw) -> "FusedConv":
+        if conv.groups != 1:
+            raise ValueError("FusedConv: dense convolutions only")
+        if conv.padding_mode != "zeros":
+            raise ValueError("FusedConv: zero padding only")
+        w, b = fold.fold_conv_bn(conv, bn if isinstance(bn, nn.BatchNorm2d) else None)
+        return cls(w, b, conv.stride, conv.padding, conv.dilation, act, **kw)
+
+    @classmethod
+    def from_linear(cls, lin: nn.Linear, act: int = 0, gamma: Optional[torch.Tensor] = None) -> "FusedConv":
+        w = lin.weight.detach().float()
+        b = lin.bias.detach().float() if lin.bias is not None else None
+        if gamma is not None:
+            w, b = fold.fold_layer_scale(w, b, gamma)
+        return cls(w.view(w.shape[0], w.shape[1], 1, 1), b, act=act)
+
+    def forward(self, x: torch.Tensor, res: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                act: Optional[int] = None) -> torch.Tensor:
+        a = self.act if act is None else act
+        if out is not None:
+            ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, a, out, dilation=self.dilation,
+                                scale=self.scale)
+            return out
+        return ops.conv_fused(x, self.w, self.b, res, self.padding, self.stride, a, dilation=self.dilation,
+                              scale=self.scale)
+
+
+class DepthwiseConv(nn.Module):
+    """Depthwise conv + folded BatchNorm bias + activation (reference: clf.dwconv / clfr3.dwconv2)."""
+
+    def __init__(self, conv: nn.Conv2d, bn: Optional[nn.Module], act: int):
+        super().__init__()
+        if conv.groups != conv.in_channels or conv.out_channels != conv.in_channels:
+            raise ValueError("DepthwiseConv: groups == in_channels == out_channels only")
+        w, b = fold.fold_conv_bn(conv, bn if isinstance(bn, nn.BatchNorm2d) else None)
+        self.register_buffer("w", fold.dw_to_rsc_half(w))
+        self.register_buffer("b", b.half().contiguous())
+        self.stride, self.padding, self.dilation, self.act = conv.stride, conv.padding, conv.dilation, int(act)
+
+    def forward(self, x: torch.Tensor, pool_sums: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.dwconv(x, self.w, self.b, self.stride, self.padding, self.act, dilation=self.dilation,
+                          pool_sums=pool_sums)
+
+
+class SqueezeExcite(nn.Module):
+    """x * sigmoid(W2 act(W1 mean(x) + b1) + b2). Squeeze channels are zero-padded to a multiple of 8, which is exact
+    because act(0) = 0 for the supported activations (reference: pad_conv_pairs, fused.py:400-434)."""
+
+    def __init__(self, fc1: nn.Conv2d, fc2: nn.Conv2d, act: int):
+        super().__init__()
+        if act not in (ops.ACT_NONE, ops.ACT_RELU, ops.ACT_RELU6, ops.ACT_SILU, ops.ACT_HARDSWISH, ops.ACT_GELU_ERF,
+                       ops.ACT_GELU_TANH):
+            raise ValueError("SqueezeExcite: unsupported activation")
+        w1 = fc1.weight.detach().float().flatten(1)     # [Cs, C]
+        b1 = fc1.bias.detach().float() if fc1.bias is not None else torch.zeros(w1.shape[0])
+        w2 = fc2.weight.detach().float().flatten(1)     # [C, Cs]
+        b2 = fc2.bias.detach().float() if fc2.bias is not None else torch.zeros(w2.shape[0])
+        Cs, C = w1.shape
+        Csp = fold.round_up(Cs, 8)
+        w1p = torch.zeros(Csp, C)
+        w1p[:Cs] = w1
+        b1p = torch.zeros(Csp)
+        b1p[:Cs] = b1
+        w2p = torch.zeros(C, Csp)
+        w2p[:, :Cs] = w2
+        self.register_buffer("w1", w1p.half().contiguous())
+        self.register_buffer("b1", b1p.half().contiguous())
+        self.register_buffer("w2", w2p.half().contiguous())
+        self.register_buffer("b2", b2.half().contiguous())
+        self.act = int(act)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        g = ops.global_avgpool(x)
+        s = ops.se_gate(g, self.w1, self.b1, self.w2, self.b2, self.act)
+        return ops.se_scale(x, s)
+
+
+class LayerNormCL(nn.Module):
+    """LayerNorm over the channels of a channels-last tensor (torchvision LayerNorm2d / nn.LayerNorm on NHWC)."""
+
+    def __init__(self, ln: nn.LayerNorm):
+        super().__init__()
+        self.register_buffer("w", ln.weight.detach().half().contiguous())
+        self.register_buffer("b", ln.bias.detach().half().contiguous())
+        self.eps = float(ln.eps)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.layernorm_cl(x, self.w, self.b, self.eps)

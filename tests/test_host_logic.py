@@ -1,0 +1,81 @@
+"""Host-side logic that needs no GPU: folding arithmetic, layout helpers, registries, compiled-module construction."""
+import pytest
+import torch
+from torch import nn
+
+from fast_vision_models_b200 import fold, ops
+from fast_vision_models_b200.classification import zoo
+from fast_vision_models_b200.weights import seeded_init, seeded_input
+from oracle import models_ref, ops_ref
+
+
+def test_fold_conv_bn_matches_unfolded_fp32():
+    torch.manual_seed(0)
+    conv = nn.Conv2d(8, 16, 3, padding=1, bias=True)
+    bn = nn.BatchNorm2d(16)
+    seeded_init(nn.Sequential(conv, bn), seed=3)
+    x = torch.randn(2, 8, 9, 9)
+    ref = bn.eval()(conv(x))
+    w, b = fold.fold_conv_bn(conv, bn)
+    y = torch.nn.functional.conv2d(x, w, b, padding=1)
+    assert (y - ref).abs().max() <= 1e-4 * (ref.abs().max() + 1e-6)   # the reference's own fold check is 1e-3
+    wr, br = models_ref.fold_bn_ref(conv, bn)
+    assert torch.equal(wr, w.half()) and torch.equal(br, b.half())    # product and oracle fold identically
+
+
+def test_layer_scale_fold_and_padding():
+    w = torch.randn(6, 4)
+    b = torch.randn(6)
+    g = torch.rand(6)
+    wf, bf = fold.fold_layer_scale(w, b, g)
+    assert torch.allclose(wf, w * g[:, None]) and torch.allclose(bf, b * g)
+    w4 = torch.randn(5, 3, 2, 2)
+    assert fold.pad_in_channels(w4, 8).shape == (5, 8, 2, 2)
+    assert fold.pad_in_channels(w4, 8)[:, 3:].abs().sum() == 0
+    wo, bo = fold.pad_out_channels(w4, torch.ones(5), 8)
+    assert wo.shape[0] == 8 and bo[5:].abs().sum() == 0
+    assert fold.dw_to_rsc_half(torch.randn(16, 1, 3, 5)).shape == (3, 5, 16)
+
+
+@pytest.mark.parametrize("L,k,s,p,ceil", [(112, 3, 2, 1, False), (7, 2, 2, 0, True), (8, 3, 2, 0, True),
+                                          (5, 3, 2, 1, True), (13, 3, 3, 1, True)])
+def test_pool_output_rule_matches_torch(L, k, s, p, ceil):
+    x = torch.zeros(1, 1, L, L)
+    want = torch.nn.functional.max_pool2d(x, k, s, p, ceil_mode=ceil).shape[-1]
+    assert ops._pool_out(L, k, s, p, ceil) == want
+    assert ops_ref.pool_out_ref(L, k, s, p, ceil) == want
+
+
+def test_registry_and_aliases():
+    assert zoo.ALIASES["cuda-kernels"] == "opt" and zoo.ALIASES["b200"] == "opt" and zoo.ALIASES["upstream"] == "base"
+    assert {"resnet50", "efficientnet_b4", "convnext_tiny"} <= set(zoo.names())
+    with pytest.raises(KeyError):
+        zoo.load("vit_b16", "b200", device="cpu")
+
+
+def test_compiled_modules_build_on_cpu_and_refuse_to_run_there():
+    m = zoo.load("resnet50", "b200", device="cpu")
+    assert m.input_size == (3, 224, 224)
+    n_convs = sum(1 for mod in m.model.modules() if type(mod).__name__ == "FusedConv")
+    assert n_convs == 54          # 53 folded conv+BN pairs + the FC head as a GEMM (reference graph: 39 + 14 + Linear)
+    with pytest.raises(ops.FvmError):
+        m.model(torch.zeros(1, 3, 64, 64))
+
+
+def test_seeded_init_is_deterministic():
+    a = zoo.build_upstream("resnet18", seed=1)
+    b = zoo.build_upstream("resnet18", seed=1)
+    for pa, pb in zip(a.state_dict().values(), b.state_dict().values()):
+        assert torch.equal(pa, pb)
+    assert torch.equal(seeded_input((1, 3, 8, 8), 0), seeded_input((1, 3, 8, 8), 0))
+
+
+def test_bilinear_oracle_matches_torch_interpolate():
+    x = torch.randn(2, 8, 5, 7).half()
+    for align in (False, True):
+        y = ops_ref.bilinear_ref(x, 11, 13, align=align).float()
+        ref = torch.nn.functional.interpolate(x.float(), size=(11, 13), mode="bilinear", align_corners=align)
+        assert (y - ref).abs().max() < 2e-3
+    am = ops_ref.up_argmax_ref(x, 20, 28)
+    ref = torch.nn.functional.interpolate(x.float(), size=(20, 28), mode="bilinear", align_corners=False).argmax(1)
+    assert (am.long() == ref).float().mean() > 0.999

@@ -1,0 +1,74 @@
+"""Whole-network GPU parity: b200 tier vs the CPU oracle, vs the golden vectors from the reference's portable tier,
+and vs the upstream fp32 model. Tolerances are the ones the task states: relative L2 <= 1e-2 on logits, >= 99.5 %
+argmax agreement."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+from fast_vision_models_b200.classification import zoo
+from fast_vision_models_b200.weights import seeded_input
+from oracle import models_ref
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 1e-2
+
+CASES = [
+    ("resnet50", (2, 3, 64, 64), None, "resnet50_2x64"),
+    ("resnet50", (2, 3, 224, 224), None, "resnet50_2x224"),
+    ("efficientnet_b4", (2, 3, 96, 96), None, "efficientnet_b4_2x96"),
+    ("convnext_tiny", (2, 3, 64, 64), 1e-6, "convnext_tiny_2x64_ls1e-06"),
+    ("convnext_tiny", (2, 3, 64, 64), "uniform", "convnext_tiny_2x64_lsuniform"),
+]
+
+
+@pytest.mark.parametrize("name,shape,ls,tag", CASES)
+def test_b200_tier_matches_reference_golden_and_oracle(name, shape, ls, tag):
+    gold = np.load(os.path.join(GOLD, tag + ".npz"))
+    m = zoo.load(name, "b200", device="cuda", seed=1, layer_scale=ls)
+    x = seeded_input(shape, seed=0)
+    y = m.model(x.cuda()).cpu()
+    port, y32 = torch.from_numpy(gold["portable"]), torch.from_numpy(gold["fp32"])
+    assert rel_l2(y, port) < TOL, rel_l2(y, port)
+    assert rel_l2(y, y32) < TOL
+    assert bool((y.argmax(1) == port.argmax(1)).all())
+    if shape[2] <= 96:
+        ref = models_ref.model_ref(zoo.build_upstream(name, seed=1, layer_scale=ls), x)
+        assert rel_l2(y, ref) < 3e-3, rel_l2(y, ref)
+    # graph replay gives the same answer as the first (capturing) call, and as the un-graphed path
+    y2 = m.model(x.cuda()).cpu()
+    assert torch.equal(y, y2)
+    eager = zoo.load(name, "b200", device="cuda", seed=1, layer_scale=ls, graphs=False)
+    assert torch.equal(eager.model(x.cuda()).cpu(), y)
+
+
+def test_convnext_unfolded_layer_scale_epilogue():
+    x = seeded_input((2, 3, 64, 64), seed=0)
+    m = zoo.load("convnext_tiny", "b200", device="cuda", seed=1, layer_scale="uniform", fold_scale=False)
+    y = m.model(x.cuda()).cpu()
+    ref = models_ref.convnext_ref(zoo.build_upstream("convnext_tiny", seed=1, layer_scale="uniform"), x, fold_scale=False)
+    assert rel_l2(y, ref) < 3e-3
+
+
+def test_resnet50_batch64_agreement_with_upstream_fp32_and_portable_on_device():
+    # BASELINE-sized batch: the b200 tier against the upstream fp32 model and the portable tier on the same GPU
+    x = seeded_input((64, 3, 224, 224), seed=0).cuda()
+    fast = zoo.load("resnet50", "b200", device="cuda", seed=1).model(x)
+    up = zoo.load("resnet50", "upstream", device="cuda", seed=1).model
+    with torch.inference_mode():
+        y32 = up(x)
+    port = zoo.load("resnet50", "portable", device="cuda", seed=1).model(x)
+    assert rel_l2(fast, y32) < TOL and rel_l2(fast, port) < TOL
+    assert (fast.argmax(1) == y32.argmax(1)).float().mean() >= 0.995
+
+
+def test_other_batch_and_resolution_need_no_recompile():
+    m = zoo.load("resnet18", "b200", device="cuda", seed=1)
+    up = zoo.load("resnet18", "upstream", device="cuda", seed=1).model
+    for shape in ((1, 3, 224, 224), (3, 3, 160, 192), (5, 3, 97, 131)):
+        x = seeded_input(shape, seed=3).cuda()
+        with torch.inference_mode():
+            assert rel_l2(m.model(x), up(x)) < TOL

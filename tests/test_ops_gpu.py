@@ -1,0 +1,222 @@
+"""GPU parity of every kernel against the CPU oracle, called through the C-ABI (ctypes) operator layer."""
+import pytest
+import torch
+
+from conftest import rel_l2
+from fast_vision_models_b200 import ops
+from oracle import ops_ref as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+# fp16 outputs of fp32-accumulated ops: the CUDA result and the oracle differ by summation order and one rounding
+TOL_REL_L2 = 1e-3
+TOL_ULP = 2 ** -9       # |a-b| <= TOL_ULP * max(|b|, 1): about four fp16 ulps
+
+
+def gen(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).half()
+
+
+def cl(t):
+    return t.to(DEV).contiguous(memory_format=torch.channels_last)
+
+
+def close(y, ref, tol=TOL_REL_L2):
+    y, ref = y.float().cpu(), ref.float().cpu()
+    assert y.shape == ref.shape, (y.shape, ref.shape)
+    assert torch.isfinite(y).all()
+    assert rel_l2(y, ref) < tol, rel_l2(y, ref)
+    assert ((y - ref).abs() <= 4 * TOL_ULP * ref.abs().clamp_min(1.0) + 1e-3).all()
+
+
+CONV_CASES = [
+    # N, H, W, C, K, R, S, pad, stride, dil, act, res
+    (2, 8, 8, 64, 64, 1, 1, 0, 1, 1, 0, False),
+    (2, 56, 56, 64, 256, 1, 1, 0, 1, 1, 1, True),
+    (3, 14, 14, 256, 1024, 1, 1, 0, 1, 1, 1, True),
+    (2, 7, 7, 2048, 512, 1, 1, 0, 1, 1, 1, False),
+    (2, 9, 9, 48, 24, 1, 1, 0, 1, 1, 3, False),        # ragged channels: C and K below one tile
+    (2, 9, 9, 144, 40, 1, 1, 0, 1, 1, 0, True),
+    (2, 5, 5, 64, 1000, 1, 1, 0, 1, 1, 0, False),       # classifier-head shape: K not a multiple of 64
+    (1, 1, 1, 2048, 1000, 1, 1, 0, 1, 1, 0, False),     # one pixel
+    (2, 8, 8, 64, 64, 3, 3, 1, 1, 1, 0, False),
+    (2, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1, True),
+    (2, 28, 28, 128, 128, 3, 3, 1, 2, 1, 1, False),
+    (2, 14, 14, 256, 512, 1, 1, 0, 2, 1, 0, False),     # stride-2 1x1 downsample
+    (2, 17, 13, 64, 64, 3, 3, 1, 1, 1, 1, False),       # odd sizes: tiles cross rows and images
+    (2, 16, 16, 64, 64, 3, 3, 2, 1, 2, 1, False),       # dilation 2
+    (1, 32, 32, 64, 64, 3, 3, 12, 1, 12, 1, False),     # ASPP-style dilation 12
+    (1, 40, 40, 64, 64, 3, 3, 36, 1, 36, 1, False),     # dilation 36: most taps fall outside the image
+    (2, 15, 15, 48, 48, 5, 5, 2, 2, 1, 3, False),
+    (2, 32, 32, 8, 64, 7, 7, 3, 2, 1, 1, False),        # ResNet stem on zero-padded RGB
+    (2, 32, 32, 8, 96, 4, 4, 0, 4, 1, 0, False),        # ConvNeXt patchify stem
+    (2, 12, 12, 96, 192, 2, 2, 0, 2, 1, 0, False),      # ConvNeXt downsample
+    (2, 14, 14, 96, 384, 1, 1, 0, 1, 1, 5, False),      # fc1 + GELU
+    (2, 14, 14, 96, 96, 1, 1, 0, 1, 1, 6, True),
+    (2, 6, 6, 64, 64, 1, 1, 0, 1, 1, 4, False),         # hardswish
+    (2, 6, 6, 64, 64, 1, 1, 0, 1, 1, 2, False),         # relu6
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_fused_matches_oracle(case):
+    N, H, W, C, K, Rr, S, pad, stride, dil, act, res = case
+    x = gen((N, C, H, W), 1)
+    w = gen((K, C, Rr, S), 2, 0.05)
+    b = gen((K,), 3, 0.1)
+    P = (H + 2 * pad - dil * (Rr - 1) - 1) // stride + 1
+    Q = (W + 2 * pad - dil * (S - 1) - 1) // stride + 1
+    r = gen((N, K, P, Q), 4) if res else None
+    ref = R.conv_fused_ref(x, w, b, r, (pad, pad), (stride, stride), act, (dil, dil))
+    y = ops.conv_fused(cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (stride, stride), act,
+                       dilation=(dil, dil))
+    assert ops.last_status() == 0
+    close(y, ref)
+
+
+@pytest.mark.parametrize("tile", [64, 128, 192, 256])
+def test_conv_every_tile_width(tile):
+    x, w, b, r = gen((2, 128, 28, 28), 1), gen((256, 128, 1, 1), 2, 0.05), gen((256,), 3, 0.1), gen((2, 256, 28, 28), 4)
+    ref = R.conv_fused_ref(x, w, b, r, act=1)
+    y = ops.conv_fused(cl(x), cl(w), b.to(DEV), cl(r), act=1, tile_n=tile)
+    assert ops.last_status() == 0
+    close(y, ref)
+
+
+def test_conv_no_bias_scale_and_sliced_io():
+    # input read from a channel slice, output written into a channel slice of a wider buffer (concat-free ASPP),
+    # un-folded LayerScale as an fp32 epilogue scale
+    x_wide = gen((2, 128, 10, 10), 1)
+    w = gen((64, 64, 3, 3), 2, 0.05)
+    scale = torch.rand(64, generator=torch.Generator().manual_seed(5)) + 0.5
+    r = gen((2, 64, 10, 10), 4)
+    ref = R.conv_fused_ref(x_wide[:, 64:], w, None, r, (1, 1), (1, 1), 0, scale=scale)
+    xd = cl(x_wide)
+    out_wide = torch.zeros((2, 192, 10, 10), dtype=torch.float16, device=DEV).contiguous(memory_format=torch.channels_last)
+    ops.conv_fused_into(xd[:, 64:], cl(w), None, cl(r), (1, 1), (1, 1), 0, out_wide[:, 64:128], scale=scale.to(DEV))
+    assert ops.last_status() == 0
+    close(out_wide[:, 64:128], ref)
+    assert out_wide[:, :64].abs().sum() == 0 and out_wide[:, 128:].abs().sum() == 0   # neighbours untouched
+
+
+def test_conv_linearity_at_full_size():
+    # size-independent property at a BASELINE-sized layer: conv(x1 + x2) == conv(x1) + conv(x2) up to fp16 rounding
+    N, C, K, H = 64, 256, 256, 14
+    x1, x2 = cl(gen((N, C, H, H), 1, 0.5)), cl(gen((N, C, H, H), 2, 0.5))
+    w = cl(gen((K, C, 3, 3), 3, 0.02))
+    y12 = ops.conv_fused((x1.float() + x2.float()).half(), w, None, None, (1, 1), (1, 1), 0)
+    y1 = ops.conv_fused(x1, w, None, None, (1, 1), (1, 1), 0)
+    y2 = ops.conv_fused(x2, w, None, None, (1, 1), (1, 1), 0)
+    assert ops.last_status() == 0
+    assert rel_l2(y12, y1.float() + y2.float()) < 2e-3
+
+
+def test_conv_rejects_bad_arguments():
+    x = cl(gen((1, 12, 4, 4), 1))        # C not a multiple of 8
+    w = cl(gen((8, 12, 1, 1), 2))
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x, w)
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(gen((1, 8, 4, 4), 1), gen((8, 8, 1, 1), 2))   # CPU tensors
+
+
+DW_CASES = [
+    # N, H, W, C, k, stride, pad, dil, act
+    (2, 20, 20, 48, 3, 1, 1, 1, 3), (2, 21, 19, 144, 3, 2, 1, 1, 3), (2, 17, 17, 192, 5, 1, 2, 1, 3),
+    (2, 16, 16, 336, 5, 2, 2, 1, 3), (2, 14, 14, 96, 7, 1, 3, 1, 0), (2, 7, 7, 768, 7, 1, 3, 1, 0),
+    (1, 40, 40, 64, 3, 1, 1, 1, 1), (1, 12, 12, 32, 3, 1, 2, 2, 5), (3, 5, 5, 8, 3, 1, 1, 1, 0),
+]
+
+
+@pytest.mark.parametrize("case", DW_CASES)
+def test_dwconv_matches_oracle(case):
+    N, H, W, C, k, stride, pad, dil, act = case
+    x, w, b = gen((N, C, H, W), 1), gen((k, k, C), 2, 0.2), gen((C,), 3, 0.1)
+    ref = R.dwconv_ref(x, w, b, (stride, stride), (pad, pad), act, (dil, dil))
+    y = ops.dwconv(cl(x), w.to(DEV), b.to(DEV), (stride, stride), (pad, pad), act, dilation=(dil, dil))
+    close(y, ref)
+
+
+def test_dwconv_fused_pool_sums():
+    x, w, b = gen((3, 144, 19, 19), 1), gen((3, 3, 144), 2, 0.2), gen((144,), 3, 0.1)
+    ref = R.dwconv_ref(x, w, b, (1, 1), (1, 1), 3)
+    sums = torch.zeros((3, 144), dtype=torch.float32, device=DEV)
+    y = ops.dwconv(cl(x), w.to(DEV), b.to(DEV), (1, 1), (1, 1), 3, pool_sums=sums)
+    close(y, ref)
+    want = ref.float().sum(dim=(2, 3))
+    assert (sums.cpu() - want).abs().max() <= 1e-3 * want.abs().max() + 1e-2
+
+
+@pytest.mark.parametrize("shape,k,s,p,ceil", [((2, 64, 112, 112), 3, 2, 1, False), ((2, 16, 9, 9), 2, 2, 0, True),
+                                              ((1, 8, 7, 5), 3, 1, 1, False), ((2, 24, 8, 8), 3, 2, 0, True)])
+def test_pools_match_oracle(shape, k, s, p, ceil):
+    x = gen(shape, 1)
+    y = ops.maxpool(cl(x), k, s, p, ceil)
+    assert torch.equal(y.cpu().float(), R.maxpool_ref(x, k, s, p, ceil).float())    # max is exact
+    for cip in (True, False):
+        close(ops.avgpool(cl(x), k, s, p, ceil, cip), R.avgpool_ref(x, k, s, p, ceil, cip))
+
+
+@pytest.mark.parametrize("shape", [(64, 2048, 7, 7), (2, 144, 95, 95), (3, 8, 1, 1), (2, 1792, 12, 12), (1, 48, 190, 190)])
+def test_global_avgpool_matches_oracle_and_is_deterministic(shape):
+    x = gen(shape, 1)
+    xd = cl(x)
+    y = ops.global_avgpool(xd)
+    close(y, R.global_avgpool_ref(x))
+    assert torch.equal(y, ops.global_avgpool(xd))
+
+
+@pytest.mark.parametrize("N,C,Cs,act", [(4, 144, 8, 3), (2, 2688, 112, 3), (3, 48, 16, 1), (64, 672, 32, 3)])
+def test_se_gate_and_scale_match_oracle(N, C, Cs, act):
+    g, w1, b1 = gen((N, C, 1, 1), 1), gen((Cs, C), 2, 0.1), gen((Cs,), 3, 0.1)
+    w2, b2 = gen((C, Cs), 4, 0.1), gen((C,), 5, 0.1)
+    ref_s = R.se_gate_ref(g, w1, b1, w2, b2, act)
+    s = ops.se_gate(g.to(DEV), w1.to(DEV), b1.to(DEV), w2.to(DEV), b2.to(DEV), act)
+    close(s, ref_s, 2e-3)
+    x = gen((N, C, 6, 5), 6)
+    close(ops.se_scale(cl(x), ref_s.to(DEV)), R.se_scale_ref(x, ref_s))
+
+
+@pytest.mark.parametrize("shape", [(2, 96, 14, 14), (2, 192, 9, 7), (1, 384, 5, 5), (3, 768, 7, 7), (2, 8, 3, 3),
+                                   (2, 1536, 2, 2), (5, 768, 1, 1)])
+def test_layernorm_matches_oracle(shape):
+    x, w, b = gen(shape, 1), (gen((shape[1],), 2, 0.2) + 1).half(), gen((shape[1],), 3, 0.1)
+    y = ops.layernorm_cl(cl(x), w.to(DEV), b.to(DEV), 1e-6)
+    close(y, R.layernorm_cl_ref(x, w, b, 1e-6), 2e-3)
+
+
+def test_layernorm_idempotent_on_normalised_rows():
+    # size-independent property at a BASELINE-sized tensor: LN(LN(x)) == LN(x) for unit gamma, zero beta
+    x = cl(gen((64, 96, 56, 56), 1))
+    one, zero = torch.ones(96, dtype=torch.float16, device=DEV), torch.zeros(96, dtype=torch.float16, device=DEV)
+    y1 = ops.layernorm_cl(x, one, zero, 1e-6)
+    y2 = ops.layernorm_cl(y1, one, zero, 1e-6)
+    assert rel_l2(y2, y1) < 2e-3
+
+
+def test_input_and_elementwise_ops_match_oracle():
+    x32 = torch.randn(2, 3, 17, 19, generator=torch.Generator().manual_seed(1))
+    assert torch.equal(ops.input_nhwc8(x32.to(DEV)).cpu(), R.input_nhwc8_ref(x32))
+    y, b, r = gen((2, 24, 6, 7), 1), gen((24,), 2), gen((2, 24, 6, 7), 3)
+    yd = cl(y).clone(memory_format=torch.channels_last)
+    close(ops.bias_act_(yd, b.to(DEV), cl(r), True), R.bias_act_ref(y, b, r, True))
+    sc, sh = torch.rand(24) + 0.5, torch.randn(24) * 0.1
+    close(ops.affine_act(cl(y), sc.to(DEV), sh.to(DEV), 1), R.affine_act_ref(y, sc, sh, 1))
+    close(ops.add_act(cl(y), cl(r), 1), R.add_act_ref(y, r, 1))
+
+
+@pytest.mark.parametrize("align", [False, True])
+def test_bilinear_and_up_argmax_match_oracle(align):
+    x = gen((2, 256, 1, 1), 1)
+    close(ops.upsample_bilinear(cl(x), 8, 16, align=align), R.bilinear_ref(x, 8, 16, align))
+    x = gen((2, 24, 9, 13), 2)
+    close(ops.upsample_bilinear(cl(x), 33, 41, align=align), R.bilinear_ref(x, 33, 41, align))
+    base = gen((2, 24, 33, 41), 3)
+    close(ops.upsample_bilinear(cl(x), 33, 41, align=align, base=cl(base), relu=True),
+          R.bilinear_ref(x, 33, 41, align, base=base, relu=True))
+    am = ops.up_argmax(cl(x), 72, 104, align, num_classes=19).cpu()
+    ref = R.up_argmax_ref(x, 72, 104, align, num_classes=19)
+    assert am.dtype == torch.int32 and am.shape == ref.shape
+    # near-ties between channels may resolve differently where the fp32 lerp is contracted into FMAs
+    assert (am == ref).float().mean() >= 0.999
