@@ -51,6 +51,8 @@ CONV_CASES = [
     (2, 15, 15, 48, 48, 5, 5, 2, 2, 1, 3, False),
     (2, 32, 32, 8, 64, 7, 7, 3, 2, 1, 1, False),        # ResNet stem on zero-padded RGB
     (2, 32, 32, 8, 96, 4, 4, 0, 4, 1, 0, False),        # ConvNeXt patchify stem
+    (2, 37, 41, 8, 48, 3, 3, 1, 2, 1, 3, False),        # EfficientNet-B4 stem shape (tap-packed path, 9 taps)
+    (3, 30, 30, 8, 264, 3, 3, 1, 1, 1, 0, False),       # 8-channel input, K too wide for the tap-packed path
     (2, 12, 12, 96, 192, 2, 2, 0, 2, 1, 0, False),      # ConvNeXt downsample
     (2, 14, 14, 96, 384, 1, 1, 0, 1, 1, 5, False),      # fc1 + GELU
     (2, 14, 14, 96, 96, 1, 1, 0, 1, 1, 6, True),
