@@ -37,6 +37,7 @@ static constexpr int EPI_WARPS = 4 * EPI_GROUPS;
 static constexpr int STORE_WARP = 2 + EPI_WARPS;
 static constexpr int CONV_THREADS = 32 * (STORE_WARP + 1);   // producer, MMA, epilogue warps, store warp
 static constexpr int MAX_BIAS_BYTES = 16 * 1024;
+static constexpr int EPI_BACKOFF_NS = 64;     // sleep between polls of the epilogue / store warps
 static constexpr int MAX_STAGES = 8;
 static constexpr int MAX_EPI = 6;     // staging buffers for residual-in / output-out tiles
 static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI + 1;   // stages, accumulators, staging, resident B
@@ -65,6 +66,7 @@ struct ConvParams {
     int act;
     int has_res;
     int bias_elems;   // n_tiles * BN: length of the zero-padded bias copy in shared memory
+    FastDiv div_ntiles, div_pq, div_q;
     const __half* bias;
     const float* scale;
     int* status;
@@ -273,7 +275,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             int pit = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++pit) {
-                const int m_tile = tile / p.n_tiles;
+                const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
                 const int n_tile = tile - m_tile * p.n_tiles;
                 const int m0 = m_tile * BM;
                 const int n0 = n_tile * p.BN;
@@ -296,9 +298,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 int img = 0, h0 = 0, w0 = 0;
                 if (p.im2col) {
-                    img = m0 / PQ;
+                    img = static_cast<int>(fastdiv(static_cast<uint32_t>(m0), p.div_pq));
                     const int rem = m0 - img * PQ;
-                    const int pp = rem / p.Q;
+                    const int pp = static_cast<int>(fastdiv(static_cast<uint32_t>(rem), p.div_q));
                     const int qq = rem - pp * p.Q;
                     h0 = pp * p.sh - p.ph;
                     w0 = qq * p.sw - p.pw;
@@ -442,15 +444,15 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (++e == p.nepi) e = 0;
                 continue;
             }
-            const int m_tile = tile / p.n_tiles;
+            const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
             const int n_tile = tile - m_tile * p.n_tiles;
             const int n0 = n_tile * p.BN;
             TRACE(2 + group, it, 0);
             // staging buffer: with a residual it is filled by TMA (res_full); without, wait until it is free
-            const bool got_buf = p.has_res ? mbar_wait(res_full_bar(e), (e_phase >> e) & 1u, abort_flag)
-                                           : mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag);
+            const bool got_buf = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(e), (e_phase >> e) & 1u, abort_flag)
+                                           : mbar_wait<EPI_BACKOFF_NS>(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag);
             TRACE(2 + group, it, 1);
-            if (!got_buf || !mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+            if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), acc_phase, abort_flag)) {
                 if (lane == 0) atomicExch(p.status, STATUS_WAIT_EPILOGUE);
                 ok = false;
                 break;
@@ -492,12 +494,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             bool ok = true;
             int sit = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++sit) {
-                const int m_tile = tile / p.n_tiles;
+                const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
                 const int n_tile = tile - m_tile * p.n_tiles;
                 const int m0 = m_tile * BM;
                 const int n0 = n_tile * p.BN;
                 TRACE(6, sit, 0);
-                if (!mbar_wait(epi_done_bar(e), (e_phase >> e) & 1u, abort_flag)) {
+                if (!mbar_wait<EPI_BACKOFF_NS>(epi_done_bar(e), (e_phase >> e) & 1u, abort_flag)) {
                     atomicExch(p.status, STATUS_WAIT_STORE);
                     ok = false;
                     break;
@@ -684,6 +686,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.BN = force_bn > 0 ? force_bn : pick_bn(p.m_tiles, K, p.kblocks, false, st->sms);
     if (p.BN < 32 || p.BN > 256 || (p.BN & 31)) return FVM_ERR_ARG;
     p.n_tiles = (K + p.BN - 1) / p.BN;
+    p.div_ntiles = fastdiv_init(static_cast<uint32_t>(p.n_tiles));
     if (p.n_tiles > 1 && (p.BN & 63)) return FVM_ERR_ARG;   // split K only in whole 64-channel store boxes
     p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0);
     p.act = act;
@@ -691,6 +694,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.bias = static_cast<const __half*>(bias);
     p.scale = scale;
     p.status = st->status_dev;
+    p.div_pq = fastdiv_init(static_cast<uint32_t>(P) * Q);
+    p.div_q = fastdiv_init(static_cast<uint32_t>(Q));
     p.nsub = (p.BN + 63) / 64;
 
     SmemPlan sp;

@@ -60,11 +60,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait. `abort_flag` is a word in shared memory shared by all roles of the CTA: the first role that gives up
 // sets it (and the caller records a status code); the other roles see it on their next poll and leave too.
+// BACKOFF_NS > 0 puts the warp to sleep between polls: many-lane waiters (epilogue warps) then leave the issue slots
+// of their scheduler to the single-thread producer / MMA roles instead of spinning next to them.
+template <int BACKOFF_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     for (;;) {
+        if (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0xff) == 0) {
             if (*abort_flag) return false;
@@ -73,6 +77,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
         }
     }
+}
+
+// Division by a run-time constant as multiply-high + shift (valid for numerators below 2^31); `mul`/`shr` from
+// fastdiv_init on the host.
+struct FastDiv {
+    uint32_t div, mul, shr;
+};
+__host__ inline FastDiv fastdiv_init(uint32_t d) {
+    FastDiv f;
+    f.div = d;
+    if (d <= 1) {
+        f.mul = 0;
+        f.shr = 0;
+        return f;
+    }
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) ++lg;
+    const uint32_t p = 31 + lg;
+    f.mul = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+    f.shr = p - 32;
+    return f;
+}
+__device__ __forceinline__ uint32_t fastdiv(uint32_t n, const FastDiv& f) {
+    return f.div <= 1 ? n : (__umulhi(n, f.mul) >> f.shr);
 }
 
 // ---------------------------------------------------------------- TMA

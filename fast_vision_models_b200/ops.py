@@ -411,17 +411,27 @@ def add_act(a, b, act: int = 0) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------------ resize / argmax
 def upsample_bilinear(x, H: int, W: int, sf_h: Optional[float] = None, sf_w: Optional[float] = None,
-                      align: bool = False, base=None, relu: bool = False) -> torch.Tensor:
-    """segx::upsample_bilinear(x, H, W, sf_h?, sf_w?, align) and upsample_add (segx_ops.cu:131-217)."""
+                      align: bool = False, base=None, relu: bool = False, out: Optional[torch.Tensor] = None
+                      ) -> torch.Tensor:
+    """segx::upsample_bilinear(x, H, W, sf_h?, sf_w?, align) and upsample_add (segx_ops.cu:131-217). `out` may be a
+    channel slice of a wider channels-last buffer."""
     init(x.device)
     x, N, C, h, w, ldx = nhwc_view(x, "x")
-    y = empty_nhwc(N, C, H, W, x.device)
+    ldy = C
+    if out is None:
+        y = empty_nhwc(N, C, H, W, x.device)
+    else:
+        y, No, Co, Ho, Wo, ldy = nhwc_view(out, "out")
+        if y is not out or (No, Co, Ho, Wo) != (N, C, H, W):
+            raise FvmError("upsample_bilinear: out must be a channels-last [N,C,H,W] tensor or channel slice")
     if base is not None:
         base, *_s, ldb = nhwc_view(base, "base")
         if ldb != C:
             base = base.contiguous(memory_format=torch.channels_last)
+    if base is not None and ldy != C:
+        raise FvmError("upsample_bilinear: base and a sliced output cannot be combined")
     _check(lib().fvm_bilinear_f16(x.data_ptr(), _ptr(base), y.data_ptr(), N, h, w, C, H, W, int(align),
-                                  float(sf_h or 0.0), float(sf_w or 0.0), int(relu), ldx, C, _stream()), "bilinear_f16")
+                                  float(sf_h or 0.0), float(sf_w or 0.0), int(relu), ldx, ldy, _stream()), "bilinear_f16")
     return y
 
 

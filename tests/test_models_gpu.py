@@ -72,3 +72,38 @@ def test_other_batch_and_resolution_need_no_recompile():
         x = seeded_input(shape, seed=3).cuda()
         with torch.inference_mode():
             assert rel_l2(m.model(x), up(x)) < TOL
+
+
+def test_deeplabv3_logits_and_classmap_match_oracle_and_upstream():
+    from fast_vision_models_b200.segmentation import zoo as segzoo
+    from fast_vision_models_b200.segmentation.common import classmap
+    x = seeded_input((2, 3, 64, 96), seed=0)
+    w = segzoo.build("deeplabv3-r50", "b200", device="cuda", num_classes=19, seed=1)
+    logits = w.logits(x.cuda()).cpu()
+    up = segzoo.build_upstream("deeplabv3-r50", 19, seed=1)
+    ref = models_ref.deeplabv3_logits_ref(up, x)[:, :19].float()
+    assert logits.shape == (2, 19, 8, 12)
+    assert rel_l2(logits, ref) < 3e-3, rel_l2(logits, ref)
+    with torch.inference_mode():
+        y32 = up.classifier(up.backbone(x)["out"])
+    assert rel_l2(logits, y32) < TOL
+    cm = classmap(w, x.cuda()).cpu()
+    assert cm.dtype == torch.int32 and cm.shape == (2, 64, 96)
+    want = models_ref.deeplabv3_classmap_ref(up, x)
+    assert (cm == want).float().mean() >= 0.995
+    full = torch.nn.functional.interpolate(y32, size=(64, 96), mode="bilinear", align_corners=False).argmax(1)
+    assert (cm.long() == full).float().mean() >= 0.995
+    # other output size through the same fused kernel
+    cm2 = w.predict(x.cuda(), (128, 192)).cpu()
+    assert cm2.shape == (2, 128, 192)
+
+
+def test_backbones_registry_features():
+    from fast_vision_models_b200 import backbones
+    x = seeded_input((2, 3, 96, 96), seed=0).cuda()
+    for name in ("tv-resnet50", "tv-convnext_tiny"):
+        fast = backbones.build(name, "b200", seed=1)
+        up = backbones.build(name, "upstream", seed=1)
+        f, u = fast.fn(x), up.fn(x)
+        assert f.shape == u.shape
+        assert rel_l2(f, u) < TOL
