@@ -225,10 +225,8 @@ def main():
     sec_e2e = time.perf_counter() - t0
 
     # ---------------------------------------------------------------- max over ranks
-    t = torch.tensor([ms_dev, sec_e2e * 1e3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dev, ms_e2e = float(t[0]), float(t[1])
+    from fast_vision_models_b200 import parallel
+    ms_dev, ms_e2e = parallel.max_over_ranks([ms_dev, sec_e2e * 1e3], device=dev)
     total_images = BATCH * steps * world
     value = total_images / (ms_dev / 1e3)
     e2e_value = total_images / (ms_e2e / 1e3)
