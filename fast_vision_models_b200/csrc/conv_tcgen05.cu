@@ -59,7 +59,7 @@ struct ConvParams {
     int tmem_cols;   // allocated TMEM columns (power of two >= 32)
     int n_tiles, m_tiles, stages;
     int nsub;      // 64-channel staging sub-tiles per output tile = ceil(BN / 64)
-    int nepi;      // staging buffers (2..6)
+    int nepi;      // staging buffers (1..6)
     int im2col;    // 0: A via 2-D tiled map over [M, C]; 1: A via im2col map over [N, H, W, C]
     int tapk;      // 1: C == 8 "tap-packed" mode: a k-block is 8 filter taps x 8 channels, weights resident in smem
     int taps;      // R * S
@@ -585,7 +585,9 @@ static bool plan_smem(int BN, int kblocks, int K, bool tapk, SmemPlan* out) {
     if (bias_bytes > MAX_BIAS_BYTES) return false;
     const uint32_t fixed = 1024 + 8 * NUM_BARRIERS + MISC_BYTES + bias_bytes + bres_bytes;
     const uint32_t total = 227 * 1024;
-    if (fixed + 2 * epi_bytes + 2 * stage_bytes > total) return false;
+    // deep reductions reach the epilogue rarely: they may run on a single staging buffer and give the rest to the pipeline
+    const int floor_epi = kblocks >= 16 ? 1 : 2;
+    if (fixed + static_cast<uint32_t>(floor_epi) * epi_bytes + 2 * stage_bytes > total) return false;
     const uint32_t budget = total - fixed;
     // Short reductions are epilogue-dominated: 4 accumulators and one staging buffer per epilogue group plus spares for
     // stores in flight. Deep reductions keep 2 accumulators / 2-3 staging buffers and give the pipeline the memory.
@@ -595,7 +597,8 @@ static bool plan_smem(int BN, int kblocks, int K, bool tapk, SmemPlan* out) {
     int nacc = (kblocks <= 8 && max_acc >= 4) ? 4 : 2;
     const int min_stages = 4;   // loads in flight span tiles of this persistent CTA, also when one tile has a single k-block
     int nepi = nacc == 4 ? MAX_EPI : 3;
-    while (nepi > 2 && static_cast<uint32_t>(nepi) * epi_bytes + static_cast<uint32_t>(min_stages) * stage_bytes > budget)
+    while (nepi > floor_epi &&
+           static_cast<uint32_t>(nepi) * epi_bytes + static_cast<uint32_t>(min_stages) * stage_bytes > budget)
         --nepi;
     if (nepi < nacc) nacc = 2;
     int stages = static_cast<int>((budget - static_cast<uint32_t>(nepi) * epi_bytes) / stage_bytes);

@@ -5,12 +5,15 @@ conv + add + activation chains, :206-236 for depthwise, r3.py:188-199 for squeez
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 from torch import nn
 
 from . import fold, ops
+
+AUTOTUNE = os.environ.get("FVM_B200_AUTOTUNE", "1") != "0"   # kill switch, in the style of the reference's CLF_* variables
 
 _ACT_CODES = {
     nn.ReLU: ops.ACT_RELU, nn.ReLU6: ops.ACT_RELU6, nn.SiLU: ops.ACT_SILU, nn.Hardswish: ops.ACT_HARDSWISH,
@@ -44,6 +47,44 @@ class FusedConv(nn.Module):
         self.register_buffer("b", None if b is None else b.half().contiguous())
         self.register_buffer("scale", None if scale is None else scale.float().contiguous())
         self.stride, self.padding, self.dilation, self.act = tuple(stride), tuple(padding), tuple(dilation), int(act)
+        self._tiles = {}      # (input shape, has residual) -> output-channel tile chosen by timing
+
+    def _tile_for(self, x: torch.Tensor, res, out: torch.Tensor, act: int) -> int:
+        """Output-channel tile for this layer at this input shape. The library's own rule picks from wave efficiency
+        and shared-memory fit; where several tile widths are possible they are timed once (first call at a new shape,
+        outside stream capture) and the fastest is kept -- the reference's `pick()` (fused_conv.cu:216-227) is a fixed
+        rule tuned for another GPU, here the choice is measured on the device that runs it."""
+        key = (tuple(x.shape), res is not None)
+        t = self._tiles.get(key)
+        if t is not None:
+            return t
+        if not AUTOTUNE or torch.cuda.is_current_stream_capturing():
+            return 0
+        K = self.w.shape[0]
+        cands = [0] + [c for c in (64, 128, 256) if c < K or (c == 256 and K > 256)]
+        if K <= 64 or self.w.shape[1] == 8:
+            cands = [0]    # one tile anyway / 8-channel stems keep the library's tap-packed path (it needs all of K in one tile)
+        best, best_ms = 0, float("inf")
+        if len(cands) > 1:
+            for c in cands:
+                try:
+                    for _ in range(2):
+                        ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
+                                            dilation=self.dilation, scale=self.scale, tile_n=c)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(5):
+                        ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
+                                            dilation=self.dilation, scale=self.scale, tile_n=c)
+                    e1.record()
+                    e1.synchronize()
+                    ms = e0.elapsed_time(e1)
+                except ops.FvmError:
+                    continue
+                if ms < best_ms * 0.97:      # a different tile must be clearly faster than the default
+                    best, best_ms = c, ms
+        self._tiles[key] = best
+        return best
 
     @classmethod
     def from_conv_bn(cls, conv: nn.Conv2d, bn: Optional[nn.Module] = None, act: int = 0, **kw) -> "FusedConv":
@@ -65,12 +106,16 @@ class FusedConv(nn.Module):
     def forward(self, x: torch.Tensor, res: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 act: Optional[int] = None) -> torch.Tensor:
         a = self.act if act is None else act
-        if out is not None:
-            ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, a, out, dilation=self.dilation,
-                                scale=self.scale)
-            return out
-        return ops.conv_fused(x, self.w, self.b, res, self.padding, self.stride, a, dilation=self.dilation,
-                              scale=self.scale)
+        if out is None:
+            N, _, H, W = x.shape
+            K, _, R, S = self.w.shape
+            P = (H + 2 * self.padding[0] - self.dilation[0] * (R - 1) - 1) // self.stride[0] + 1
+            Q = (W + 2 * self.padding[1] - self.dilation[1] * (S - 1) - 1) // self.stride[1] + 1
+            out = ops.empty_nhwc(N, K, P, Q, x.device)
+        tile = self._tile_for(x, res, out, a)
+        ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, a, out, dilation=self.dilation,
+                            scale=self.scale, tile_n=tile)
+        return out
 
 
 class DepthwiseConv(nn.Module):
