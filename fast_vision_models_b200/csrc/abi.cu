@@ -74,8 +74,9 @@ extern "C" int fvm_conv2d_f16(const void* x, const void* w, const void* bias, co
                          static_cast<cudaStream_t>(stream));
 }
 
-// Same as fvm_conv2d_f16 with the output-channel tile forced (multiple of 16, <= 256): used by tests and tuning runs
-// to exercise every tile shape on one problem.
+// Same as fvm_conv2d_f16 with the tile shape forced: tile_n low 16 bits = output-channel tile (multiple of 32, <= 256;
+// 0 = choose), bits 16 and up = 128-pixel sub-tiles per tile (1, 2 or 4; 0 = choose). Used by tests and by the host's
+// per-layer tuning to exercise every tile shape on one problem.
 extern "C" int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const void* res, const float* scale,
                                    void* y, int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh,
                                    int sw, int dh, int dw, long long ldx, long long ldy, long long ldr, int act,

@@ -58,11 +58,15 @@ struct ConvParams {
     int nacc;        // accumulator buffers in TMEM (2 or 4)
     int tmem_cols;   // allocated TMEM columns (power of two >= 32)
     int n_tiles, m_tiles, stages;
-    int nsub;      // 64-channel staging sub-tiles per output tile = ceil(BN / 64)
+    int mt;        // 128-row sub-tiles per (macro) tile: 1, 2 or 4; a tile is 128*mt output pixels x BN channels
+    int a_loads, a_rows;   // tiled-mode A loads per k-block and rows per load (a TMA box has at most 256 rows)
+    int nsub;      // 64-channel staging sub-tiles per 128-row sub-tile = ceil(BN / 64)
     int nepi;      // staging buffers (1..6)
     int im2col;    // 0: A via 2-D tiled map over [M, C]; 1: A via im2col map over [N, H, W, C]
     int tapk;      // 1: C == 8 "tap-packed" mode: a k-block is 8 filter taps x 8 channels, weights resident in smem
     int taps;      // R * S
+    int bres;      // 1: the weights of this CTA's n-tile stay resident in shared memory (loaded once); each CTA keeps one
+                   // n-tile and walks the m-tiles; pipeline stages then hold A only
     int act;
     int has_res;
     int bias_elems;   // n_tiles * BN: length of the zero-padded bias copy in shared memory
@@ -104,18 +108,15 @@ __device__ __forceinline__ float2 unpack_h2(uint32_t u) {
 // 64-channel staging sub-tile (128-byte swizzle: 16-byte chunk index XOR (row & 7)); `bias_s` at the chunk's bias.
 // ACT: 0 none, 1 relu, 2 = read p.act at run time. All loads are issued before the arithmetic.
 template <int ACT, bool RES>
-__device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t taddr, uint8_t* stage_row, uint32_t ch0,
-                                               uint32_t row_xor, const uint8_t* bias_s, int n, int left) {
+__device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t taddr, uint32_t stage_row, uint32_t ch0,
+                                               uint32_t row_xor, uint32_t bias_s, int n, int left) {
     uint32_t v[32];
     __syncwarp();
     tmem_ld_32x32b_x32(taddr, v);     // in flight while the bias and residual chunks are fetched from shared memory
-    uint4 bw[4], rw[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) bw[j] = *reinterpret_cast<const uint4*>(bias_s + 16 * j);
+    uint4 rw[4];
     if (RES) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            rw[j] = *reinterpret_cast<const uint4*>(stage_row + (((ch0 + j) ^ row_xor) << 4));
+        for (int j = 0; j < 4; ++j) rw[j] = lds128(stage_row + (((ch0 + j) ^ row_xor) << 4));
     }
 #ifdef FVM_CONV_TRACE
     const long long tr0 = clock64();
@@ -128,38 +129,50 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         if (8 * j < left) {
-            float f[8];
-            const uint32_t b4[4] = {bw[j].x, bw[j].y, bw[j].z, bw[j].w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 t = unpack_h2(b4[k]);
-                f[2 * k] = __uint_as_float(v[8 * j + 2 * k]) + t.x;
-                f[2 * k + 1] = __uint_as_float(v[8 * j + 2 * k + 1]) + t.y;
-            }
-            if (p.scale) {
-                const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.scale + n + 8 * j));
-                const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.scale + n + 8 * j + 4));
-                f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
-                f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
-            }
-            if (RES) {
-                const uint32_t r4[4] = {rw[j].x, rw[j].y, rw[j].z, rw[j].w};
+            const uint32_t r4[4] = {rw[j].x, rw[j].y, rw[j].z, rw[j].w};
+            uint32_t o[4];
+            unsigned long long bw[4];     // 8 fp32 bias values as 4 pairs
+            lds_2xf2(bias_s + 32u * j, bw[0], bw[1]);
+            lds_2xf2(bias_s + 32u * j + 16u, bw[2], bw[3]);
+            if (ACT != 2 && p.scale == nullptr) {
+                // fast path: packed fp32 adds, activation on the packed fp16 result (relu commutes with the rounding)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float2 t = unpack_h2(r4[k]);
-                    f[2 * k] += t.x;
-                    f[2 * k + 1] += t.y;
+                    unsigned long long t = f2_add(f2_pack(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]), bw[k]);
+                    if (RES) t = f2_add(t, h2_to_f2(r4[k]));
+                    o[k] = f2_to_h2(t);
+                    if (ACT == 1) o[k] = h2_relu(o[k]);
                 }
-            }
-            if (ACT == 1) {
+            } else {
+                float f[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) f[k] = fmaxf(f[k], 0.f);
-            } else if (ACT == 2) {
+                for (int k = 0; k < 4; ++k) {
+                    float blo, bhi;
+                    f2_unpack(bw[k], blo, bhi);
+                    f[2 * k] = __uint_as_float(v[8 * j + 2 * k]) + blo;
+                    f[2 * k + 1] = __uint_as_float(v[8 * j + 2 * k + 1]) + bhi;
+                }
+                if (p.scale) {
+                    const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.scale + n + 8 * j));
+                    const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.scale + n + 8 * j + 4));
+                    f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
+                    f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
+                }
+                if (RES) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) f[k] = act_f(f[k], p.act);
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 t = unpack_h2(r4[k]);
+                        f[2 * k] += t.x;
+                        f[2 * k + 1] += t.y;
+                    }
+                }
+                const int act = ACT == 2 ? p.act : ACT;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] = act_f(f[k], act);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] = pack_h2(f[2 * k], f[2 * k + 1]);
             }
-            *reinterpret_cast<uint4*>(stage_row + (((ch0 + j) ^ row_xor) << 4)) =
-                make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]), pack_h2(f[6], f[7]));
+            sts128(stage_row + (((ch0 + j) ^ row_xor) << 4), make_uint4(o[0], o[1], o[2], o[3]));
         }
     }
 #ifdef FVM_CONV_TRACE
@@ -170,18 +183,35 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
 // All columns of this thread's row of one tile. BN is a multiple of 32, so every TMEM read is a full 32-column load
 // inside the accumulator buffer.
 template <int ACT, bool RES>
-__device__ __forceinline__ void epilogue_rows(const ConvParams& p, uint32_t t_row, uint8_t* stage_row0, uint32_t row_xor,
-                                              const uint8_t* bias_s, int n0, int ncols) {
+__device__ __forceinline__ void epilogue_rows(const ConvParams& p, uint32_t t_row, uint32_t stage_row0, uint32_t row_xor,
+                                              uint32_t bias_s, int n0, int ncols) {
     for (int c0 = 0; c0 < ncols; c0 += 32) {
-        uint8_t* sub = stage_row0 + static_cast<uint32_t>(c0 >> 6) * SUB_BYTES;
+        const uint32_t sub = stage_row0 + static_cast<uint32_t>(c0 >> 6) * SUB_BYTES;
         epilogue_chunk<ACT, RES>(p, t_row + static_cast<uint32_t>(c0), sub, static_cast<uint32_t>((c0 & 63) >> 3), row_xor,
-                                 bias_s + 2 * (n0 + c0), n0 + c0, ncols - c0);
+                                 bias_s + 4u * static_cast<uint32_t>(n0 + c0), n0 + c0, ncols - c0);
     }
+}
+
+// Tile number `it` of this CTA. Default: tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the n-tile fastest.
+// Weight-resident mode: the CTA owns n-tile (blockIdx.x % n_tiles) and walks m-tiles with stride gridDim.x / n_tiles
+// (the grid is a multiple of n_tiles).
+__device__ __forceinline__ bool tile_at(const ConvParams& p, int it, int& m_tile, int& n_tile) {
+    if (p.bres) {
+        const int q = static_cast<int>(fastdiv(blockIdx.x, p.div_ntiles));
+        n_tile = static_cast<int>(blockIdx.x) - q * p.n_tiles;
+        m_tile = q + it * static_cast<int>(fastdiv(gridDim.x, p.div_ntiles));
+        return m_tile < p.m_tiles;
+    }
+    const int tile = static_cast<int>(blockIdx.x) + it * static_cast<int>(gridDim.x);
+    if (tile >= p.m_tiles * p.n_tiles) return false;
+    m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
+    n_tile = tile - m_tile * p.n_tiles;
+    return true;
 }
 
 // Shared memory map (after rounding the base up to 1024 bytes):
 //   [stages x (A tile 16 KB | B tile BN*128 B)] [nepi x nsub x 16 KB staging] [barriers] [tmem slot, abort flag]
-//   [bias copy, fp16, zero-padded to n_tiles*BN]
+//   [bias copy, fp32, zero-padded to n_tiles*BN]
 // Staging sub-tiles use the same 128-byte swizzle as the TMA maps of the residual and the output, so the residual
 // arrives by TMA load, is combined in place by the epilogue threads (one row each, conflict-free 16-byte accesses)
 // and leaves by TMA store: every byte of global traffic of this kernel is a bulk copy.
@@ -191,14 +221,18 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t b_stage_bytes = p.tapk ? 0u : static_cast<uint32_t>(p.BN) * BK * 2;
-    const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
+    const uint32_t b_kb_bytes = static_cast<uint32_t>(p.BN) * BK * 2;          // one k-block of a weight tile
+    const uint32_t b_stage_bytes = (p.tapk || p.bres) ? 0u : b_kb_bytes;
+    const uint32_t a_stage_bytes = static_cast<uint32_t>(p.mt) * A_STAGE_BYTES;
+    const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
+    const uint32_t tap_a_bytes = static_cast<uint32_t>(p.mt) * TAP_A_BYTES;   // one tap of all sub-tiles of a stage
     // tap-packed mode: all weights of the (single) n-tile stay resident: one [BN x 16 B] block per tap
     const uint32_t tap_b_bytes = static_cast<uint32_t>(p.BN) * 16u;
     const uint32_t bres_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
-    const uint32_t bres_bytes = p.tapk ? static_cast<uint32_t>(p.kblocks * TAPS_PER_KBLOCK) * tap_b_bytes : 0u;
+    const uint32_t bres_bytes = p.tapk ? static_cast<uint32_t>(p.kblocks * TAPS_PER_KBLOCK) * tap_b_bytes
+                                       : (p.bres ? static_cast<uint32_t>(p.kblocks) * b_kb_bytes : 0u);
     const uint32_t epi_base = bres_base + bres_bytes;
-    const uint32_t epi_bytes = static_cast<uint32_t>(p.nsub) * SUB_BYTES;
+    const uint32_t epi_bytes = static_cast<uint32_t>(p.mt * p.nsub) * SUB_BYTES;   // staging: [mt][nsub] sub-tiles
     const uint32_t bar_base = epi_base + static_cast<uint32_t>(p.nepi) * epi_bytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
@@ -216,9 +250,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     static_assert((8 * NUM_BARRIERS + MISC_BYTES) % 16 == 0, "bias copy must be 16-byte aligned");
     const uint32_t bias_off = misc_off + MISC_BYTES;
     {
-        __half* bias_s = reinterpret_cast<__half*>(smem_raw + bias_off);
+        float* bias_s = reinterpret_cast<float*>(smem_raw + bias_off);     // fp32 copy: the epilogue adds it as packed pairs
         for (int i = threadIdx.x; i < p.bias_elems; i += CONV_THREADS)
-            bias_s[i] = (p.bias != nullptr && i < p.K) ? p.bias[i] : __float2half_rn(0.f);
+            bias_s[i] = (p.bias != nullptr && i < p.K) ? __half2float(p.bias[i]) : 0.f;
     }
     const uint32_t bias_base = smem_u32(smem_raw) + bias_off;
 
@@ -256,11 +290,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.m_tiles * p.n_tiles;
-
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop (uniform control flow); lane 0 arms the barriers, then several lanes issue
+        // their bulk loads in the same instruction (one lane per filter tap in tap-packed mode; A and B otherwise).
+        {
             int stage = 0;
             uint32_t phase = 0;
             int e = 0;
@@ -269,30 +303,43 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int PQ = p.P * p.Q;
             if (p.tapk) {
                 // weights of every tap (taps past R*S are out of bounds of the weight tensor: zero-filled)
-                mbar_expect_tx(bres_full_bar, bres_bytes);
-                for (int t = 0; t < p.kblocks * TAPS_PER_KBLOCK; ++t)
+                if (lane == 0) mbar_expect_tx(bres_full_bar, bres_bytes);
+                __syncwarp();
+                for (int t = lane; t < p.kblocks * TAPS_PER_KBLOCK; t += 32)
                     tma_load_3d(bres_base + static_cast<uint32_t>(t) * tap_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
             }
-            int pit = 0;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++pit) {
-                const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
-                const int n_tile = tile - m_tile * p.n_tiles;
-                const int m0 = m_tile * BM;
+            int m_tile, n_tile;
+            if (p.bres && tile_at(p, 0, m_tile, n_tile)) {
+                // this CTA's weight tile, all k-blocks, once: k-block kb = (tap kb / cchunks, channels (kb % cchunks)*64)
+                if (lane == 0) mbar_expect_tx(bres_full_bar, bres_bytes);
+                __syncwarp();
+                for (int kb = lane; kb < p.kblocks; kb += 32) {
+                    const int tp = kb / p.cchunks;
+                    tma_load_3d(bres_base + static_cast<uint32_t>(kb) * b_kb_bytes, &tmap_b, bres_full_bar,
+                                (kb - tp * p.cchunks) * BK, tp, n_tile * p.BN);
+                }
+            }
+            for (int pit = 0; ok && tile_at(p, pit, m_tile, n_tile); ++pit) {
+                const int m0 = m_tile * BM * p.mt;
                 const int n0 = n_tile * p.BN;
                 TRACE(0, pit, 0);
                 if (p.has_res) {
                     // residual tile of this output tile -> staging buffer e (free once its previous store was read out)
                     if (!mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag)) {
-                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
                         ok = false;
                         break;
                     }
                     e_phase ^= 1u << e;
                     const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
-                    mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(nsub) * SUB_BYTES);
-                    for (int sub = 0; sub < nsub; ++sub)
-                        tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
-                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0);
+                    if (lane == 0) mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(p.mt * nsub) * SUB_BYTES);
+                    __syncwarp();
+                    if (lane < p.mt * nsub) {     // one lane per staging sub-tile (at most 16)
+                        const int mt = lane / nsub, sub = lane - mt * nsub;
+                        tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes +
+                                        static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES,
+                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
+                    }
                     if (++e == p.nepi) e = 0;
                     TRACE(0, pit, 1);
                 }
@@ -308,37 +355,39 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
                         ok = false;
                         break;
                     }
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
-                    const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-                    if (kb == 0) TRACE(0, pit, 2);
-                    mbar_expect_tx(full_bar(stage), stage_bytes);
-                    if (kb == 0) TRACE(0, pit, 3);
+                    const uint32_t b_dst = a_dst + a_stage_bytes;
+                    if (lane == 0) mbar_expect_tx(full_bar(stage), stage_bytes);
+                    __syncwarp();
                     if (p.tapk) {
-                        // 8 taps of 8 channels: each lands as a dense [128 pixels][16 B] block (8-row x 16-byte core
+                        // 8 taps of 8 channels: each lands as a dense [128*mt pixels][16 B] block (8-row x 16-byte core
                         // matrices back to back). Taps past the filter re-read the last tap; their weights are zero.
-                        for (int j = 0; j < TAPS_PER_KBLOCK; ++j) {
+                        if (lane < TAPS_PER_KBLOCK) {
+                            const int j = lane;
                             const int t = min(kb * TAPS_PER_KBLOCK + j, p.taps - 1);
                             const int tr = t / p.S, ts = t - tr * p.S;
-                            tma_load_im2col_4d(a_dst + static_cast<uint32_t>(j) * TAP_A_BYTES, &tmap_a, full_bar(stage), 0,
+                            tma_load_im2col_4d(a_dst + static_cast<uint32_t>(j) * tap_a_bytes, &tmap_a, full_bar(stage), 0,
                                                w0, h0, img, static_cast<uint16_t>(ts * p.dw),
                                                static_cast<uint16_t>(tr * p.dh));
                         }
                         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
-                    if (p.im2col) {
-                        tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
-                                           static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
-                    } else {
-                        tma_load_2d(a_dst, &tmap_a, full_bar(stage), cc * BK, m0);
+                    if (lane == 0) {
+                        if (!p.bres) tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    } else if (p.im2col) {
+                        if (lane == 1)
+                            tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
+                                               static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                    } else if (lane <= p.a_loads) {
+                        const int l = lane - 1;
+                        tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage), cc * BK,
+                                    m0 + l * p.a_rows);
                     }
-                    if (kb == 0) TRACE(0, pit, 4);
-                    tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
-                    if (kb == 0) TRACE(0, pit, 5);
                     if (++cc == p.cchunks) {
                         cc = 0;
                         ++tap;
@@ -366,11 +415,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t acc_phase = 0;   // one parity bit per accumulator buffer
             int it = 0;
             bool ok = true;
-            if (p.tapk && blockIdx.x < total_tiles && !mbar_wait(bres_full_bar, 0u, abort_flag)) {
+            int m_tile, n_tile;
+            if ((p.tapk || p.bres) && tile_at(p, 0, m_tile, n_tile) && !mbar_wait(bres_full_bar, 0u, abort_flag)) {
                 atomicExch(p.status, STATUS_WAIT_MMA);
                 ok = false;
             }
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            for (; ok && tile_at(p, it, m_tile, n_tile); ++it) {
                 const int acc = it % p.nacc;
                 if (!mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag)) {
                     atomicExch(p.status, STATUS_WAIT_MMA);
@@ -393,25 +443,34 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (p.tapk) {
                         // K = 16 spans two taps: the two 16-byte K halves are one tap block apart (LBO); 8-row groups
                         // are 128 bytes apart (SBO); no swizzle
+                        for (int mt = 0; mt < p.mt; ++mt) {
 #pragma unroll
-                        for (int k = 0; k < TAPS_PER_KBLOCK / 2; ++k) {
-                            const uint64_t a_desc = umma_desc_interleaved(a_src + static_cast<uint32_t>(2 * k) * TAP_A_BYTES,
-                                                                          TAP_A_BYTES, 128u);
-                            const uint64_t b_desc = umma_desc_interleaved(
-                                bres_base + static_cast<uint32_t>(kb * TAPS_PER_KBLOCK + 2 * k) * tap_b_bytes, tap_b_bytes, 128u);
-                            umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+                            for (int k = 0; k < TAPS_PER_KBLOCK / 2; ++k) {
+                                const uint64_t a_desc = umma_desc_interleaved(
+                                    a_src + static_cast<uint32_t>(2 * k) * tap_a_bytes + static_cast<uint32_t>(mt) * TAP_A_BYTES,
+                                    tap_a_bytes, 128u);
+                                const uint64_t b_desc = umma_desc_interleaved(
+                                    bres_base + static_cast<uint32_t>(kb * TAPS_PER_KBLOCK + 2 * k) * tap_b_bytes, tap_b_bytes,
+                                    128u);
+                                umma_f16(d_tmem + static_cast<uint32_t>(mt * p.BN), a_desc, b_desc, idesc,
+                                         (kb | k) != 0 ? 1u : 0u);
+                            }
                         }
                         umma_commit(empty_bar(stage));
                         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
-                    const uint64_t a_desc = umma_desc_sw128(a_src);
-                    const uint64_t b_desc = umma_desc_sw128(a_src + A_STAGE_BYTES);
+                    const uint64_t b_desc = umma_desc_sw128(p.bres ? bres_base + static_cast<uint32_t>(kb) * b_kb_bytes
+                                                                   : a_src + a_stage_bytes);
+                    for (int mt = 0; mt < p.mt; ++mt) {
+                        // sub-tile mt: its own 128 rows of A, the shared B tile, accumulator columns [mt*BN, (mt+1)*BN)
+                        const uint64_t a_desc = umma_desc_sw128(a_src + static_cast<uint32_t>(mt) * A_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        // advancing 16 halves (32 bytes) along K inside the swizzle row: +2 in the >>4 address field
-                        umma_f16(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
-                                 idesc, (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < BK / 16; ++k) {
+                            // advancing 16 halves (32 bytes) along K inside the swizzle row: +2 in the >>4 address field
+                            umma_f16(d_tmem + static_cast<uint32_t>(mt * p.BN), a_desc + static_cast<uint64_t>(2 * k),
+                                     b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
                     if (kb == 0) TRACE(1, it, 3);
                     umma_commit(empty_bar(stage));   // frees the stage once these MMAs have read it
@@ -430,22 +489,21 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int group = (warp - 2) >> 2;
         const int row = lane_group * 32 + lane;       // row of the tile = TMEM lane
         const uint32_t row_xor = static_cast<uint32_t>(row & 7);
-        const uint8_t* bias_s = smem_raw + bias_off;
-        uint8_t* stage0 = smem_raw + (epi_base - smem_u32(smem_raw)) + static_cast<uint32_t>(row) * 128u;
+        const uint32_t bias_s = bias_base;
+        const uint32_t stage0 = epi_base + static_cast<uint32_t>(row) * 128u;
         uint32_t acc_phase = 0;   // parity of this group's accumulator buffer
         uint32_t e_phase = 0;     // one parity bit per staging buffer (advanced for every tile, also the other groups')
         int e = 0;
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        int m_tile, n_tile;
+        for (; ok && tile_at(p, it, m_tile, n_tile); ++it) {
             const int acc = it % p.nacc;
             if (acc != group) {       // another group's tile: only keep the staging-buffer bookkeeping in step
                 e_phase ^= 1u << e;
                 if (++e == p.nepi) e = 0;
                 continue;
             }
-            const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
-            const int n_tile = tile - m_tile * p.n_tiles;
             const int n0 = n_tile * p.BN;
             TRACE(2 + group, it, 0);
             // staging buffer: with a residual it is filled by TMA (res_full); without, wait until it is free
@@ -463,15 +521,20 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             TRACE(2 + group, it, 2);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                    static_cast<uint32_t>(acc * p.acc_stride);
-            uint8_t* stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
+            const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
             const int ncols = min(p.BN, p.K - n0);   // multiple of 8
-            switch ((p.act == 0 ? 0 : (p.act == 1 ? 1 : 2)) * 2 + (p.has_res ? 1 : 0)) {
-                case 0: epilogue_rows<0, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols); break;
-                case 1: epilogue_rows<0, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols); break;
-                case 2: epilogue_rows<1, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols); break;
-                case 3: epilogue_rows<1, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols); break;
-                case 4: epilogue_rows<2, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols); break;
-                default: epilogue_rows<2, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols); break;
+            const int variant = (p.act == 0 ? 0 : (p.act == 1 ? 1 : 2)) * 2 + (p.has_res ? 1 : 0);
+            for (int mt = 0; mt < p.mt; ++mt) {
+                const uint32_t t_sub = t_row + static_cast<uint32_t>(mt * p.BN);
+                const uint32_t s_sub = stage_row0 + static_cast<uint32_t>(mt * p.nsub) * SUB_BYTES;
+                switch (variant) {
+                    case 0: epilogue_rows<0, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 1: epilogue_rows<0, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 2: epilogue_rows<1, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 3: epilogue_rows<1, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 4: epilogue_rows<2, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    default: epilogue_rows<2, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                }
             }
             TRACE(2 + group, it, 3);
             // all TMEM reads of this warp are done: hand the accumulator back; publish this warp's rows of the staged
@@ -492,11 +555,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             int e = 0;
             bool ok = true;
-            int sit = 0;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++sit) {
-                const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
-                const int n_tile = tile - m_tile * p.n_tiles;
-                const int m0 = m_tile * BM;
+            int m_tile, n_tile;
+            for (int sit = 0; ok && tile_at(p, sit, m_tile, n_tile); ++sit) {
+                const int m0 = m_tile * BM * p.mt;
                 const int n0 = n_tile * p.BN;
                 TRACE(6, sit, 0);
                 if (!mbar_wait<EPI_BACKOFF_NS>(epi_done_bar(e), (e_phase >> e) & 1u, abort_flag)) {
@@ -507,9 +568,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 e_phase ^= 1u << e;
                 TRACE(6, sit, 1);
                 const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
-                for (int sub = 0; sub < nsub; ++sub)
-                    tma_store_2d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
-                                 n0 + sub * 64, m0);
+                for (int mt = 0; mt < p.mt && m0 + mt * BM < p.M; ++mt)     // sub-tiles past the last row: nothing to store
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_store_2d(&tmap_y,
+                                     epi_base + static_cast<uint32_t>(e) * epi_bytes +
+                                         static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES,
+                                     n0 + sub * 64, m0 + mt * BM);
                 tma_store_commit();
                 TRACE(6, sit, 2);
                 tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
@@ -576,12 +640,14 @@ struct SmemPlan {
     int stages, nepi, nacc;
     size_t bytes;
 };
-static bool plan_smem(int BN, int kblocks, int K, bool tapk, SmemPlan* out) {
+static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, SmemPlan* out) {
     const int n_tiles = (K + BN - 1) / BN;
-    const uint32_t stage_bytes = A_STAGE_BYTES + (tapk ? 0u : static_cast<uint32_t>(BN) * BK * 2);
-    const uint32_t bres_bytes = tapk ? static_cast<uint32_t>(kblocks * TAPS_PER_KBLOCK) * BN * 16u : 0u;
-    const uint32_t epi_bytes = static_cast<uint32_t>((BN + 63) / 64) * SUB_BYTES;
-    const uint32_t bias_bytes = (static_cast<uint32_t>(n_tiles * BN) * 2 + 15u) & ~15u;
+    const uint32_t stage_bytes =
+        static_cast<uint32_t>(MT) * A_STAGE_BYTES + ((tapk || bres) ? 0u : static_cast<uint32_t>(BN) * BK * 2);
+    const uint32_t bres_bytes = tapk ? static_cast<uint32_t>(kblocks * TAPS_PER_KBLOCK) * BN * 16u
+                                     : (bres ? static_cast<uint32_t>(kblocks) * BN * BK * 2 : 0u);
+    const uint32_t epi_bytes = static_cast<uint32_t>(MT * ((BN + 63) / 64)) * SUB_BYTES;
+    const uint32_t bias_bytes = (static_cast<uint32_t>(n_tiles * BN) * 4 + 15u) & ~15u;   // fp32 copy of the bias
     if (bias_bytes > MAX_BIAS_BYTES) return false;
     const uint32_t fixed = 1024 + 8 * NUM_BARRIERS + MISC_BYTES + bias_bytes + bres_bytes;
     const uint32_t total = 227 * 1024;
@@ -592,7 +658,8 @@ static bool plan_smem(int BN, int kblocks, int K, bool tapk, SmemPlan* out) {
     // Short reductions are epilogue-dominated: 4 accumulators and one staging buffer per epilogue group plus spares for
     // stores in flight. Deep reductions keep 2 accumulators / 2-3 staging buffers and give the pipeline the memory.
     int acc_stride = 32;
-    while (acc_stride < BN) acc_stride <<= 1;
+    while (acc_stride < MT * BN) acc_stride <<= 1;
+    if (acc_stride > 256) return false;    // at least two accumulator buffers in the 512 TMEM columns
     const int max_acc = 512 / acc_stride < MAX_ACC ? 512 / acc_stride : MAX_ACC;
     int nacc = (kblocks <= 8 && max_acc >= 4) ? 4 : 2;
     const int min_stages = 4;   // loads in flight span tiles of this persistent CTA, also when one tile has a single k-block
@@ -628,7 +695,7 @@ static int pick_bn(int m_tiles, int K, int kblocks, bool tapk, int sms) {
     for (int i = 0; i < nc; ++i) {
         const int bn = cands[i];
         SmemPlan sp;
-        if (!plan_smem(bn, kblocks, K, tapk, &sp)) continue;
+        if (!plan_smem(bn, 1, kblocks, K, tapk, false, &sp)) continue;
         const int nt = (K + bn - 1) / bn;
         const long long tiles = static_cast<long long>(m_tiles) * nt;
         const long long waves = (tiles + sms - 1) / sms;
@@ -644,12 +711,35 @@ static int pick_bn(int m_tiles, int K, int kblocks, bool tapk, int sms) {
     return best;
 }
 
+// Sub-tiles per tile. Layers with a short reduction spend their time in per-tile hand-offs between the single-thread
+// roles (barrier round trips, TMA and MMA issue), not in the tensor pipe: a tile of 256 or 512 output pixels amortises
+// them. Used when the accumulators still fit TMEM twice, the pipeline keeps 3 stages and every CTA still gets several
+// tiles.
+static int pick_mt(int BN, int m_tiles128, int n_tiles, int kblocks, int K, bool tapk, int sms) {
+    if (kblocks > 8) return 1;
+    for (int mt = 4; mt >= 2; mt >>= 1) {
+        if (mt * BN > 256) continue;
+        const long long tiles = static_cast<long long>((m_tiles128 + mt - 1) / mt) * n_tiles;
+        if (tiles < 4ll * sms) continue;
+        SmemPlan sp;
+        if (!plan_smem(BN, mt, kblocks, K, tapk, false, &sp)) continue;
+        if (sp.stages < 3 || sp.nepi < 2) continue;
+        return mt;
+    }
+    return 1;
+}
+
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, cudaStream_t stream) {
     DeviceState* st = device_state();
     if (!st) return FVM_ERR_SETUP;
     if (!x || !w || !y) return FVM_ERR_ARG;
+    // force_bn: low 16 bits = output-channel tile (0 = choose), bits 16..23 = sub-tiles per tile (0 = choose),
+    // bits 24..25 = weight-resident mode (0 = choose, 1 = on, 2 = off)
+    const int force_bres = force_bn > 0 ? ((force_bn >> 24) & 3) : 0;
+    const int force_mt = force_bn > 0 ? ((force_bn >> 16) & 0xff) : 0;
+    force_bn = force_bn > 0 ? (force_bn & 0xffff) : 0;
     if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0 || R <= 0 || S <= 0) return FVM_ERR_ARG;
     if ((C & 7) || (K & 7) || (ldx & 7) || (ldy & 7) || (res && (ldr & 7))) return FVM_ERR_ARG;
     if (sh <= 0 || sw <= 0 || dh <= 0 || dw <= 0 || ph < 0 || pw < 0) return FVM_ERR_ARG;
@@ -680,7 +770,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         const int Kp16 = (K + 31) / 32 * 32;   // tiles are multiples of 32 channels
         SmemPlan tp;
         p.tapk = (C == 8 && R * S > 1 && Kp16 <= 256 && (force_bn <= 0 || force_bn >= Kp16) &&
-                  plan_smem(Kp16, (R * S + TAPS_PER_KBLOCK - 1) / TAPS_PER_KBLOCK, K, true, &tp)) ? 1 : 0;
+                  plan_smem(Kp16, 1, (R * S + TAPS_PER_KBLOCK - 1) / TAPS_PER_KBLOCK, K, true, false, &tp)) ? 1 : 0;
         if (p.tapk) {
             p.kblocks = (R * S + TAPS_PER_KBLOCK - 1) / TAPS_PER_KBLOCK;
             force_bn = Kp16;
@@ -700,15 +790,38 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.div_pq = fastdiv_init(static_cast<uint32_t>(P) * Q);
     p.div_q = fastdiv_init(static_cast<uint32_t>(Q));
     p.nsub = (p.BN + 63) / 64;
+    // Measured on B200: larger tiles did not pay for themselves on the layers tried (fewer, larger hand-offs but less
+    // overlap between the roles), so the default stays at one sub-tile; the host's per-layer tuning may force more.
+    p.mt = force_mt > 0 ? force_mt : 1;
+    (void)&pick_mt;
+    if (p.mt != 1 && p.mt != 2 && p.mt != 4) return FVM_ERR_ARG;
+    p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
+    p.a_rows = BM * p.mt < 256 ? BM * p.mt : 256;
+    p.a_loads = BM * p.mt / p.a_rows;
 
+    // Weight-resident mode: the weight tile of a CTA's n-tile (all k-blocks) is loaded once and kept; the stages then
+    // carry activations only, so more tiles' worth of loads are in flight and the weights are not re-read from L2 for
+    // every tile. Used when the tile fits in 96 KB, every CTA gets at least two tiles, and the grid can be made a
+    // multiple of the n-tile count.
     SmemPlan sp;
-    if (!plan_smem(p.BN, p.kblocks, K, p.tapk != 0, &sp)) return FVM_ERR_ARG;
+    p.bres = 0;
+    if (!p.tapk && force_bres != 2 && p.n_tiles <= st->sms) {
+        const long long wbytes = static_cast<long long>(p.kblocks) * p.BN * BK * 2;
+        const int cta_per_n = st->sms / p.n_tiles;
+        const bool worth = p.m_tiles >= 2 * cta_per_n;
+        SmemPlan rp;
+        if (wbytes <= 96 * 1024 && (worth || force_bres == 1) &&
+            plan_smem(p.BN, p.mt, p.kblocks, K, false, true, &rp) && (rp.stages >= 4 || force_bres == 1))
+            p.bres = 1;
+    }
+    if (force_bres == 1 && !p.bres) return FVM_ERR_ARG;
+    if (!plan_smem(p.BN, p.mt, p.kblocks, K, p.tapk != 0, p.bres != 0, &sp)) return FVM_ERR_ARG;
     p.bias_elems = p.n_tiles * p.BN;
     p.stages = sp.stages;
     p.nepi = sp.nepi;
     p.nacc = sp.nacc;
     p.acc_stride = 32;
-    while (p.acc_stride < p.BN) p.acc_stride <<= 1;
+    while (p.acc_stride < p.mt * p.BN) p.acc_stride <<= 1;
     p.tmem_cols = p.nacc * p.acc_stride;   // a power of two between 64 and 512
     // Always request more than half of an SM's shared memory: at most one CTA per SM, so the TMEM request of a CTA
     // never waits on a co-resident CTA of the same kernel.
@@ -751,7 +864,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (!p.im2col) {
         cuuint64_t dims[2] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(p.M)};
         cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldx) * 2};
-        cuuint32_t box[2] = {BK, BM};
+        cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(p.a_rows)};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = g_encode_tiled(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides,
                                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -771,7 +884,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         int upper[2] = {up_w, up_h};
         cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
         CUresult r = g_encode_im2col(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(x), dims, strides,
-                                     lower, upper, p.tapk ? 8 : BK, BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     lower, upper, p.tapk ? 8 : BK, static_cast<cuuint32_t>(BM * p.mt), estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE,
                                      p.tapk ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -784,7 +898,12 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     }
 
     const long long total_tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-    const int grid = static_cast<int>(total_tiles < st->sms ? total_tiles : st->sms);
+    int grid = static_cast<int>(total_tiles < st->sms ? total_tiles : st->sms);
+    if (p.bres) {
+        int cta_per_n = st->sms / p.n_tiles;
+        if (cta_per_n > p.m_tiles) cta_per_n = p.m_tiles;
+        grid = cta_per_n * p.n_tiles;
+    }
     conv_tcgen05_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;

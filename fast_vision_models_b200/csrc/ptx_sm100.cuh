@@ -155,6 +155,44 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
                  : "memory");
 }
 
+// Two fp32 values in one 64-bit register and packed arithmetic on them (sm_100 executes add.f32x2 as one instruction).
+__device__ __forceinline__ unsigned long long f2_pack(uint32_t lo, uint32_t hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// (lo, hi) fp32 pair -> one fp16x2 word, round to nearest even
+__device__ __forceinline__ uint32_t f2_to_h2(unsigned long long v) {
+    float lo, hi;
+    f2_unpack(v, lo, hi);
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// fp16x2 word -> (lo, hi) fp32 pair
+__device__ __forceinline__ unsigned long long h2_to_f2(uint32_t h) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+    return f2_pack(__float_as_uint(f.x), __float_as_uint(f.y));
+}
+__device__ __forceinline__ uint32_t h2_relu(uint32_t h) {
+    uint32_t r;
+    asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(h), "r"(0u));
+    return r;
+}
+// 16 bytes of shared memory as two fp32 pairs. Not volatile: only for data that is constant while the kernel's
+// roles run (the bias copy), so the compiler may schedule it freely.
+__device__ __forceinline__ void lds_2xf2(uint32_t addr, unsigned long long& a, unsigned long long& b) {
+    asm("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)

@@ -86,6 +86,47 @@ def test_conv_every_tile_width(tile):
     close(y, ref)
 
 
+@pytest.mark.parametrize("mt", [1, 2, 4])
+@pytest.mark.parametrize("case", [(3, 20, 20, 64, 64, 1, 0, True), (3, 20, 20, 64, 64, 3, 1, False),
+                                  (3, 23, 23, 8, 64, 7, 3, False), (5, 9, 9, 128, 128, 1, 0, True),
+                                  (1, 5, 5, 64, 32, 1, 0, False)])
+def test_conv_tiles_of_several_sub_tiles(case, mt):
+    # tiles of 128*mt output pixels (mt sub-tiles share one weight tile and one hand-off): ragged last tiles included
+    N, H, W, C, K, Rr, pad, res = case
+    if mt * ((K + 31) // 32 * 32) > 256:
+        pytest.skip("accumulators would not fit TMEM twice")
+    x, w, b = gen((N, C, H, W), 1), gen((K, C, Rr, Rr), 2, 0.05), gen((K,), 3, 0.1)
+    stride = 2 if C == 8 else 1
+    P = (H + 2 * pad - Rr) // stride + 1
+    r = gen((N, K, P, P), 4) if res else None
+    ref = R.conv_fused_ref(x, w, b, r, (pad, pad), (stride, stride), 1)
+    try:
+        y = ops.conv_fused(cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (stride, stride), 1,
+                           tile_n=mt << 16)
+    except ops.FvmError:
+        assert mt == 4      # four sub-tiles may not fit shared memory; the library must say so, not mis-compute
+        return
+    assert ops.last_status() == 0
+    close(y, ref)
+
+
+@pytest.mark.parametrize("case", [(4, 20, 20, 64, 256, 1, 0, True, 64), (4, 20, 20, 64, 256, 1, 0, True, 128),
+                                  (3, 14, 14, 256, 1024, 1, 0, True, 128), (2, 20, 20, 64, 64, 3, 1, False, 64),
+                                  (2, 9, 9, 144, 40, 1, 0, True, 0), (64, 14, 14, 256, 64, 1, 0, False, 0)])
+def test_conv_weight_resident_mode_matches_streaming_mode(case):
+    # each CTA keeps the weight tile of one n-tile in shared memory and walks the m-tiles: same results, bit for bit
+    N, H, W, C, K, Rr, pad, res, bn = case
+    x, w, b = gen((N, C, H, W), 1), gen((K, C, Rr, Rr), 2, 0.05), gen((K,), 3, 0.1)
+    r = gen((N, K, H, W), 4) if res else None
+    ref = R.conv_fused_ref(x, w, b, r, (pad, pad), (1, 1), 1)
+    args = (cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (1, 1), 1)
+    y_on = ops.conv_fused(*args, tile_n=(1 << 24) | bn)
+    y_off = ops.conv_fused(*args, tile_n=(2 << 24) | bn)
+    assert ops.last_status() == 0
+    close(y_on, ref)
+    assert torch.equal(y_on, y_off)
+
+
 def test_conv_no_bias_scale_and_sliced_io():
     # input read from a channel slice, output written into a channel slice of a wider buffer (concat-free ASPP),
     # un-folded LayerScale as an fp32 epilogue scale
