@@ -19,7 +19,7 @@ CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 LIB_PATH = os.path.join(_HERE, "libfvm_b200.so")
 _STAMP = LIB_PATH + ".sha1"
-SOURCES = ["abi.cu", "conv_tcgen05.cu", "bandwidth.cu", "dwconv.cu", "noalloc.cu"]
+SOURCES = ["abi.cu", "conv_tcgen05.cu", "bandwidth.cu", "dwconv.cu"]
 HEADERS = ["fvm_internal.h", "ptx_sm100.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
@@ -109,6 +109,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "fvm_avgpool_f16": ([_P] * 2 + [_I] * 13 + [_P], _I),
         "fvm_gap_scratch_floats": ([_I] * 3, _L),
         "fvm_global_avgpool_f16": ([_P] * 3 + [_I] * 3 + [_L, _P], _I),
+        "fvm_global_avgpool_f16_noalloc": ([_P] * 2 + [_I] * 3 + [_L, _P], _I),
+        "fvm_global_avgpool_f16_noalloc_max_floats": ([], _L),
         "fvm_se_gate_f16": ([_P] * 6 + [_I] * 4 + [_F, _P], _I),
         "fvm_se_scale_f16": ([_P] * 3 + [_I] * 3 + [_P], _I),
         "fvm_layernorm_cl_f16": ([_P] * 4 + [_L, _I, _F, _L, _L, _P], _I),
@@ -133,6 +135,7 @@ def _declare(lib: ctypes.CDLL) -> None:
 OPTIONAL_SIGNATURES: dict = {}
 
 EXPORTED = ["fvm_init", "fvm_query", "fvm_last_status", "fvm_conv2d_f16", "fvm_dwconv_f16", "fvm_maxpool_f16",
-            "fvm_avgpool_f16", "fvm_gap_scratch_floats", "fvm_global_avgpool_f16", "fvm_se_gate_f16",
+            "fvm_avgpool_f16", "fvm_gap_scratch_floats", "fvm_global_avgpool_f16", "fvm_global_avgpool_f16_noalloc",
+            "fvm_global_avgpool_f16_noalloc_max_floats", "fvm_se_gate_f16",
             "fvm_se_scale_f16", "fvm_layernorm_cl_f16", "fvm_input_nhwc8_f32", "fvm_bias_act_f16",
             "fvm_affine_act_f16", "fvm_add_act_f16", "fvm_bilinear_f16", "fvm_up_argmax_f16"]

@@ -652,3 +652,55 @@ extern "C" int fvm_up_argmax_f16(const void* s, int32_t* out, int N, int h, int 
         resize_scale(w, W, align, 0.f), total);
     FVM_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------- allocation-free GAP
+// Global average pool for callers that must not allocate: the fp32 partial sums live in a fixed array inside the
+// library image instead of a caller-provided scratch buffer. Every GPU that loads the library carries the array
+// (FVM_GAP_NOALLOC_MAX_FLOATS * 4 bytes = 4 MiB) until the process exits.
+#define FVM_GAP_NOALLOC_MAX_FLOATS (1 << 20)
+static __device__ __align__(256) float g_gap_noalloc_scratch[FVM_GAP_NOALLOC_MAX_FLOATS];
+
+namespace {
+struct NoAllocGapState {
+    float* scratch = nullptr;   // device address of g_gap_noalloc_scratch on this device
+    int sms = 0;
+    bool ready = false;
+};
+NoAllocGapState g_noalloc_gap[64];
+}  // namespace
+
+extern "C" long long fvm_global_avgpool_f16_noalloc_max_floats(void) { return FVM_GAP_NOALLOC_MAX_FLOATS; }
+
+extern "C" int fvm_global_avgpool_f16_noalloc(const void* x, void* y, int N, int HW, int C, long long ldx,
+                                              void* stream) {
+    if (!x || !y || N <= 0 || N > 65535 || HW <= 0 || C <= 0 || (C & 7) || (ldx & 7) || ldx < C || !aligned16(x))
+        return FVM_ERR_ARG;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FVM_ERR_SETUP;
+    NoAllocGapState& st = g_noalloc_gap[dev];
+    if (!st.ready) {
+        // First call on this device (it is the current device): in host code the array's name is only a handle, the
+        // address a kernel can use comes from the runtime. Nothing is allocated here.
+        float* ptr = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gap_noalloc_scratch) != cudaSuccess || !ptr)
+            return FVM_ERR_SETUP;
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            return FVM_ERR_SETUP;
+        st.scratch = ptr;
+        st.sms = sms;
+        st.ready = true;
+    }
+    const int splits = gap_splits(N, HW, C, st.sms);
+    if (static_cast<long long>(N) * splits * C > FVM_GAP_NOALLOC_MAX_FLOATS) return FVM_ERR_ARG;   // beyond the fixed scratch
+    const int chunk = (HW + splits - 1) / splits;
+    dim3 grid(((C >> 3) + GAP_VX - 1) / GAP_VX, splits, N), block(GAP_VX, GAP_RY);
+    // stage 1 overwrites every partial sum stage 2 reads: nothing in the shared array has to start at zero
+    gap_partial_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(x), st.scratch,
+                                                                              HW, C, ldx, splits, chunk);
+    count_launch();
+    const long long total = static_cast<long long>(N) * C;
+    gap_final_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        st.scratch, static_cast<__half*>(y), C, splits, 1.f / static_cast<float>(HW), total);
+    FVM_LAUNCH_CHECK();
+}

@@ -83,6 +83,19 @@ int fvm_avgpool_f16(const void* x, void* y, int N, int H, int W, int C, int kh, 
 long long fvm_gap_scratch_floats(int N, int HW, int C);
 int fvm_global_avgpool_f16(const void* x, void* y, float* partial, int N, int HW, int C, long long ldx, void* stream);
 
+/* Allocation-free variant of fvm_global_avgpool_f16 -- no counterpart in the reference. For callers that cannot
+ * obtain device memory at call time: code that runs while a stream is being captured, a serving loop that must never
+ * enter the driver's allocator, or a host process whose memory was carved up once at start-up and has no scratch to
+ * lend. The partial sums live in a 4 MiB array that is part of the library image on every GPU that loads it, so the
+ * caller passes only input and output. Returns 1 (FVM_ERR_ARG) when the problem needs more than
+ * fvm_global_avgpool_f16_noalloc_max_floats() floats of scratch (N * splits * C, the value fvm_gap_scratch_floats
+ * reports) -- it never falls back to allocating. The first call on a device looks up the array's device address (no
+ * allocation); make that call before any stream capture. All calls on a device share the one array: two calls whose
+ * kernels can overlap on the GPU (different streams, no ordering) race on it; calls ordered on one stream do not.
+ * Nothing in the array has to be cleared between calls. Results are bit-identical to fvm_global_avgpool_f16. */
+long long fvm_global_avgpool_f16_noalloc_max_floats(void);
+int fvm_global_avgpool_f16_noalloc(const void* x, void* y, int N, int HW, int C, long long ldx, void* stream);
+
 /* Squeeze-excite gate: s[n,:] = W2 * act(W1 * g[n,:] + b1) + b2 with g fp16 [N,C], W1 fp16 [Cs,C], W2 fp16 [C,Cs];
  * stands for the two clf::conv_fused calls on [N,C,1,1] tensors the reference issues (r3.py:188-199). Output fp16 [N,C]
  * (pre-sigmoid). If mean_scale != 0, g is read as fp32 sums [N,C] and multiplied by mean_scale first (fused squeeze). */
