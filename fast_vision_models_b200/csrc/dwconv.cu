@@ -155,6 +155,300 @@ dwconv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const 
     }
 }
 
+
+// Fast path for square 3/5/7-tap kernels without dilation: S, the stride and the strip width are compile-time, so the
+// accumulators (TW x 8 fp32) and one kernel row of weights (S x 8 fp32) stay in registers; every input vector of a
+// kernel row is loaded and converted once and feeds up to ceil(S / stride) outputs. Loads are the only memory
+// instructions in the inner loop: (TW-1)*stride + S input vectors and S weight vectors per kernel row per TW outputs.
+template <int S, int SW, int TW>
+__global__ void __launch_bounds__(DW_THREADS)
+dwconv_fast_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const __half* __restrict__ bias,
+                   __half* __restrict__ y, float* __restrict__ pool_sums, int H, int W, int C, int R, int P, int Q,
+                   int sh, int ph, int pw, long long ldx, long long ldy, int act, long long items_per_image) {
+    extern __shared__ float pool_acc[];   // [C] when pool_sums != nullptr
+    const int cv = C >> 3;
+    const long long n = blockIdx.y;
+    if (pool_sums) {
+        for (int c = threadIdx.x; c < C; c += DW_THREADS) pool_acc[c] = 0.f;
+        __syncthreads();
+    }
+    const long long i = static_cast<long long>(blockIdx.x) * DW_THREADS + threadIdx.x;
+    if (i < items_per_image) {
+        const int QT = (Q + TW - 1) / TW;
+        const int v = static_cast<int>(i % cv);
+        long long t = i / cv;
+        const int qt = static_cast<int>(t % QT);
+        const int p = static_cast<int>(t / QT);
+        const int q0 = qt * TW;
+
+        float acc[TW][8];
+        {
+            float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (bias) {
+                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + v * 8));
+                const __half2* hb = reinterpret_cast<const __half2*>(&bv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __half22float2(hb[k]);
+                    b[2 * k] = f.x;
+                    b[2 * k + 1] = f.y;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < TW; ++j)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[j][k] = b[k];
+        }
+
+        constexpr int L = (TW - 1) * SW + S;       // input columns one kernel row of the strip touches
+        const int iw0 = q0 * SW - pw;
+        const __half* ximg = x + n * H * W * ldx + v * 8;
+        for (int r = 0; r < R; ++r) {
+            const int h = p * sh - ph + r;
+            if (h < 0 || h >= H) continue;
+            const __half* xrow = ximg + static_cast<long long>(h) * W * ldx;
+            const __half* wrow = w + static_cast<long long>(r) * S * C + v * 8;
+            float wf[S][8];
+#pragma unroll
+            for (int s2 = 0; s2 < S; ++s2) {
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + static_cast<long long>(s2) * C));
+                const __half2* hw = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __half22float2(hw[k]);
+                    wf[s2][2 * k] = f.x;
+                    wf[s2][2 * k + 1] = f.y;
+                }
+            }
+#pragma unroll
+            for (int l = 0; l < L; ++l) {
+                const int ww = iw0 + l;
+                float xf[8];
+                if (ww >= 0 && ww < W) {
+                    const uint4 xv = __ldg(reinterpret_cast<const uint4*>(xrow + static_cast<long long>(ww) * ldx));
+                    const __half2* hx = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __half22float2(hx[k]);
+                        xf[2 * k] = f.x;
+                        xf[2 * k + 1] = f.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) xf[k] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < TW; ++j) {
+                    constexpr int dummy = 0;
+                    (void)dummy;
+                    const int s2 = l - j * SW;          // compile-time after unrolling
+                    if (s2 >= 0 && s2 < S) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc[j][k] = fmaf(xf[k], wf[s2][k], acc[j][k]);
+                    }
+                }
+            }
+        }
+
+        float psum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < TW; ++j) {
+            const int q = q0 + j;
+            if (q < Q) {
+                __align__(16) __half2 o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    o[k] = __floats2half2_rn(act_f(acc[j][2 * k], act), act_f(acc[j][2 * k + 1], act));
+                    if (pool_sums) {
+                        const float2 f = __half22float2(o[k]);
+                        psum[2 * k] += f.x;
+                        psum[2 * k + 1] += f.y;
+                    }
+                }
+                *reinterpret_cast<uint4*>(y + ((n * P + p) * Q + q) * ldy + v * 8) = *reinterpret_cast<uint4*>(o);
+            }
+        }
+        if (pool_sums) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) atomicAdd(&pool_acc[v * 8 + k], psum[k]);
+        }
+    }
+    if (pool_sums) {
+        __syncthreads();
+        for (int c = threadIdx.x; c < C; c += DW_THREADS) {
+            const float sum = pool_acc[c];
+            if (sum != 0.f) atomicAdd(pool_sums + n * C + c, sum);
+        }
+    }
+}
+
+
+// Tiled path (the default for square 3/5/7-tap kernels, stride 1 or 2, no dilation): a block stages the input halo
+// tile of TH x TWB output pixels x 64 channels in shared memory with 16-byte async copies (out-of-image taps are
+// zero-filled by the copy), so every input byte is fetched from L2 about once instead of once per kernel row; each
+// thread then produces a strip of 8 output columns for 8 channels from shared memory, with one kernel row of weights
+// and the 64 fp32 accumulators in registers.
+static constexpr int DWT_CBV = 8;        // channel vectors (of 8 channels) per block
+static constexpr int DWT_TW = 8;         // output columns per thread
+static constexpr int DWT_STRIPS = DW_THREADS / DWT_CBV;   // 16 strips per block
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+
+template <int S, int SW>
+__global__ void __launch_bounds__(DW_THREADS)
+dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const __half* __restrict__ bias,
+                   __half* __restrict__ y, float* __restrict__ pool_sums, int H, int W, int C, int R, int P, int Q,
+                   int sh, int ph, int pw, long long ldx, long long ldy, int act, int strips_x, int tiles_x,
+                   int tiles_y) {
+    extern __shared__ __align__(16) uint8_t dw_smem[];
+    const int cv = C >> 3;
+    const int TH = DWT_STRIPS / strips_x;                 // output rows per block
+    const int TWB = strips_x * DWT_TW;                    // output columns per block
+    const int tile_h = (TH - 1) * sh + R;
+    const int tile_w = (TWB - 1) * SW + S;
+    float* pool_acc = reinterpret_cast<float*>(dw_smem + static_cast<size_t>(tile_h) * tile_w * DWT_CBV * 16);
+
+    const long long n = blockIdx.y;
+    int bid = blockIdx.x;
+    const int tx = bid % tiles_x;
+    bid /= tiles_x;
+    const int ty = bid % tiles_y;
+    const int vb = bid / tiles_y;                          // channel-vector block
+    const int p0 = ty * TH, q0 = tx * TWB;
+    const int h0 = p0 * sh - ph, w0 = q0 * SW - pw;
+    const int v0 = vb * DWT_CBV;
+
+    if (pool_sums && threadIdx.x < DWT_CBV * 8) pool_acc[threadIdx.x] = 0.f;
+
+    // stage the halo tile: [tile_h][tile_w][DWT_CBV] vectors of 16 bytes
+    const __half* ximg = x + n * H * W * ldx;
+    const uint32_t smem0 = smem_u32(dw_smem);
+    const int total = tile_h * tile_w * DWT_CBV;
+    for (int idx = threadIdx.x; idx < total; idx += DW_THREADS) {
+        const int vv = idx % DWT_CBV;
+        const int px = idx / DWT_CBV;
+        const int cx = px % tile_w, cy = px / tile_w;
+        const int h = h0 + cy, ww = w0 + cx, v = v0 + vv;
+        const bool valid = h >= 0 && h < H && ww >= 0 && ww < W && v < cv;
+        const __half* src = valid ? ximg + (static_cast<long long>(h) * W + ww) * ldx + v * 8 : ximg;
+        cp_async16_zfill(smem0 + static_cast<uint32_t>(idx) * 16u, src, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    const int vv = threadIdx.x % DWT_CBV;
+    const int strip = threadIdx.x / DWT_CBV;
+    const int sx = strip % strips_x, sy = strip / strips_x;
+    const int v = v0 + vv;
+    const int p = p0 + sy, qs = q0 + sx * DWT_TW;
+    const bool active = v < cv && p < P && qs < Q;
+    if (active) {
+        // accumulators, weights and inputs as fp32 pairs: one packed FMA does two channels (same arithmetic as scalar
+        // fp32 FMAs, half the instructions)
+        unsigned long long acc[DWT_TW][4];
+        {
+            unsigned long long b2[4] = {0ull, 0ull, 0ull, 0ull};
+            if (bias) {
+                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + v * 8));
+                b2[0] = h2_to_f2(bv.x); b2[1] = h2_to_f2(bv.y); b2[2] = h2_to_f2(bv.z); b2[3] = h2_to_f2(bv.w);
+            }
+#pragma unroll
+            for (int j = 0; j < DWT_TW; ++j)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[j][k] = b2[k];
+        }
+        constexpr int L = (DWT_TW - 1) * SW + S;
+        for (int r = 0; r < R; ++r) {
+            const __half* wrow = w + static_cast<long long>(r) * S * C + v * 8;
+            unsigned long long wf[S][4];
+#pragma unroll
+            for (int s2 = 0; s2 < S; ++s2) {
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + static_cast<long long>(s2) * C));
+                wf[s2][0] = h2_to_f2(wv.x); wf[s2][1] = h2_to_f2(wv.y); wf[s2][2] = h2_to_f2(wv.z); wf[s2][3] = h2_to_f2(wv.w);
+            }
+            // row (sy*sh + r) of the tile, columns sx*8*SW .. + L
+            const uint32_t row_addr =
+                smem0 + (static_cast<uint32_t>((sy * sh + r) * tile_w + sx * DWT_TW * SW) * DWT_CBV + vv) * 16u;
+#pragma unroll
+            for (int l = 0; l < L; ++l) {
+                const uint4 xv = lds128(row_addr + static_cast<uint32_t>(l * DWT_CBV) * 16u);
+                const unsigned long long xf[4] = {h2_to_f2(xv.x), h2_to_f2(xv.y), h2_to_f2(xv.z), h2_to_f2(xv.w)};
+#pragma unroll
+                for (int j = 0; j < DWT_TW; ++j) {
+                    const int s2 = l - j * SW;          // compile-time after unrolling
+                    if (s2 >= 0 && s2 < S) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) acc[j][k] = f2_fma(xf[k], wf[s2][k], acc[j][k]);
+                    }
+                }
+            }
+        }
+        float psum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < DWT_TW; ++j) {
+            const int q = qs + j;
+            if (q < Q) {
+                __align__(16) __half2 o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float lo, hi;
+                    f2_unpack(acc[j][k], lo, hi);
+                    o[k] = __floats2half2_rn(act_f(lo, act), act_f(hi, act));
+                    if (pool_sums) {
+                        const float2 f = __half22float2(o[k]);
+                        psum[2 * k] += f.x;
+                        psum[2 * k + 1] += f.y;
+                    }
+                }
+                *reinterpret_cast<uint4*>(y + ((n * P + p) * Q + q) * ldy + v * 8) = *reinterpret_cast<uint4*>(o);
+            }
+        }
+        if (pool_sums) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) atomicAdd(&pool_acc[vv * 8 + k], psum[k]);
+        }
+    }
+    if (pool_sums) {
+        __syncthreads();
+        if (threadIdx.x < DWT_CBV * 8) {
+            const int c = v0 * 8 + threadIdx.x;
+            const float sum = pool_acc[threadIdx.x];
+            if (c < C && sum != 0.f) atomicAdd(pool_sums + n * C + c, sum);
+        }
+    }
+}
+
+template <int S, int SW>
+static int launch_dw_tile(const __half* xp, const __half* wp, const __half* bp, __half* yp, float* pool_sums, int N, int H,
+                          int W, int C, int R, int P, int Q, int sh, int ph, int pw, long long ldx, long long ldy, int act,
+                          cudaStream_t st) {
+    const int cv = C >> 3;
+    const int strips_x = Q > DWT_TW ? 2 : 1;
+    const int TH = DWT_STRIPS / strips_x, TWB = strips_x * DWT_TW;
+    const int tile_h = (TH - 1) * sh + R, tile_w = (TWB - 1) * SW + S;
+    const size_t smem = static_cast<size_t>(tile_h) * tile_w * DWT_CBV * 16 + DWT_CBV * 8 * sizeof(float);
+    if (smem > 200 * 1024) return -1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(dwconv_tile_kernel<S, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+            cudaSuccess)
+            return FVM_ERR_SETUP;
+        attr_set = true;
+    }
+    const int tiles_x = (Q + TWB - 1) / TWB, tiles_y = (P + TH - 1) / TH, vblocks = (cv + DWT_CBV - 1) / DWT_CBV;
+    const long long bx = static_cast<long long>(tiles_x) * tiles_y * vblocks;
+    if (bx > 0x7fffffffll) return FVM_ERR_ARG;
+    dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(N));
+    dwconv_tile_kernel<S, SW><<<grid, DW_THREADS, smem, st>>>(xp, wp, bp, yp, pool_sums, H, W, C, R, P, Q, sh, ph, pw, ldx,
+                                                              ldy, act, strips_x, tiles_x, tiles_y);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
+}
+
 }  // namespace fvm
 
 using namespace fvm;
@@ -174,6 +468,53 @@ extern "C" int fvm_dwconv_f16(const void* x, const void* w_rsc, const void* bias
     const int Q = (W + 2 * pw - dw * (S - 1) - 1) / sw + 1;
     if (P <= 0 || Q <= 0) return FVM_ERR_ARG;
     const int cv = C >> 3;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xp = static_cast<const __half*>(x);
+    const __half* wp = static_cast<const __half*>(w_rsc);
+    const __half* bp = static_cast<const __half*>(bias);
+    __half* yp = static_cast<__half*>(y);
+    const size_t smem = pool_sums ? static_cast<size_t>(C) * sizeof(float) : 0;
+    // Fast path: square 3/5/7 kernels, stride 1 or 2 (same in both directions), no dilation. Strips of 8 outputs on
+    // wide maps, 4 on narrow ones (the grid must still cover the machine a few times over).
+    if (R == S && (S == 3 || S == 5 || S == 7) && dh == 1 && dw == 1 && sh == sw && (sw == 1 || sw == 2) && Q >= 4) {
+        int rc = -1;
+        if (S == 3) rc = sw == 1 ? launch_dw_tile<3, 1>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st)
+                                 : launch_dw_tile<3, 2>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+        else if (S == 5) rc = sw == 1 ? launch_dw_tile<5, 1>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st)
+                                      : launch_dw_tile<5, 2>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+        else rc = sw == 1 ? launch_dw_tile<7, 1>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st)
+                          : launch_dw_tile<7, 2>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+        if (rc >= 0) return rc;      // -1: the tile does not fit shared memory, use the register path below
+    }
+    if (R == S && (S == 3 || S == 5 || S == 7) && dh == 1 && dw == 1 && sh == sw && (sw == 1 || sw == 2)) {
+        const long long work8 = static_cast<long long>(N) * P * ((Q + 7) / 8) * cv;
+        const int TWF = (Q >= 24 && work8 >= 148ll * 4 * DW_THREADS && S < 7) ? 8 : 4;
+        const int QTF = (Q + TWF - 1) / TWF;
+        const long long itemsF = static_cast<long long>(P) * QTF * cv;
+        const long long bxF = (itemsF + DW_THREADS - 1) / DW_THREADS;
+        if (bxF > 0x7fffffffll) return FVM_ERR_ARG;
+        dim3 gridF(static_cast<unsigned>(bxF), static_cast<unsigned>(N));
+#define DWF_GO(SV, SWV, TWV)                                                                                       \
+    dwconv_fast_kernel<SV, SWV, TWV><<<gridF, DW_THREADS, smem, st>>>(xp, wp, bp, yp, pool_sums, H, W, C, R, P, Q, sh, \
+                                                                      ph, pw, ldx, ldy, act, itemsF)
+#define DWF_S(SV)                                   \
+    do {                                            \
+        if (sw == 1) {                              \
+            if (TWF == 8) DWF_GO(SV, 1, 8);         \
+            else DWF_GO(SV, 1, 4);                  \
+        } else {                                    \
+            if (TWF == 8) DWF_GO(SV, 2, 8);         \
+            else DWF_GO(SV, 2, 4);                  \
+        }                                           \
+    } while (0)
+        if (S == 3) DWF_S(3);
+        else if (S == 5) DWF_S(5);
+        else DWF_S(7);
+#undef DWF_S
+#undef DWF_GO
+        count_launch();
+        return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
+    }
     // wide strips where rows are long; narrow ones on small maps so that the grid still fills the machine
     const int TW = Q >= 32 ? 4 : (Q >= 12 ? 2 : 1);
     const int QT = (Q + TW - 1) / TW;
@@ -181,12 +522,6 @@ extern "C" int fvm_dwconv_f16(const void* x, const void* w_rsc, const void* bias
     const long long bx = (items + DW_THREADS - 1) / DW_THREADS;
     if (bx > 0x7fffffffll) return FVM_ERR_ARG;
     dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(N));
-    const size_t smem = pool_sums ? static_cast<size_t>(C) * sizeof(float) : 0;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const __half* xp = static_cast<const __half*>(x);
-    const __half* wp = static_cast<const __half*>(w_rsc);
-    const __half* bp = static_cast<const __half*>(bias);
-    __half* yp = static_cast<__half*>(y);
 #define DW_GO(TWV)                                                                                                    \
     dwconv_kernel<TWV><<<grid, DW_THREADS, smem, st>>>(xp, wp, bp, yp, pool_sums, H, W, C, R, S, P, Q, sh, sw, ph, pw, \
                                                        dh, dw, ldx, ldy, act, items)
