@@ -22,6 +22,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "fvm_internal.h"
@@ -249,11 +250,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // the bias copy that follows is 16-byte aligned, as its 128-bit shared loads require
     static_assert((8 * NUM_BARRIERS + MISC_BYTES) % 16 == 0, "bias copy must be 16-byte aligned");
     const uint32_t bias_off = misc_off + MISC_BYTES;
-    {
-        float* bias_s = reinterpret_cast<float*>(smem_raw + bias_off);     // fp32 copy: the epilogue adds it as packed pairs
-        for (int i = threadIdx.x; i < p.bias_elems; i += CONV_THREADS)
-            bias_s[i] = (p.bias != nullptr && i < p.K) ? __half2float(p.bias[i]) : 0.f;
-    }
     const uint32_t bias_base = smem_u32(smem_raw) + bias_off;
 
     const int warp = threadIdx.x >> 5;
@@ -289,6 +285,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touches only this CTA's shared memory / TMEM and constant inputs. From here on the kernel reads
+    // activations and writes outputs, which must wait for the preceding kernels of the stream (programmatic dependent
+    // launch: this grid may have been started while its predecessor was still draining).
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -491,6 +492,14 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t row_xor = static_cast<uint32_t>(row & 7);
         const uint32_t bias_s = bias_base;
         const uint32_t stage0 = epi_base + static_cast<uint32_t>(row) * 128u;
+        {
+            // fp32 copy of the bias (the epilogue adds it as packed pairs), filled by the epilogue warps only, off the
+            // producer's and the MMA issuer's path; a named barrier over the 16 epilogue warps publishes it
+            float* bias_f = reinterpret_cast<float*>(smem_raw + bias_off);
+            for (int i = threadIdx.x - 64; i < p.bias_elems; i += EPI_WARPS * 32)
+                bias_f[i] = (p.bias != nullptr && i < p.K) ? __half2float(p.bias[i]) : 0.f;
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        }
         uint32_t acc_phase = 0;   // parity of this group's accumulator buffer
         uint32_t e_phase = 0;     // one parity bit per staging buffer (advanced for every tile, also the other groups')
         int e = 0;
@@ -903,6 +912,28 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         int cta_per_n = st->sms / p.n_tiles;
         if (cta_per_n > p.m_tiles) cta_per_n = p.m_tiles;
         grid = cta_per_n * p.n_tiles;
+    }
+    // Programmatic dependent launch: the grid may start (set-up only) while the previous kernel of the stream drains;
+    // the kernel itself waits (griddepcontrol.wait) before it touches activations or outputs.
+    static int use_pdl = [] { const char* v = getenv("FVM_B200_PDL"); return (v && v[0] == '0') ? 0 : 1; }();
+    if (use_pdl) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(static_cast<unsigned>(grid));
+        cfg.blockDim = dim3(CONV_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, conv_tcgen05_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p) == cudaSuccess) {
+            count_launch();
+            return FVM_OK;
+        }
+        (void)cudaGetLastError();   // not accepted here (e.g. by an older driver during capture): plain launches from now on
+        use_pdl = 0;
     }
     conv_tcgen05_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
     count_launch();

@@ -61,9 +61,14 @@ class FusedConv(nn.Module):
         if not AUTOTUNE or torch.cuda.is_current_stream_capturing():
             return 0
         K = self.w.shape[0]
-        cands = [0] + [c for c in (64, 128, 256) if c < K or (c == 256 and K > 256)]
+        # tile code: low 16 bits = output-channel tile (0 = library's choice), bits 16.. = 128-pixel sub-tiles per tile
+        widths = [0] + [c for c in (64, 128, 256) if c < K or (c == 256 and K > 256)]
         if K <= 64 or self.w.shape[1] == 8:
-            cands = [0]    # one tile anyway / 8-channel stems keep the library's tap-packed path (it needs all of K in one tile)
+            widths = [0]   # one tile anyway / 8-channel stems keep the library's tap-packed path (all of K in one tile)
+        cands = list(widths)
+        rows = x.shape[0] * out.shape[2] * out.shape[3]
+        if rows >= 148 * 8 * 128 and self.w.shape[2] * self.w.shape[3] * ((self.w.shape[1] + 63) // 64) <= 9:
+            cands += [c | (2 << 16) for c in widths if (c or K) <= 128]   # short reductions on large maps: 256-pixel tiles
         best, best_ms = 0, float("inf")
         if len(cands) > 1:
             for c in cands:
