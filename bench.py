@@ -35,6 +35,9 @@ CPU_BATCH = 8
 # inputs once and writes its output once; weights once per forward of 64 images): 59.52 MB and 8.178 GFLOP per image.
 ALGO_BYTES_PER_IMAGE = {"resnet50": 59.52e6}
 ALGO_FLOPS_PER_IMAGE = {"resnet50": 8.178e9}
+# DRAM traffic of one 64-image forward from an ncu capture of the replayed graph (dram__bytes_read.sum +
+# dram__bytes_write.sum summed over its 59 launches; profiles/resnet50_b64_forward_launches.md).
+NCU_TRAFFIC_PER_STEP = {("resnet50", 64): 2481.8e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -240,7 +243,8 @@ def main():
         algo_flops = ALGO_FLOPS_PER_IMAGE.get(MODEL, 0.0) * BATCH
         achieved = algo_bytes / (ms_step / 1e3) / 1e9 if algo_bytes else None
         roof = {"bound": "hbm", "achieved": round(achieved, 1) if achieved else None, "peak": pk["hbm_gbs"],
-                "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4) if achieved else None, "traffic": None,
+                "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4) if achieved else None,
+                "traffic": NCU_TRAFFIC_PER_STEP.get((MODEL, BATCH)),
                 "peak_source": pk["source"],
                 "kernel": "whole forward graph; conv_tcgen05_kernel is the dominant kernel (see profiles/)",
                 "algorithmic_bytes_per_step": algo_bytes, "algorithmic_flops_per_step": algo_flops,
