@@ -119,10 +119,11 @@ def reference_arm(args, rank):
     warmup = max(1, min(args.warmup, 3))
     ips, cores, sec = cpu_upstream(steps, warmup)
     sample = f"{MODEL} fp32 eager, batch {CPU_BATCH} of 3x224x224, median of {steps} forwards after {warmup} warm-ups"
-    line = {"impl": "reference", "metric": "ResNet-50 inference images/s", "value": round(ips, 2), "unit": "images/s",
+    line = {"impl": "reference", "metric": "ResNet-50 fp16 b64 images/s", "value": round(ips, 2), "unit": "images/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": round(sec * 1e3, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{MODEL} upstream fp32 on host cores, batch {CPU_BATCH}, 224x224"},
+            "config": {"workload": f"{MODEL} batch {BATCH} per GPU, 3x224x224 fp32 NCHW in, logits out",
+                       "reference_arm": f"upstream fp32 tier on the host cores, bounded sample: batch {CPU_BATCH} per step"},
             "cpu_baseline": {"value": round(ips, 2), "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": round(ips, 2), "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}

@@ -156,6 +156,22 @@ dwconv_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const 
 }
 
 
+template <int S, int SW, int ACT>
+static int launch_dw_tile_act(const __half* xp, const __half* wp, const __half* bp, __half* yp, float* pool_sums, int N,
+                              int H, int W, int C, int R, int P, int Q, int sh, int ph, int pw, long long ldx,
+                              long long ldy, int act, cudaStream_t st);
+template <int S, int SW>
+static int launch_dw_tile(const __half* xp, const __half* wp, const __half* bp, __half* yp, float* pool_sums, int N, int H,
+                          int W, int C, int R, int P, int Q, int sh, int ph, int pw, long long ldx, long long ldy, int act,
+                          cudaStream_t st) {
+    switch (act) {
+        case 0: return launch_dw_tile_act<S, SW, 0>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+        case 1: return launch_dw_tile_act<S, SW, 1>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+        case 3: return launch_dw_tile_act<S, SW, 3>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+        default: return launch_dw_tile_act<S, SW, -1>(xp, wp, bp, yp, pool_sums, N, H, W, C, R, P, Q, sh, ph, pw, ldx, ldy, act, st);
+    }
+}
+
 // Fast path for square 3/5/7-tap kernels without dilation: S, the stride and the strip width are compile-time, so the
 // accumulators (TW x 8 fp32) and one kernel row of weights (S x 8 fp32) stay in registers; every input vector of a
 // kernel row is loaded and converted once and feeds up to ceil(S / stride) outputs. Loads are the only memory
@@ -287,7 +303,8 @@ dwconv_fast_kernel(const __half* __restrict__ x, const __half* __restrict__ w, c
 // tile of TH x TWB output pixels x 64 channels in shared memory with 16-byte async copies (out-of-image taps are
 // zero-filled by the copy), so every input byte is fetched from L2 about once instead of once per kernel row; each
 // thread then produces a strip of 8 output columns for 8 channels from shared memory, with one kernel row of weights
-// and the 64 fp32 accumulators in registers.
+// and the 64 fp32 accumulators in registers. Arithmetic: fp16x2 FMAs within a kernel row, fp32 across rows, as the
+// reference's dwconv2 does for the same kernel sizes; every other shape takes the fp32 paths below.
 static constexpr int DWT_CBV = 8;        // channel vectors (of 8 channels) per block
 static constexpr int DWT_TW = 8;         // output columns per thread
 static constexpr int DWT_STRIPS = DW_THREADS / DWT_CBV;   // 16 strips per block
@@ -297,7 +314,8 @@ __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
 
-template <int S, int SW>
+// ACT: activation known at compile time (0 none, 1 relu, 3 silu) or -1 = use the run-time code.
+template <int S, int SW, int ACT>
 __global__ void __launch_bounds__(DW_THREADS)
 dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, const __half* __restrict__ bias,
                    __half* __restrict__ y, float* __restrict__ pool_sums, int H, int W, int C, int R, int P, int Q,
@@ -347,8 +365,7 @@ dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, c
     const int p = p0 + sy, qs = q0 + sx * DWT_TW;
     const bool active = v < cv && p < P && qs < Q;
     if (active) {
-        // accumulators, weights and inputs as fp32 pairs: one packed FMA does two channels (same arithmetic as scalar
-        // fp32 FMAs, half the instructions)
+        // fp32 accumulators as packed pairs
         unsigned long long acc[DWT_TW][4];
         {
             unsigned long long b2[4] = {0ull, 0ull, 0ull, 0ull};
@@ -361,31 +378,43 @@ dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, c
 #pragma unroll
                 for (int k = 0; k < 4; ++k) acc[j][k] = b2[k];
         }
+        // Arithmetic of the reference's dwconv2 (classification/fast/csrc/r3.cu:354-415, its default mode): within one
+        // kernel row the taps are accumulated with fp16x2 FMAs starting from zero, the row sums are added in fp32.
+        // No fp16->fp32 conversion of inputs or weights is needed, which is what made the fp32 version issue-bound.
         constexpr int L = (DWT_TW - 1) * SW + S;
         for (int r = 0; r < R; ++r) {
             const __half* wrow = w + static_cast<long long>(r) * S * C + v * 8;
-            unsigned long long wf[S][4];
+            uint4 wr[S];
 #pragma unroll
-            for (int s2 = 0; s2 < S; ++s2) {
-                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow + static_cast<long long>(s2) * C));
-                wf[s2][0] = h2_to_f2(wv.x); wf[s2][1] = h2_to_f2(wv.y); wf[s2][2] = h2_to_f2(wv.z); wf[s2][3] = h2_to_f2(wv.w);
-            }
+            for (int s2 = 0; s2 < S; ++s2)
+                wr[s2] = __ldg(reinterpret_cast<const uint4*>(wrow + static_cast<long long>(s2) * C));
+            __half2 racc[DWT_TW][4];
+#pragma unroll
+            for (int j = 0; j < DWT_TW; ++j)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) racc[j][k] = __float2half2_rn(0.f);
             // row (sy*sh + r) of the tile, columns sx*8*SW .. + L
             const uint32_t row_addr =
                 smem0 + (static_cast<uint32_t>((sy * sh + r) * tile_w + sx * DWT_TW * SW) * DWT_CBV + vv) * 16u;
 #pragma unroll
             for (int l = 0; l < L; ++l) {
                 const uint4 xv = lds128(row_addr + static_cast<uint32_t>(l * DWT_CBV) * 16u);
-                const unsigned long long xf[4] = {h2_to_f2(xv.x), h2_to_f2(xv.y), h2_to_f2(xv.z), h2_to_f2(xv.w)};
+                const __half2* hx = reinterpret_cast<const __half2*>(&xv);
 #pragma unroll
                 for (int j = 0; j < DWT_TW; ++j) {
                     const int s2 = l - j * SW;          // compile-time after unrolling
                     if (s2 >= 0 && s2 < S) {
+                        const __half2* hw = reinterpret_cast<const __half2*>(&wr[s2]);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) acc[j][k] = f2_fma(xf[k], wf[s2][k], acc[j][k]);
+                        for (int k = 0; k < 4; ++k) racc[j][k] = __hfma2(hx[k], hw[k], racc[j][k]);
                     }
                 }
             }
+#pragma unroll
+            for (int j = 0; j < DWT_TW; ++j)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    acc[j][k] = f2_add(acc[j][k], h2_to_f2(*reinterpret_cast<const uint32_t*>(&racc[j][k])));
         }
         float psum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
@@ -395,9 +424,17 @@ dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, c
                 __align__(16) __half2 o[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    float lo, hi;
-                    f2_unpack(acc[j][k], lo, hi);
-                    o[k] = __floats2half2_rn(act_f(lo, act), act_f(hi, act));
+                    // the sum is rounded to fp16 first; relu acts on the fp16 pair, other activations are evaluated
+                    // in fp32 on the rounded value and rounded again (reference: r3.cu:404-413)
+                    const uint32_t hv = f2_to_h2(acc[j][k]);
+                    o[k] = *reinterpret_cast<const __half2*>(&hv);
+                    if (ACT == 1) {
+                        o[k] = __hmax2(o[k], __float2half2_rn(0.f));
+                    } else if (ACT != 0) {
+                        const float2 f = __half22float2(o[k]);
+                        if (ACT == 3) o[k] = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+                        else o[k] = __floats2half2_rn(act_f(f.x, act), act_f(f.y, act));
+                    }
                     if (pool_sums) {
                         const float2 f = __half22float2(o[k]);
                         psum[2 * k] += f.x;
@@ -422,8 +459,8 @@ dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, c
     }
 }
 
-template <int S, int SW>
-static int launch_dw_tile(const __half* xp, const __half* wp, const __half* bp, __half* yp, float* pool_sums, int N, int H,
+template <int S, int SW, int ACT>
+static int launch_dw_tile_act(const __half* xp, const __half* wp, const __half* bp, __half* yp, float* pool_sums, int N, int H,
                           int W, int C, int R, int P, int Q, int sh, int ph, int pw, long long ldx, long long ldy, int act,
                           cudaStream_t st) {
     const int cv = C >> 3;
@@ -434,7 +471,7 @@ static int launch_dw_tile(const __half* xp, const __half* wp, const __half* bp, 
     if (smem > 200 * 1024) return -1;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(dwconv_tile_kernel<S, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        if (cudaFuncSetAttribute(dwconv_tile_kernel<S, SW, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
             cudaSuccess)
             return FVM_ERR_SETUP;
         attr_set = true;
@@ -443,7 +480,7 @@ static int launch_dw_tile(const __half* xp, const __half* wp, const __half* bp, 
     const long long bx = static_cast<long long>(tiles_x) * tiles_y * vblocks;
     if (bx > 0x7fffffffll) return FVM_ERR_ARG;
     dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(N));
-    dwconv_tile_kernel<S, SW><<<grid, DW_THREADS, smem, st>>>(xp, wp, bp, yp, pool_sums, H, W, C, R, P, Q, sh, ph, pw, ldx,
+    dwconv_tile_kernel<S, SW, ACT><<<grid, DW_THREADS, smem, st>>>(xp, wp, bp, yp, pool_sums, H, W, C, R, P, Q, sh, ph, pw, ldx,
                                                               ldy, act, strips_x, tiles_x, tiles_y);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;

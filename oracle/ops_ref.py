@@ -45,8 +45,47 @@ def conv_fused_ref(x, w, bias=None, res=None, padding=(0, 0), stride=(1, 1), act
     return act_ref(v, act).half()
 
 
+def _pair(v):
+    return (v, v) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+
+def dwconv2_ref(x, w_rsc, bias, stride, padding, act):
+    """dwconv2_k MODE 2 (the reference's default for 3x3 / 5x5 / 7x7, classification/fast/csrc/r3.cu:354-415):
+    af = float(bias); per kernel row: acc = 0 in fp16, acc = fma_fp16(x, w, acc) over the row's taps in order, then
+    af += float(acc); v = half(af); relu / relu6 on the fp16 value, other activations in fp32 on float(v), rounded again.
+    The fp16 FMA is emulated as half(float(x) * float(w) + float(acc)): the product is exact in fp32."""
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    N, C, H, W = x.shape
+    R, S, _ = w_rsc.shape
+    P = (H + 2 * ph - R) // sh + 1
+    Q = (W + 2 * pw - S) // sw + 1
+    xp = F.pad(x.float(), (pw, pw, ph, ph))        # out-of-image taps: x = 0, fma(0, w, acc) = acc (the kernel skips them)
+    wf = w_rsc.float()
+    af = torch.zeros((N, C, P, Q)) if bias is None else bias.float().view(1, C, 1, 1).expand(N, C, P, Q).clone()
+    for r in range(R):
+        acc = torch.zeros((N, C, P, Q))
+        for s in range(S):
+            xs = xp[:, :, r:r + (P - 1) * sh + 1:sh, s:s + (Q - 1) * sw + 1:sw]
+            acc = (xs * wf[r, s].view(1, C, 1, 1) + acc).half().float()
+        af = af + acc
+    v = af.half()
+    if act == 0:
+        return v
+    if act in (1, 2):
+        return act_ref(v.float(), act).half()
+    return act_ref(v.float(), act).half()
+
+
 def dwconv_ref(x, w_rsc, bias=None, stride=(1, 1), padding=(0, 0), act=0, dilation=(1, 1)):
-    """dwconv_tw, fused_conv.cu:428-475: acc = float(bias); acc += float(x)*float(w) over in-image taps; half(act(acc))."""
+    """Square 3/5/7-tap kernels without dilation follow dwconv2 (see dwconv2_ref), which is what the reference runs for
+    them (r3.cu:443-447); every other shape follows dwconv_tw, fused_conv.cu:428-475: acc = float(bias);
+    acc += float(x)*float(w) over in-image taps; half(act(acc))."""
+    R, S = w_rsc.shape[0], w_rsc.shape[1]
+    sh, sw = _pair(stride)
+    if R == S and R in (3, 5, 7) and _pair(dilation) == (1, 1) and sh == sw and sh in (1, 2) \
+            and (x.shape[3] + 2 * _pair(padding)[1] - S) // sw + 1 >= 4:
+        return dwconv2_ref(x, w_rsc, bias, stride, padding, act)
     C = x.shape[1]
     w = w_rsc.float().permute(2, 0, 1).unsqueeze(1)     # [C,1,R,S]
     v = F.conv2d(x.float(), w, None if bias is None else bias.float(), stride, padding, dilation, groups=C)
