@@ -70,8 +70,8 @@ extern "C" int fvm_last_status(int* code) {
 extern "C" int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* res, const float* scale,
                               void* y, int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw,
                               int dh, int dw, long long ldx, long long ldy, long long ldr, int act, void* stream) {
-    return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act, 0,
-                         static_cast<cudaStream_t>(stream));
+    return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act, 0, -1,
+                         -1, static_cast<cudaStream_t>(stream));
 }
 
 // Same as fvm_conv2d_f16 with the tile shape forced: tile_n low 16 bits = output-channel tile (multiple of 32, <= 256;
@@ -82,5 +82,15 @@ extern "C" int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bia
                                    int sw, int dh, int dw, long long ldx, long long ldy, long long ldr, int act,
                                    int tile_n, void* stream) {
     return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act,
-                         tile_n, static_cast<cudaStream_t>(stream));
+                         tile_n, -1, -1, static_cast<cudaStream_t>(stream));
+}
+
+// fvm_conv2d_f16_tile with separate bottom / right padding (ph_hi, pw_hi; negative = same as top / left): used by the
+// host when it re-expresses a stride-2 RGB stem over column pairs (16 channels per tap), where the two sides differ.
+extern "C" int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias, const void* res, const float* scale,
+                                  void* y, int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh,
+                                  int sw, int dh, int dw, long long ldx, long long ldy, long long ldr, int act,
+                                  int tile_n, int ph_hi, int pw_hi, void* stream) {
+    return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act,
+                         tile_n, ph_hi, pw_hi, static_cast<cudaStream_t>(stream));
 }

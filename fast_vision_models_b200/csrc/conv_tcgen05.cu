@@ -43,8 +43,7 @@ static constexpr int MAX_STAGES = 8;
 static constexpr int MAX_EPI = 6;     // staging buffers for residual-in / output-out tiles
 static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI + 1;   // stages, accumulators, staging, resident B
 static constexpr int MISC_BYTES = 16 + (NUM_BARRIERS & 1) * 8;   // tmem slot, abort flag; keeps what follows 16-byte aligned
-static constexpr int TAPS_PER_KBLOCK = 8;                    // tap-packed mode: 8 taps x 8 channels = 64 K elements
-static constexpr uint32_t TAP_A_BYTES = BM * 16;             // one tap of one A tile: 128 pixels x 8 channels
+static constexpr int TAPS_PER_KBLOCK = 8;                    // tap-packed mode, 8-channel taps: 8 taps x 8 channels = 64 K elements
 static constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 static constexpr uint32_t SUB_BYTES = BM * 64 * 2;       // one 128-row x 64-channel staging sub-tile, 16 KB
 
@@ -64,7 +63,8 @@ struct ConvParams {
     int nsub;      // 64-channel staging sub-tiles per 128-row sub-tile = ceil(BN / 64)
     int nepi;      // staging buffers (1..6)
     int im2col;    // 0: A via 2-D tiled map over [M, C]; 1: A via im2col map over [N, H, W, C]
-    int tapk;      // 1: C == 8 "tap-packed" mode: a k-block is 8 filter taps x 8 channels, weights resident in smem
+    int tapk;      // 8 or 16: "tap-packed" mode for inputs of 8 / 16 channels: a k-block is 8 / 4 filter taps of that
+                   // many channels (64 K elements), weights resident in smem; 0: one tap of 64 channels per k-block
     int taps;      // R * S
     int bres;      // 1: the weights of this CTA's n-tile stay resident in shared memory (loaded once); each CTA keeps one
                    // n-tile and walks the m-tiles; pipeline stages then hold A only
@@ -226,11 +226,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t b_stage_bytes = (p.tapk || p.bres) ? 0u : b_kb_bytes;
     const uint32_t a_stage_bytes = static_cast<uint32_t>(p.mt) * A_STAGE_BYTES;
     const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
-    const uint32_t tap_a_bytes = static_cast<uint32_t>(p.mt) * TAP_A_BYTES;   // one tap of all sub-tiles of a stage
+    const int tpk = p.tapk ? BK / p.tapk : 0;                                  // taps per k-block (8 or 4)
+    const uint32_t tap_sub_bytes = static_cast<uint32_t>(BM * p.tapk * 2);    // one tap of one 128-pixel sub-tile
+    const uint32_t tap_a_bytes = static_cast<uint32_t>(p.mt) * tap_sub_bytes;  // one tap of all sub-tiles of a stage
     // tap-packed mode: all weights of the (single) n-tile stay resident: one [BN x 16 B] block per tap
-    const uint32_t tap_b_bytes = static_cast<uint32_t>(p.BN) * 16u;
+    const uint32_t tap_b_bytes = static_cast<uint32_t>(p.BN * p.tapk * 2);
     const uint32_t bres_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
-    const uint32_t bres_bytes = p.tapk ? static_cast<uint32_t>(p.kblocks * TAPS_PER_KBLOCK) * tap_b_bytes
+    const uint32_t bres_bytes = p.tapk ? static_cast<uint32_t>(p.kblocks * tpk) * tap_b_bytes
                                        : (p.bres ? static_cast<uint32_t>(p.kblocks) * b_kb_bytes : 0u);
     const uint32_t epi_base = bres_base + bres_bytes;
     const uint32_t epi_bytes = static_cast<uint32_t>(p.mt * p.nsub) * SUB_BYTES;   // staging: [mt][nsub] sub-tiles
@@ -306,7 +308,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 // weights of every tap (taps past R*S are out of bounds of the weight tensor: zero-filled)
                 if (lane == 0) mbar_expect_tx(bres_full_bar, bres_bytes);
                 __syncwarp();
-                for (int t = lane; t < p.kblocks * TAPS_PER_KBLOCK; t += 32)
+                for (int t = lane; t < p.kblocks * tpk; t += 32)
                     tma_load_3d(bres_base + static_cast<uint32_t>(t) * tap_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
             }
             int m_tile, n_tile;
@@ -367,9 +369,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (p.tapk) {
                         // 8 taps of 8 channels: each lands as a dense [128*mt pixels][16 B] block (8-row x 16-byte core
                         // matrices back to back). Taps past the filter re-read the last tap; their weights are zero.
-                        if (lane < TAPS_PER_KBLOCK) {
+                        if (lane < tpk) {
                             const int j = lane;
-                            const int t = min(kb * TAPS_PER_KBLOCK + j, p.taps - 1);
+                            const int t = min(kb * tpk + j, p.taps - 1);
                             const int tr = t / p.S, ts = t - tr * p.S;
                             tma_load_im2col_4d(a_dst + static_cast<uint32_t>(j) * tap_a_bytes, &tmap_a, full_bar(stage), 0,
                                                w0, h0, img, static_cast<uint16_t>(ts * p.dw),
@@ -441,6 +443,23 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tc_fence_after();
                     if (kb == 0) TRACE(1, it, 1);
                     const uint32_t a_src = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
+                    if (p.tapk == 16) {
+                        // one MMA (K = 16) per tap: rows of 32 bytes in the 32-byte-swizzled layout
+                        for (int mt = 0; mt < p.mt; ++mt) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint64_t a_desc = umma_desc_sw32(a_src + static_cast<uint32_t>(k) * tap_a_bytes +
+                                                                       static_cast<uint32_t>(mt) * tap_sub_bytes);
+                                const uint64_t b_desc =
+                                    umma_desc_sw32(bres_base + static_cast<uint32_t>(kb * 4 + k) * tap_b_bytes);
+                                umma_f16(d_tmem + static_cast<uint32_t>(mt * p.BN), a_desc, b_desc, idesc,
+                                         (kb | k) != 0 ? 1u : 0u);
+                            }
+                        }
+                        umma_commit(empty_bar(stage));
+                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     if (p.tapk) {
                         // K = 16 spans two taps: the two 16-byte K halves are one tap block apart (LBO); 8-row groups
                         // are 128 bytes apart (SBO); no swizzle
@@ -448,7 +467,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                             for (int k = 0; k < TAPS_PER_KBLOCK / 2; ++k) {
                                 const uint64_t a_desc = umma_desc_interleaved(
-                                    a_src + static_cast<uint32_t>(2 * k) * tap_a_bytes + static_cast<uint32_t>(mt) * TAP_A_BYTES,
+                                    a_src + static_cast<uint32_t>(2 * k) * tap_a_bytes + static_cast<uint32_t>(mt) * tap_sub_bytes,
                                     tap_a_bytes, 128u);
                                 const uint64_t b_desc = umma_desc_interleaved(
                                     bres_base + static_cast<uint32_t>(kb * TAPS_PER_KBLOCK + 2 * k) * tap_b_bytes, tap_b_bytes,
@@ -653,7 +672,7 @@ static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, 
     const int n_tiles = (K + BN - 1) / BN;
     const uint32_t stage_bytes =
         static_cast<uint32_t>(MT) * A_STAGE_BYTES + ((tapk || bres) ? 0u : static_cast<uint32_t>(BN) * BK * 2);
-    const uint32_t bres_bytes = tapk ? static_cast<uint32_t>(kblocks * TAPS_PER_KBLOCK) * BN * 16u
+    const uint32_t bres_bytes = tapk ? static_cast<uint32_t>(kblocks) * BN * BK * 2   // 8 x 16 B or 4 x 32 B per row
                                      : (bres ? static_cast<uint32_t>(kblocks) * BN * BK * 2 : 0u);
     const uint32_t epi_bytes = static_cast<uint32_t>(MT * ((BN + 63) / 64)) * SUB_BYTES;
     const uint32_t bias_bytes = (static_cast<uint32_t>(n_tiles * BN) * 4 + 15u) & ~15u;   // fp32 copy of the bias
@@ -740,7 +759,11 @@ static int pick_mt(int BN, int m_tiles128, int n_tiles, int kblocks, int K, bool
 
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
-                  long long ldx, long long ldy, long long ldr, int act, int force_bn, cudaStream_t stream) {
+                  long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
+                  cudaStream_t stream) {
+    // ph / pw pad the top / left; ph_hi / pw_hi the bottom / right (negative: same as top / left)
+    if (ph_hi < 0) ph_hi = ph;
+    if (pw_hi < 0) pw_hi = pw;
     DeviceState* st = device_state();
     if (!st) return FVM_ERR_SETUP;
     if (!x || !w || !y) return FVM_ERR_ARG;
@@ -758,8 +781,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         (reinterpret_cast<uintptr_t>(bias) & 15))
         return FVM_ERR_ARG;
     if (act < 0 || act > 6) return FVM_ERR_ARG;
-    const int P = (H + 2 * ph - dh * (R - 1) - 1) / sh + 1;
-    const int Q = (W + 2 * pw - dw * (S - 1) - 1) / sw + 1;
+    const int P = (H + ph + ph_hi - dh * (R - 1) - 1) / sh + 1;
+    const int Q = (W + pw + pw_hi - dw * (S - 1) - 1) / sw + 1;
     if (P <= 0 || Q <= 0) return FVM_ERR_ARG;
     const long long M_ll = static_cast<long long>(N) * P * Q;
     if (M_ll > 0x7fffff00ll) return FVM_ERR_ARG;
@@ -778,10 +801,11 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     {
         const int Kp16 = (K + 31) / 32 * 32;   // tiles are multiples of 32 channels
         SmemPlan tp;
-        p.tapk = (C == 8 && R * S > 1 && Kp16 <= 256 && (force_bn <= 0 || force_bn >= Kp16) &&
-                  plan_smem(Kp16, 1, (R * S + TAPS_PER_KBLOCK - 1) / TAPS_PER_KBLOCK, K, true, false, &tp)) ? 1 : 0;
+        const int tpk = (C == 8 || C == 16) ? BK / C : 1;      // taps per k-block in tap-packed mode
+        p.tapk = ((C == 8 || C == 16) && R * S > 1 && Kp16 <= 256 && (force_bn <= 0 || force_bn >= Kp16) &&
+                  plan_smem(Kp16, 1, (R * S + tpk - 1) / tpk, K, true, false, &tp)) ? C : 0;
         if (p.tapk) {
-            p.kblocks = (R * S + TAPS_PER_KBLOCK - 1) / TAPS_PER_KBLOCK;
+            p.kblocks = (R * S + tpk - 1) / tpk;
             force_bn = Kp16;
         }
     }
@@ -790,7 +814,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.n_tiles = (K + p.BN - 1) / p.BN;
     p.div_ntiles = fastdiv_init(static_cast<uint32_t>(p.n_tiles));
     if (p.n_tiles > 1 && (p.BN & 63)) return FVM_ERR_ARG;   // split K only in whole 64-channel store boxes
-    p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0);
+    p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && ph_hi == 0 && pw_hi == 0);
     p.act = act;
     p.has_res = res != nullptr;
     p.bias = static_cast<const __half*>(bias);
@@ -862,11 +886,12 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         // weights [K][R*S][C]
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(R * S), static_cast<cuuint64_t>(K)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 2, static_cast<cuuint64_t>(R) * S * C * 2};
-        cuuint32_t box[3] = {static_cast<cuuint32_t>(p.tapk ? 8 : BK), 1, static_cast<cuuint32_t>(p.BN)};
+        cuuint32_t box[3] = {static_cast<cuuint32_t>(p.tapk ? p.tapk : BK), 1, static_cast<cuuint32_t>(p.BN)};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = g_encode_tiled(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(w), dims, strides,
                                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    p.tapk ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                                    p.tapk == 8 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                                : (p.tapk == 16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B),
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
     }
@@ -882,8 +907,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     } else {
         // NHWC activation as (C, W, H, N); the filter-window origin moves inside the box
         // [-pad, size + pad - dilation*(taps-1) - 1], stepping by the conv stride; each load adds the tap offset.
-        const int up_w = pw - (S - 1) * dw, up_h = ph - (R - 1) * dh;
-        if (pw > 128 || ph > 128 || up_w < -128 || up_h < -128 || (S - 1) * dw > 255 || (R - 1) * dh > 255)
+        const int up_w = pw_hi - (S - 1) * dw, up_h = ph_hi - (R - 1) * dh;
+        if (pw > 128 || ph > 128 || pw_hi > 127 || ph_hi > 127 || up_w < -128 || up_h < -128 || (S - 1) * dw > 255 || (R - 1) * dh > 255)
             return FVM_ERR_ARG;
         cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H),
                               static_cast<cuuint64_t>(N)};
@@ -893,9 +918,10 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         int upper[2] = {up_w, up_h};
         cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
         CUresult r = g_encode_im2col(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(x), dims, strides,
-                                     lower, upper, p.tapk ? 8 : BK, static_cast<cuuint32_t>(BM * p.mt), estr,
+                                     lower, upper, p.tapk ? p.tapk : BK, static_cast<cuuint32_t>(BM * p.mt), estr,
                                      CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                     p.tapk ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                                     p.tapk == 8 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                                 : (p.tapk == 16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B),
                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;

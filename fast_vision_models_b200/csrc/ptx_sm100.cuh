@@ -263,6 +263,17 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                           // layout type: SWIZZLE_128B
     return d;
 }
+// K-major operand tile whose rows are 32 bytes (16 halves = one MMA K step) wide, written by TMA with the 32-byte
+// swizzle: 8-row groups are 256 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw32(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(256 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(6) << 61;                           // layout type: SWIZZLE_32B
+    return d;
+}
 // K-major tile without swizzle ("interleaved"): core matrices of 8 rows x 16 bytes stored contiguously (128 bytes);
 // `sbo` = byte distance between 8-row groups, `lbo` = byte distance between the two 16-byte K halves of one MMA.
 __device__ __forceinline__ uint64_t umma_desc_interleaved(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {

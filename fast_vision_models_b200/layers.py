@@ -13,7 +13,8 @@ from torch import nn
 
 from . import fold, ops
 
-AUTOTUNE = os.environ.get("FVM_B200_AUTOTUNE", "1") != "0"   # kill switch, in the style of the reference's CLF_* variables
+AUTOTUNE = os.environ.get("FVM_B200_AUTOTUNE", "1") != "0"
+PAIR_STEMS = os.environ.get("FVM_B200_PAIR_STEMS", "1") != "0"   # run RGB stems over column pairs (16-channel taps)   # kill switch, in the style of the reference's CLF_* variables
 
 _ACT_CODES = {
     nn.ReLU: ops.ACT_RELU, nn.ReLU6: ops.ACT_RELU6, nn.SiLU: ops.ACT_SILU, nn.Hardswish: ops.ACT_HARDSWISH,
@@ -48,6 +49,30 @@ class FusedConv(nn.Module):
         self.register_buffer("scale", None if scale is None else scale.float().contiguous())
         self.stride, self.padding, self.dilation, self.act = tuple(stride), tuple(padding), tuple(dilation), int(act)
         self._tiles = {}      # (input shape, has residual) -> output-channel tile chosen by timing
+        self.register_buffer("w_pair", None)
+        self._pair = None
+        if PAIR_STEMS and self.w.shape[1] == 8 and self.stride[1] % 2 == 0 and self.dilation == (1, 1) \
+                and self.w.shape[2] * self.w.shape[3] > 1:
+            self._make_column_pairs(w)
+
+    def _make_column_pairs(self, w: torch.Tensor) -> None:
+        """An 8-channel (zero-padded RGB) stem with an even horizontal stride, re-expressed over pairs of input columns:
+        the NHWC8 input [N,H,W,8] is the same memory as [N,H,W/2,16], a tap then covers two columns x 8 channels, the
+        stride halves and the kernel has about half as many (twice as wide) taps. Same products, same sums (the added
+        weights are zero); the TMA unit gathers half as many rows."""
+        K, C, R, S = w.shape              # C == 8 after padding
+        pw, sw = self.padding[1], self.stride[1]
+        odd = pw % 2
+        lo2 = (pw + 1) // 2
+        S2 = (S - 1 - pw) // 2 + lo2 + 1
+        w2 = torch.zeros((K, 16, R, S2), dtype=w.dtype)
+        for p2 in range(S2):
+            for dx in range(2):
+                s = 2 * p2 + dx - odd
+                if 0 <= s < S:
+                    w2[:, dx * 8:(dx + 1) * 8, :, p2] = w[:, :, :, s]
+        self.w_pair = fold.to_krsc_half(w2)
+        self._pair = (S2, lo2, sw // 2)
 
     def _tile_for(self, x: torch.Tensor, res, out: torch.Tensor, act: int) -> int:
         """Output-channel tile for this layer at this input shape. The library's own rule picks from wave efficiency
@@ -117,6 +142,16 @@ class FusedConv(nn.Module):
             P = (H + 2 * self.padding[0] - self.dilation[0] * (R - 1) - 1) // self.stride[0] + 1
             Q = (W + 2 * self.padding[1] - self.dilation[1] * (S - 1) - 1) // self.stride[1] + 1
             out = ops.empty_nhwc(N, K, P, Q, x.device)
+        if self._pair is not None and x.shape[3] % 2 == 0 and x.is_contiguous(memory_format=torch.channels_last):
+            S2, lo2, sw2 = self._pair
+            N, _, H, W = x.shape
+            Q = out.shape[3]
+            hi2 = (Q - 1) * sw2 + S2 - W // 2 - lo2
+            if hi2 >= 0:
+                x2 = x.permute(0, 2, 3, 1).reshape(N, H, W // 2, 16).permute(0, 3, 1, 2)    # a view: no copy
+                ops.conv_fused_into(x2, self.w_pair, self.b, res, (self.padding[0], lo2), (self.stride[0], sw2), a, out,
+                                    scale=self.scale, pad_hi=(self.padding[0], hi2))
+                return out
         tile = self._tile_for(x, res, out, a)
         ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, a, out, dilation=self.dilation,
                             scale=self.scale, tile_n=tile)

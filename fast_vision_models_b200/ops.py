@@ -127,8 +127,9 @@ def _krsc(w: torch.Tensor) -> torch.Tensor:
 
 
 def conv_fused_into(x, w, bias, res, padding, stride, act: int, out: torch.Tensor, dilation=(1, 1),
-                    scale: Optional[torch.Tensor] = None, tile_n: int = 0) -> None:
-    """clf::conv_fused_into / segx::conv_fused_into: y = act((conv(x,w)+bias)*scale + res) written into `out`."""
+                    scale: Optional[torch.Tensor] = None, tile_n: int = 0, pad_hi=None) -> None:
+    """clf::conv_fused_into / segx::conv_fused_into: y = act((conv(x,w)+bias)*scale + res) written into `out`.
+    `pad_hi` = (bottom, right) padding when it differs from `padding` = (top, left)."""
     init(x.device)
     x, N, C, H, W, ldx = nhwc_view(x, "x")
     w = _krsc(w)
@@ -138,8 +139,9 @@ def conv_fused_into(x, w, bias, res, padding, stride, act: int, out: torch.Tenso
     ph, pw = _pair(padding)
     sh, sw = _pair(stride)
     dh, dw = _pair(dilation)
-    P = (H + 2 * ph - dh * (R - 1) - 1) // sh + 1
-    Q = (W + 2 * pw - dw * (S - 1) - 1) // sw + 1
+    ph_hi, pw_hi = (ph, pw) if pad_hi is None else _pair(pad_hi)
+    P = (H + ph + ph_hi - dh * (R - 1) - 1) // sh + 1
+    Q = (W + pw + pw_hi - dw * (S - 1) - 1) // sw + 1
     out_v, No, Ko, Po, Qo, ldy = nhwc_view(out, "out")
     if out_v is not out or (No, Ko, Po, Qo) != (N, K, P, Q):
         raise FvmError(f"conv_fused_into: out must be a channels-last [N,K,P,Q]={N, K, P, Q} tensor or channel slice, "
@@ -159,7 +161,9 @@ def conv_fused_into(x, w, bias, res, padding, stride, act: int, out: torch.Tenso
     L = lib()
     args = [x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(res), _ptr(scale), out.data_ptr(), N, H, W, C, K, R, S, ph, pw,
             sh, sw, dh, dw, ldx, ldy, ldr, int(act)]
-    if tile_n:
+    if pad_hi is not None:
+        rc = L.fvm_conv2d_f16_pad(*args, int(tile_n), ph_hi, pw_hi, _stream())
+    elif tile_n:
         rc = L.fvm_conv2d_f16_tile(*args, int(tile_n), _stream())
     else:
         rc = L.fvm_conv2d_f16(*args, _stream())

@@ -60,6 +60,22 @@ int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* r
                    int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                    long long ldx, long long ldy, long long ldr, int act, void* stream);
 
+/* fvm_conv2d_f16 with the tile shape forced -- the counterpart of the reference's `cfg` argument of clf::conv_fused
+ * (fused_conv.cu:180-227, a tile-configuration index). tile_n: low 16 bits = output-channel tile (multiple of 32, at
+ * most 256; 0 = choose), bits 16..23 = 128-pixel sub-tiles per tile (1, 2, 4; 0 = choose), bits 24..25 = keep the
+ * weight tile resident in shared memory (0 = choose, 1 = on, 2 = off). Shapes that do not fit return 1. */
+int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y,
+                        int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
+                        long long ldx, long long ldy, long long ldr, int act, int tile_n, void* stream);
+
+/* fvm_conv2d_f16_tile with separate bottom / right padding (ph_hi, pw_hi; negative = same as top / left). The host
+ * uses it to run a stride-2 RGB stem (reference: the zero-padded 8-channel stem, fused.py:90-105) over column pairs:
+ * the NHWC8 input viewed as [N, H, W/2, 16] with re-packed weights, which halves the rows the TMA unit gathers. */
+int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y,
+                       int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
+                       long long ldx, long long ldy, long long ldr, int act, int tile_n, int ph_hi, int pw_hi,
+                       void* stream);
+
 /* Depthwise RxS convolution -- replaces clf::dwconv (fused_conv.cu:418-502), clfr3::dwconv2 (r3.cu:335-454) and
  * segx::dwconv (segmentation/fast/csrc/seg_kernels.cu:124-158):
  *   y[n,p,q,c] = act( bias[c] + sum_{r,s} x[n, p*sh-ph+r*dh, q*sw-pw+s*dw, c] * w[r,s,c] ), fp32 accumulation.

@@ -127,6 +127,51 @@ def test_conv_weight_resident_mode_matches_streaming_mode(case):
     assert torch.equal(y_on, y_off)
 
 
+@pytest.mark.parametrize("case", [(2, 20, 22, 16, 64, 3, 3, 1, 1), (2, 17, 19, 16, 48, 7, 4, 3, 1), (3, 12, 12, 16, 96, 2, 2, 0, 2),
+                                  (1, 9, 40, 16, 256, 1, 5, 0, 1)])
+def test_conv_sixteen_channel_taps(case):
+    # 16-channel inputs take the tap-packed path with one MMA per filter tap (32-byte-swizzled rows)
+    N, H, W, C, K, Rr, S, pad, stride = case
+    x, w, b = gen((N, C, H, W), 1), gen((K, C, Rr, S), 2, 0.05), gen((K,), 3, 0.1)
+    ref = R.conv_fused_ref(x, w, b, None, (pad, pad), (stride, stride), 1)
+    y = ops.conv_fused(cl(x), cl(w), b.to(DEV), None, (pad, pad), (stride, stride), 1)
+    assert ops.last_status() == 0
+    close(y, ref)
+
+
+@pytest.mark.parametrize("C", [16, 64])
+def test_conv_separate_low_and_high_padding(C):
+    x, w, b = gen((2, C, 11, 14), 1), gen((64, C, 3, 4), 2, 0.05), gen((64,), 3, 0.1)
+    lo, hi = (1, 2), (0, 1)            # (top, left), (bottom, right)
+    xp = torch.nn.functional.pad(x.float(), (lo[1], hi[1], lo[0], hi[0])).half()
+    ref = R.conv_fused_ref(xp, w, b, None, (0, 0), (1, 1), 1)
+    out = ops.empty_nhwc(2, 64, ref.shape[2], ref.shape[3], DEV)
+    ops.conv_fused_into(cl(x), cl(w), b.to(DEV), None, lo, (1, 1), 1, out, pad_hi=hi)
+    assert ops.last_status() == 0
+    close(out, ref)
+
+
+@pytest.mark.parametrize("case", [(2, 64, 64, 64, 7, 2, 3), (2, 38, 46, 48, 3, 2, 1), (2, 32, 48, 96, 4, 4, 0)])
+def test_rgb_stem_over_column_pairs_matches_the_plain_stem(case):
+    # FusedConv re-expresses an even-stride RGB stem over pairs of input columns; both ways must agree with the oracle
+    from fast_vision_models_b200 import layers
+    N, H, W, K, k, stride, pad = case
+    conv = torch.nn.Conv2d(3, K, k, stride=stride, padding=pad, bias=True)
+    x32 = torch.randn(N, 3, H, W, generator=torch.Generator().manual_seed(5))
+    x8 = ops.input_nhwc8(x32.to(DEV))
+    fc = layers.FusedConv.from_conv_bn(conv, None, 1).to(DEV)
+    assert fc._pair is not None
+    y_pair = fc(x8)
+    fc._pair = None
+    y_plain = fc(x8)
+    w8 = torch.zeros(K, 8, k, k)
+    w8[:, :3] = conv.weight.detach()
+    ref = R.conv_fused_ref(R.input_nhwc8_ref(x32), w8.half(), conv.bias.detach().half(), None, (pad, pad), (stride, stride), 1)
+    assert ops.last_status() == 0
+    close(y_pair, ref)
+    close(y_plain, ref)
+
+
 def test_conv_no_bias_scale_and_sliced_io():
     # input read from a channel slice, output written into a channel slice of a wider buffer (concat-free ASPP),
     # un-folded LayerScale as an fp32 epilogue scale
