@@ -609,7 +609,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 mbar_arrive(epi_free_bar(e));
                 if (++e == p.nepi) e = 0;
             }
-            tma_store_wait_all();               // all output bytes are written before the CTA exits
+            // Shared memory must outlive the stores' reads of it; the writes themselves complete asynchronously and are
+            // visible to the next kernel through the usual kernel-boundary ordering.
+            tma_store_wait_read();
         }
     }
 

@@ -101,14 +101,16 @@ class FusedConv(nn.Module):
                     for _ in range(2):
                         ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
                                             dilation=self.dilation, scale=self.scale, tile_n=c)
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                    for _ in range(5):
-                        ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
-                                            dilation=self.dilation, scale=self.scale, tile_n=c)
-                    e1.record()
-                    e1.synchronize()
-                    ms = e0.elapsed_time(e1)
+                    ms = float("inf")
+                    for _rep in range(3):          # best of three short bursts: robust against a stray stall
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        for _ in range(6):
+                            ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
+                                                dilation=self.dilation, scale=self.scale, tile_n=c)
+                        e1.record()
+                        e1.synchronize()
+                        ms = min(ms, e0.elapsed_time(e1))
                 except ops.FvmError:
                     continue
                 if ms < best_ms * 0.97:      # a different tile must be clearly faster than the default
