@@ -107,7 +107,7 @@ __device__ __forceinline__ float2 unpack_h2(uint32_t u) {
 // Epilogue arithmetic for one 32-column chunk of one output row: accumulator + bias (* scale) (+ residual) ->
 // activation -> fp16, combined in place with the staged residual chunk. `stage_row` points at this row inside the
 // 64-channel staging sub-tile (128-byte swizzle: 16-byte chunk index XOR (row & 7)); `bias_s` at the chunk's bias.
-// ACT: 0 none, 1 relu, 2 = read p.act at run time. All loads are issued before the arithmetic.
+// ACT: 0 none, 1 relu, 3 silu, 5 gelu (erf), 2 = read p.act at run time. All loads are issued before the arithmetic.
 template <int ACT, bool RES>
 __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t taddr, uint32_t stage_row, uint32_t ch0,
                                                uint32_t row_xor, uint32_t bias_s, int n, int left) {
@@ -136,13 +136,27 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
             lds_2xf2(bias_s + 32u * j, bw[0], bw[1]);
             lds_2xf2(bias_s + 32u * j + 16u, bw[2], bw[3]);
             if (ACT != 2 && p.scale == nullptr) {
-                // fast path: packed fp32 adds, activation on the packed fp16 result (relu commutes with the rounding)
+                // fast path: packed fp32 adds; relu on the packed fp16 result (it commutes with the rounding); SiLU and
+                // GELU in fp32 with the activation known at compile time
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     unsigned long long t = f2_add(f2_pack(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]), bw[k]);
                     if (RES) t = f2_add(t, h2_to_f2(r4[k]));
-                    o[k] = f2_to_h2(t);
-                    if (ACT == 1) o[k] = h2_relu(o[k]);
+                    if (ACT == 3 || ACT == 5) {
+                        float lo, hi;
+                        f2_unpack(t, lo, hi);
+                        if (ACT == 3) {
+                            lo = __fdividef(lo, 1.f + __expf(-lo));
+                            hi = __fdividef(hi, 1.f + __expf(-hi));
+                        } else {
+                            lo = 0.5f * lo * (1.f + erff(lo * 0.70710678118654752f));
+                            hi = 0.5f * hi * (1.f + erff(hi * 0.70710678118654752f));
+                        }
+                        o[k] = pack_h2(lo, hi);
+                    } else {
+                        o[k] = f2_to_h2(t);
+                        if (ACT == 1) o[k] = h2_relu(o[k]);
+                    }
                 }
             } else {
                 float f[8];
@@ -551,7 +565,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                    static_cast<uint32_t>(acc * p.acc_stride);
             const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
             const int ncols = min(p.BN, p.K - n0);   // multiple of 8
-            const int variant = (p.act == 0 ? 0 : (p.act == 1 ? 1 : 2)) * 2 + (p.has_res ? 1 : 0);
+            // activation as a template argument for the common ones (0 none, 1 relu, 3 silu, 5 gelu-erf); 2 = read at run time
+            const int act_t = (p.act == 0 || p.act == 1 || p.act == 3 || p.act == 5) ? p.act : 2;
+            const int variant = act_t * 2 + (p.has_res ? 1 : 0);
             for (int mt = 0; mt < p.mt; ++mt) {
                 const uint32_t t_sub = t_row + static_cast<uint32_t>(mt * p.BN);
                 const uint32_t s_sub = stage_row0 + static_cast<uint32_t>(mt * p.nsub) * SUB_BYTES;
@@ -561,7 +577,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     case 2: epilogue_rows<1, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
                     case 3: epilogue_rows<1, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
                     case 4: epilogue_rows<2, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    default: epilogue_rows<2, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 5: epilogue_rows<2, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 6: epilogue_rows<3, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 7: epilogue_rows<3, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 10: epilogue_rows<5, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    default: epilogue_rows<5, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
                 }
             }
             TRACE(2 + group, it, 3);
