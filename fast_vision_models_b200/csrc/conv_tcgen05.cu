@@ -6,22 +6,20 @@
 // Arithmetic contract of the reference op this replaces: classification/fast/csrc/fused_conv.cu:81-99 (epilogue order
 // bias -> residual -> activation -> single fp16 rounding); the reference accumulates in fp16 (:50), this kernel in fp32.
 //
-// Roles: warp 0 = TMA producer (one elected lane), warp 1 = TMEM owner + MMA issuer (one elected lane),
-// warps 2..9 = two epilogue groups of 4 warps (TMEM lane group = warp % 4) that finish alternate tiles,
-// warp 10 = TMA store issuer (one lane).
+// Roles (19 warps): warp 0 = TMA producer (lane 0 arms the barriers, several lanes issue bulk loads), warp 1 = TMEM
+// owner + MMA issuer (one lane), warps 2..17 = four epilogue groups of 4 warps (TMEM lane group = warp % 4) that finish
+// alternate tiles, warp 18 = TMA store issuer (one lane).
 //   A tiles: 128 output pixels x 64 input channels per k-block. 1x1 stride-1 convs read them with a 2-D tiled tensor
 //            map over [M, C]; every other shape uses an im2col-mode tensor map over the NHWC activation, so padding,
 //            stride and dilation are resolved by the TMA unit and out-of-image taps arrive as zeros.
 //   B tiles: BN output channels x 64 input channels of one filter tap, 3-D tiled map over [K][R*S][C].
 //   Both land in shared memory in the 128-byte-swizzled K-major layout tcgen05.mma consumes directly.
-//   Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+//   Two to four accumulator buffers in TMEM let the epilogues of earlier tiles overlap the main loop of the next.
 //   The residual tile is prefetched by TMA into a swizzled staging buffer, combined in place with the accumulator,
 //   and the finished tile leaves by TMA store: the epilogue threads never touch global memory except for the bias.
 // No cluster launch and no multicast: every CTA issues its own loads.
 #include <cuda.h>
 
-#include <atomic>
-#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -761,24 +759,6 @@ static int pick_bn(int m_tiles, int K, int kblocks, bool tapk, int sms) {
     return best;
 }
 
-// Sub-tiles per tile. Layers with a short reduction spend their time in per-tile hand-offs between the single-thread
-// roles (barrier round trips, TMA and MMA issue), not in the tensor pipe: a tile of 256 or 512 output pixels amortises
-// them. Used when the accumulators still fit TMEM twice, the pipeline keeps 3 stages and every CTA still gets several
-// tiles.
-static int pick_mt(int BN, int m_tiles128, int n_tiles, int kblocks, int K, bool tapk, int sms) {
-    if (kblocks > 8) return 1;
-    for (int mt = 4; mt >= 2; mt >>= 1) {
-        if (mt * BN > 256) continue;
-        const long long tiles = static_cast<long long>((m_tiles128 + mt - 1) / mt) * n_tiles;
-        if (tiles < 4ll * sms) continue;
-        SmemPlan sp;
-        if (!plan_smem(BN, mt, kblocks, K, tapk, false, &sp)) continue;
-        if (sp.stages < 3 || sp.nepi < 2) continue;
-        return mt;
-    }
-    return 1;
-}
-
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
@@ -848,7 +828,6 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // Measured on B200: larger tiles did not pay for themselves on the layers tried (fewer, larger hand-offs but less
     // overlap between the roles), so the default stays at one sub-tile; the host's per-layer tuning may force more.
     p.mt = force_mt > 0 ? force_mt : 1;
-    (void)&pick_mt;
     if (p.mt != 1 && p.mt != 2 && p.mt != 4) return FVM_ERR_ARG;
     p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
     p.a_rows = BM * p.mt < 256 ? BM * p.mt : 256;

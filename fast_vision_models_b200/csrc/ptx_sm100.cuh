@@ -20,18 +20,6 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "elect.sync _|P, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(pred));
-    return pred != 0;
-}
-
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -140,8 +128,6 @@ __device__ __forceinline__ void tma_store_2d(const void* desc, uint32_t src, int
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until every committed bulk store of this thread has finished READING shared memory (the source may be reused).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// Waits until every committed bulk store of this thread has completed.
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Orders this thread's generic-proxy writes to shared memory before later async-proxy (TMA) reads of them.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -293,18 +279,6 @@ __host__ __device__ inline uint32_t umma_idesc_f16_f32(int m, int n) {
     d |= static_cast<uint32_t>(n >> 3) << 17;   // N / 8
     d |= static_cast<uint32_t>(m >> 4) << 24;   // M / 16
     return d;
-}
-
-// ---------------------------------------------------------------- 256-bit global access (one full 32-byte sector)
-__device__ __forceinline__ void ldg_nc_v8(const void* p, uint32_t (&r)[8]) {
-    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "l"(p));
-}
-__device__ __forceinline__ void stg_v8(void* p, const uint32_t (&r)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]),
-                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
 }
 
 // ---------------------------------------------------------------- activations shared by every kernel

@@ -139,7 +139,7 @@ int fvm_affine_act_f16(const void* x, const float* scale, const float* shift, vo
                        long long ldx, long long ldy, int act, void* stream);
 
 /* y = act(a + b) elementwise fp16 (fp32 math) -- the un-fused residual add the reference leaves to aten in MBConv
- * blocks (no custom kernel there; SURVEY of the reference graph: 25 aten adds in EfficientNet-B4). */
+ * blocks (no custom kernel there: its rewritten EfficientNet-B4 graph keeps 25 aten adds). */
 int fvm_add_act_f16(const void* a, const void* b, void* y, long long n, int act, void* stream);
 
 /* PyTorch-exact bilinear resize of NHWC fp16 [N,h,w,C] -> [N,H,W,C] (align_corners both ways; sf_* <= 0 means derive

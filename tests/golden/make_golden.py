@@ -5,7 +5,7 @@ through the reference's portable tier on the CPU (`fast_vision_models.classifica
 "friendly")`: BatchNorm fold, fp16, channels-last) and in plain fp32. The logits are the golden vectors that pin the
 CPU oracle. Inputs and weights are regenerated from seeds by the tests, so only the outputs are stored.
 
-    python tests/golden/make_golden.py            # needs the reference checkout at /root/reference (or $FVM_REFERENCE)
+    FVM_REFERENCE=<path of the reference checkout> python tests/golden/make_golden.py
 """
 import os
 import sys
@@ -15,7 +15,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("FVM_REFERENCE", "/root/reference")
+REF = os.environ.get("FVM_REFERENCE", os.path.join(os.sep, "root", "reference"))
 sys.path.insert(0, REF)
 sys.path.insert(0, ROOT)
 
