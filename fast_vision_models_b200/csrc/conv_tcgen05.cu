@@ -39,7 +39,10 @@ static constexpr int MAX_BIAS_BYTES = 16 * 1024;
 static constexpr int EPI_BACKOFF_NS = 64;     // sleep between polls of the epilogue / store warps
 static constexpr int MAX_STAGES = 8;
 static constexpr int MAX_EPI = 6;     // staging buffers for residual-in / output-out tiles
-static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI + 1;   // stages, accumulators, staging, resident B
+static constexpr int MAX_HALO = 3;    // halo-tile buffers (3x3 stride-1 mode)
+static constexpr int NUM_BARRIERS = 2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI + 1 + 2 * MAX_HALO;   // stages, accumulators, staging, resident B, halo
+static constexpr int HALO_TH = 16, HALO_TW = 8;   // output patch of a halo-mode tile: 16 rows x 8 columns = 128 pixels
+static constexpr int HALO_PITCH = 16;             // pixels per staged halo row (a multiple of 8: 8-row groups stay 1024-aligned)
 static constexpr int MISC_BYTES = 16 + (NUM_BARRIERS & 1) * 8;   // tmem slot, abort flag; keeps what follows 16-byte aligned
 static constexpr int TAPS_PER_KBLOCK = 8;                    // tap-packed mode, 8-channel taps: 8 taps x 8 channels = 64 K elements
 static constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;   // 16 KB
@@ -64,6 +67,13 @@ struct ConvParams {
     int tapk;      // 8 or 16: "tap-packed" mode for inputs of 8 / 16 channels: a k-block is 8 / 4 filter taps of that
                    // many channels (64 K elements), weights resident in smem; 0: one tap of 64 channels per k-block
     int taps;      // R * S
+    int halo;      // 1: 3x3 stride-1 'halo' mode: a tile is a 16x8 pixel patch of one image; its input patch (+ border) is
+                   // staged once per 64 channels and the 9 taps are shifted views of it (9x fewer L2 reads than im2col)
+    int halo_rows, nh, tiles_x, tiles_y;   // staged rows (16 + 2*dilation), halo buffers, patches per image row / column
+    FastDiv div_txy, div_tx;
+#ifdef FVM_CONV_TRACE
+    int dbg;
+#endif
     int bres;      // 1: the weights of this CTA's n-tile stay resident in shared memory (loaded once); each CTA keeps one
                    // n-tile and walks the m-tiles; pipeline stages then hold A only
     int act;
@@ -236,7 +246,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t b_kb_bytes = static_cast<uint32_t>(p.BN) * BK * 2;          // one k-block of a weight tile
     const uint32_t b_stage_bytes = (p.tapk || p.bres) ? 0u : b_kb_bytes;
-    const uint32_t a_stage_bytes = static_cast<uint32_t>(p.mt) * A_STAGE_BYTES;
+    const uint32_t a_stage_bytes = p.halo ? 0u : static_cast<uint32_t>(p.mt) * A_STAGE_BYTES;
     const uint32_t stage_bytes = a_stage_bytes + b_stage_bytes;
     const int tpk = p.tapk ? BK / p.tapk : 0;                                  // taps per k-block (8 or 4)
     const uint32_t tap_sub_bytes = static_cast<uint32_t>(BM * p.tapk * 2);    // one tap of one 128-pixel sub-tile
@@ -246,7 +256,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t bres_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
     const uint32_t bres_bytes = p.tapk ? static_cast<uint32_t>(p.kblocks * tpk) * tap_b_bytes
                                        : (p.bres ? static_cast<uint32_t>(p.kblocks) * b_kb_bytes : 0u);
-    const uint32_t epi_base = bres_base + bres_bytes;
+    const uint32_t halo_base = bres_base + bres_bytes;
+    const uint32_t halo_bytes = p.halo ? static_cast<uint32_t>(p.halo_rows * HALO_PITCH) * 128u : 0u;   // multiple of 2 KB
+    const uint32_t epi_base = halo_base + static_cast<uint32_t>(p.nh) * halo_bytes;
     const uint32_t epi_bytes = static_cast<uint32_t>(p.mt * p.nsub) * SUB_BYTES;   // staging: [mt][nsub] sub-tiles
     const uint32_t bar_base = epi_base + static_cast<uint32_t>(p.nepi) * epi_bytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -257,6 +269,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     auto epi_done_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + MAX_EPI + e); };
     auto epi_free_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 2 * MAX_EPI + e); };
     const uint32_t bres_full_bar = bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI);
+    auto hfull_bar = [&](int h) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI + 1 + h); };
+    auto hempty_bar = [&](int h) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI + 1 + MAX_HALO + h); };
     const uint32_t misc_off = (bar_base - smem_u32(smem_raw)) + 8u * NUM_BARRIERS;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + misc_off + 4);
@@ -266,7 +280,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t bias_off = misc_off + MISC_BYTES;
     const uint32_t bias_base = smem_u32(smem_raw) + bias_off;
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // warp-uniform by construction
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -284,6 +298,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(epi_free_bar(e), 1);
         }
         mbar_init(bres_full_bar, 1);
+        for (int h = 0; h < p.nh; ++h) {
+            mbar_init(hfull_bar(h), 1);
+            mbar_init(hempty_bar(h), 1);
+        }
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
@@ -334,9 +352,20 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                 (kb - tp * p.cchunks) * BK, tp, n_tile * p.BN);
                 }
             }
+            int hs = 0;
+            uint32_t hphase = 0;
             for (int pit = 0; ok && tile_at(p, pit, m_tile, n_tile); ++pit) {
                 const int m0 = m_tile * BM * p.mt;
                 const int n0 = n_tile * p.BN;
+                // halo mode: m_tile = (image, patch row, patch column)
+                int himg = 0, hy0 = 0, hx0 = 0;
+                if (p.halo) {
+                    himg = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_txy));
+                    const int rem = m_tile - himg * p.tiles_x * p.tiles_y;
+                    const int ty = static_cast<int>(fastdiv(static_cast<uint32_t>(rem), p.div_tx));
+                    hy0 = ty * HALO_TH;
+                    hx0 = (rem - ty * p.tiles_x) * HALO_TW;
+                }
                 TRACE(0, pit, 0);
                 if (p.has_res) {
                     // residual tile of this output tile -> staging buffer e (free once its previous store was read out)
@@ -351,9 +380,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     __syncwarp();
                     if (lane < p.mt * nsub) {     // one lane per staging sub-tile (at most 16)
                         const int mt = lane / nsub, sub = lane - mt * nsub;
-                        tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes +
-                                        static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES,
-                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
+                        const uint32_t dst = epi_base + static_cast<uint32_t>(e) * epi_bytes +
+                                             static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES;
+                        if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg);
+                        else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
                     }
                     if (++e == p.nepi) e = 0;
                     TRACE(0, pit, 1);
@@ -366,6 +396,40 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const int qq = rem - pp * p.Q;
                     h0 = pp * p.sh - p.ph;
                     w0 = qq * p.sw - p.pw;
+                }
+                if (p.halo) {
+                    // per 64-channel chunk: one staged input patch (rows hy0-ph .., 16 pixels from hx0-pw, zero outside
+                    // the image), then the 9 weight tiles of that chunk through the stage ring (unless resident)
+                    for (int hc = 0; ok && hc < p.cchunks; ++hc) {
+                        if (!mbar_wait(hempty_bar(hs), hphase ^ 1u, abort_flag)) {
+                            if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                            ok = false;
+                            break;
+                        }
+                        if (lane == 0) {
+                            mbar_expect_tx(hfull_bar(hs), halo_bytes);
+                            tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), hc * BK,
+                                        hx0 - p.pw, hy0 - p.ph, himg);
+                        }
+                        __syncwarp();
+                        if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
+                        if (p.bres) continue;
+                        for (int tp = 0; tp < p.taps; ++tp) {
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                                if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                                ok = false;
+                                break;
+                            }
+                            if (lane == 0) {
+                                mbar_expect_tx(full_bar(stage), stage_bytes);
+                                tma_load_3d(smem_base + static_cast<uint32_t>(stage) * stage_bytes, &tmap_b, full_bar(stage),
+                                            hc * BK, tp, n0);
+                            }
+                            __syncwarp();
+                            if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        }
+                    }
+                    continue;
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
@@ -419,18 +483,37 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
+                for (int i = 0; i < p.nh; ++i) {
+                    if (!mbar_wait(hempty_bar(hs), hphase ^ 1u, abort_flag)) break;
+                    if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // One elected lane runs the whole role. The descriptors are kept as 32-bit low words (start address) that advance
+        // by constants; the high words (stride, version, swizzle) never change; the four MMAs of a k-block are one
+        // instruction sequence.
+        if (elect_one()) {
             const uint32_t idesc = umma_idesc_f16_f32(BM, p.BN);
+            const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
+            const uint32_t hi_halo = static_cast<uint32_t>(umma_desc_sw128_at(0, HALO_PITCH * 128u) >> 32);
+            auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
+            const uint32_t stage_step = stage_bytes >> 4;
+            const uint32_t a_lo0 = lo_of(smem_base);
             int stage = 0;
             uint32_t phase = 0;
+            uint32_t st_lo = a_lo0;   // low descriptor word of the current stage's first byte
             uint32_t acc_phase = 0;   // one parity bit per accumulator buffer
             int it = 0;
             bool ok = true;
+            int mma_hs = 0;
+            uint32_t mma_hphase = 0;
             int m_tile, n_tile;
+            auto next_stage = [&]() {
+                st_lo += stage_step;
+                if (++stage == p.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }
+            };
             if ((p.tapk || p.bres) && tile_at(p, 0, m_tile, n_tile) && !mbar_wait(bres_full_bar, 0u, abort_flag)) {
                 atomicExch(p.status, STATUS_WAIT_MMA);
                 ok = false;
@@ -446,6 +529,53 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 tc_fence_after();
                 TRACE(1, it, 0);
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
+                if (p.halo) {
+                    for (int hc = 0; ok && hc < p.cchunks; ++hc) {
+                        if (!mbar_wait(hfull_bar(mma_hs), mma_hphase, abort_flag)) {
+                            atomicExch(p.status, STATUS_WAIT_MMA);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        // tap (tr, ts): the A rows are the staged patch shifted by (tr, ts) * dilation pixels; 8-pixel
+                        // groups (one patch row each) are one staged row (16 pixels = 2 KB) apart. The swizzle phase
+                        // follows the absolute shared-memory address, so a start at any 128-byte row needs no base offset.
+                        uint32_t b_lo_res = lo_of(bres_base + static_cast<uint32_t>(hc) * b_kb_bytes);
+                        uint32_t row_lo = lo_of(halo_base + static_cast<uint32_t>(mma_hs) * halo_bytes);
+                        for (int tr = 0; ok && tr < p.R; ++tr) {
+                            uint32_t a_lo = row_lo;
+                            for (int ts = 0; ts < p.S; ++ts) {
+                                uint32_t b_lo = b_lo_res;
+                                if (!p.bres) {
+                                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                                        atomicExch(p.status, STATUS_WAIT_MMA);
+                                        ok = false;
+                                        break;
+                                    }
+                                    tc_fence_after();
+                                    b_lo = st_lo;
+                                }
+                                umma_f16_kblock(d_tmem, a_lo, hi_halo, b_lo, hi128, idesc, static_cast<uint32_t>((hc | tr | ts) != 0));
+#ifdef FVM_CONV_TRACE
+                                if (hc == 0) { const int tq = tr * 3 + ts; if (tq == 0) TRACE(1, it, 1); else if (tq < 6) TRACE(1, it, 2 + tq); }
+#endif
+                                if (!p.bres) {
+                                    umma_commit(empty_bar(stage));
+                                    next_stage();
+                                }
+                                a_lo += static_cast<uint32_t>(p.dw) * 8u;                          // next tap: dw pixels of 128 B
+                                b_lo_res += static_cast<uint32_t>(p.cchunks) * (b_kb_bytes >> 4);  // resident: next tap's block
+                            }
+                            row_lo += static_cast<uint32_t>(p.dh * HALO_PITCH) * 8u;
+                        }
+                        umma_commit(hempty_bar(mma_hs));     // the staged patch is free once these MMAs have read it
+                        if (++mma_hs == p.nh) { mma_hs = 0; mma_hphase ^= 1u; }
+                    }
+                    if (ok) umma_commit(tfull_bar(acc));
+                    TRACE(1, it, 2);
+                    continue;
+                }
+                uint32_t bres_lo = lo_of(bres_base);
                 for (int kb = 0; kb < p.kblocks; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         atomicExch(p.status, STATUS_WAIT_MMA);
@@ -469,7 +599,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             }
                         }
                         umma_commit(empty_bar(stage));
-                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        next_stage();
                         continue;
                     }
                     if (p.tapk) {
@@ -489,30 +619,26 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             }
                         }
                         umma_commit(empty_bar(stage));
-                        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        next_stage();
                         continue;
                     }
-                    const uint64_t b_desc = umma_desc_sw128(p.bres ? bres_base + static_cast<uint32_t>(kb) * b_kb_bytes
-                                                                   : a_src + a_stage_bytes);
-                    for (int mt = 0; mt < p.mt; ++mt) {
-                        // sub-tile mt: its own 128 rows of A, the shared B tile, accumulator columns [mt*BN, (mt+1)*BN)
-                        const uint64_t a_desc = umma_desc_sw128(a_src + static_cast<uint32_t>(mt) * A_STAGE_BYTES);
-#pragma unroll
-                        for (int k = 0; k < BK / 16; ++k) {
-                            // advancing 16 halves (32 bytes) along K inside the swizzle row: +2 in the >>4 address field
-                            umma_f16(d_tmem + static_cast<uint32_t>(mt * p.BN), a_desc + static_cast<uint64_t>(2 * k),
-                                     b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
-                        }
-                    }
+                    const uint32_t b_lo = p.bres ? bres_lo : st_lo + (a_stage_bytes >> 4);
+                    bres_lo += b_kb_bytes >> 4;
+                    // sub-tile mt: its own 128 rows of A, the shared B tile, accumulator columns [mt*BN, (mt+1)*BN)
+                    for (int mt = 0; mt < p.mt; ++mt)
+                        umma_f16_kblock(d_tmem + static_cast<uint32_t>(mt * p.BN),
+                                        st_lo + static_cast<uint32_t>(mt) * (A_STAGE_BYTES >> 4), hi128, b_lo, hi128, idesc,
+                                        static_cast<uint32_t>(kb != 0));
                     if (kb == 0) TRACE(1, it, 3);
                     umma_commit(empty_bar(stage));   // frees the stage once these MMAs have read it
                     if (kb == 0) TRACE(1, it, 4);
-                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                    next_stage();
                 }
                 if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
                 TRACE(1, it, 2);
             }
         }
+        __syncwarp();
     } else if (warp < STORE_WARP) {
         // ------------------------------------------------------------------ epilogue
         // EPI_GROUPS groups of 4 warps (one warp per TMEM lane group). Group g owns accumulator buffer g and takes the
@@ -566,6 +692,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // activation as a template argument for the common ones (0 none, 1 relu, 3 silu, 5 gelu-erf); 2 = read at run time
             const int act_t = (p.act == 0 || p.act == 1 || p.act == 3 || p.act == 5) ? p.act : 2;
             const int variant = act_t * 2 + (p.has_res ? 1 : 0);
+#ifdef FVM_CONV_TRACE
+            if (!(p.dbg & 1))
+#endif
             for (int mt = 0; mt < p.mt; ++mt) {
                 const uint32_t t_sub = t_row + static_cast<uint32_t>(mt * p.BN);
                 const uint32_t s_sub = stage_row0 + static_cast<uint32_t>(mt * p.nsub) * SUB_BYTES;
@@ -597,7 +726,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else {
         // ------------------------------------------------------------------ store warp
-        if (lane == 0) {
+        if (elect_one()) {
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             int e = 0;
             bool ok = true;
@@ -614,7 +743,15 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 e_phase ^= 1u << e;
                 TRACE(6, sit, 1);
                 const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
-                for (int mt = 0; mt < p.mt && m0 + mt * BM < p.M; ++mt)     // sub-tiles past the last row: nothing to store
+                if (p.halo) {
+                    const int himg = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_txy));
+                    const int rem = m_tile - himg * p.tiles_x * p.tiles_y;
+                    const int ty = static_cast<int>(fastdiv(static_cast<uint32_t>(rem), p.div_tx));
+                    for (int sub = 0; sub < nsub; ++sub)      // 16 x 8 pixel patch, clipped at the image border
+                        tma_store_4d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                     n0 + sub * 64, (rem - ty * p.tiles_x) * HALO_TW, ty * HALO_TH, himg);
+                }
+                for (int mt = 0; !p.halo && mt < p.mt && m0 + mt * BM < p.M; ++mt)     // sub-tiles past the last row: nothing to store
                     for (int sub = 0; sub < nsub; ++sub)
                         tma_store_2d(&tmap_y,
                                      epi_base + static_cast<uint32_t>(e) * epi_bytes +
@@ -688,16 +825,17 @@ struct SmemPlan {
     int stages, nepi, nacc;
     size_t bytes;
 };
-static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, SmemPlan* out) {
+static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, SmemPlan* out, uint32_t halo_bytes = 0) {
     const int n_tiles = (K + BN - 1) / BN;
-    const uint32_t stage_bytes =
-        static_cast<uint32_t>(MT) * A_STAGE_BYTES + ((tapk || bres) ? 0u : static_cast<uint32_t>(BN) * BK * 2);
+    // halo mode (halo_bytes > 0): the activations live in two staged input patches, the stages carry weights only
+    const uint32_t stage_bytes = (halo_bytes ? 0u : static_cast<uint32_t>(MT) * A_STAGE_BYTES) +
+                                 ((tapk || bres) ? 0u : static_cast<uint32_t>(BN) * BK * 2);
     const uint32_t bres_bytes = tapk ? static_cast<uint32_t>(kblocks) * BN * BK * 2   // 8 x 16 B or 4 x 32 B per row
                                      : (bres ? static_cast<uint32_t>(kblocks) * BN * BK * 2 : 0u);
     const uint32_t epi_bytes = static_cast<uint32_t>(MT * ((BN + 63) / 64)) * SUB_BYTES;
     const uint32_t bias_bytes = (static_cast<uint32_t>(n_tiles * BN) * 4 + 15u) & ~15u;   // fp32 copy of the bias
     if (bias_bytes > MAX_BIAS_BYTES) return false;
-    const uint32_t fixed = 1024 + 8 * NUM_BARRIERS + MISC_BYTES + bias_bytes + bres_bytes;
+    const uint32_t fixed = 1024 + 8 * NUM_BARRIERS + MISC_BYTES + bias_bytes + bres_bytes + 2 * halo_bytes;
     const uint32_t total = 227 * 1024;
     // deep reductions reach the epilogue rarely: they may run on a single staging buffer and give the rest to the pipeline
     const int floor_epi = kblocks >= 16 ? 1 : 2;
@@ -716,7 +854,7 @@ static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, 
            static_cast<uint32_t>(nepi) * epi_bytes + static_cast<uint32_t>(min_stages) * stage_bytes > budget)
         --nepi;
     if (nepi < nacc) nacc = 2;
-    int stages = static_cast<int>((budget - static_cast<uint32_t>(nepi) * epi_bytes) / stage_bytes);
+    int stages = stage_bytes ? static_cast<int>((budget - static_cast<uint32_t>(nepi) * epi_bytes) / stage_bytes) : 2;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     out->nacc = nacc;
@@ -770,7 +908,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (!st) return FVM_ERR_SETUP;
     if (!x || !w || !y) return FVM_ERR_ARG;
     // force_bn: low 16 bits = output-channel tile (0 = choose), bits 16..23 = sub-tiles per tile (0 = choose),
-    // bits 24..25 = weight-resident mode (0 = choose, 1 = on, 2 = off)
+    // bits 24..25 = weight-resident mode (0 = choose, 1 = on, 2 = off), bits 26..27 = halo mode (same coding)
+    const int force_halo = force_bn > 0 ? ((force_bn >> 26) & 3) : 0;
     const int force_bres = force_bn > 0 ? ((force_bn >> 24) & 3) : 0;
     const int force_mt = force_bn > 0 ? ((force_bn >> 16) & 0xff) : 0;
     force_bn = force_bn > 0 ? (force_bn & 0xffff) : 0;
@@ -811,12 +950,36 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
             force_bn = Kp16;
         }
     }
+    // Halo mode for 3x3 stride-1 convolutions (dilation up to 4): an m-tile is a 16 x 8 patch of output pixels of one
+    // image. Chosen when few patch pixels fall outside the image (they are computed and clipped by the store).
+    uint32_t halo_bytes = 0;
+    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1) {
+        const int ty = (P + HALO_TH - 1) / HALO_TH, tx = (Q + HALO_TW - 1) / HALO_TW;
+        const double eff = static_cast<double>(P) * Q / (static_cast<double>(ty) * tx * BM);
+        // by default only for inputs of one 64-channel chunk: there the taps are accumulated in the same order as in
+        // im2col mode (bit-identical results), and the measured gain is largest
+        if (force_halo == 1 || (eff >= 0.95 && p.cchunks == 1)) {
+            p.halo = 1;
+            p.halo_rows = HALO_TH + (R - 1) * dh;
+            p.nh = 2;
+            p.tiles_x = tx;
+            p.tiles_y = ty;
+            p.div_txy = fastdiv_init(static_cast<uint32_t>(tx * ty));
+            p.div_tx = fastdiv_init(static_cast<uint32_t>(tx));
+            p.m_tiles = N * ty * tx;
+            halo_bytes = static_cast<uint32_t>(p.halo_rows * HALO_PITCH) * 128u;
+        }
+    }
+    if (force_halo == 1 && !p.halo) return FVM_ERR_ARG;
     p.BN = force_bn > 0 ? force_bn : pick_bn(p.m_tiles, K, p.kblocks, false, st->sms);
     if (p.BN < 32 || p.BN > 256 || (p.BN & 31)) return FVM_ERR_ARG;
     p.n_tiles = (K + p.BN - 1) / p.BN;
     p.div_ntiles = fastdiv_init(static_cast<uint32_t>(p.n_tiles));
     if (p.n_tiles > 1 && (p.BN & 63)) return FVM_ERR_ARG;   // split K only in whole 64-channel store boxes
     p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && ph_hi == 0 && pw_hi == 0);
+#ifdef FVM_CONV_TRACE
+    p.dbg = getenv("FVM_DBG") ? atoi(getenv("FVM_DBG")) : 0;
+#endif
     p.act = act;
     p.has_res = res != nullptr;
     p.bias = static_cast<const __half*>(bias);
@@ -829,7 +992,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // overlap between the roles), so the default stays at one sub-tile; the host's per-layer tuning may force more.
     p.mt = force_mt > 0 ? force_mt : 1;
     if (p.mt != 1 && p.mt != 2 && p.mt != 4) return FVM_ERR_ARG;
-    p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
+    if (!p.halo) p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
     p.a_rows = BM * p.mt < 256 ? BM * p.mt : 256;
     p.a_loads = BM * p.mt / p.a_rows;
 
@@ -845,11 +1008,12 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         const bool worth = p.m_tiles >= 2 * cta_per_n;
         SmemPlan rp;
         if (wbytes <= 96 * 1024 && (worth || force_bres == 1) &&
-            plan_smem(p.BN, p.mt, p.kblocks, K, false, true, &rp) && (rp.stages >= 4 || force_bres == 1))
+            plan_smem(p.BN, p.mt, p.kblocks, K, false, true, &rp, halo_bytes) &&
+            (rp.stages >= 4 || p.halo || force_bres == 1))
             p.bres = 1;
     }
     if (force_bres == 1 && !p.bres) return FVM_ERR_ARG;
-    if (!plan_smem(p.BN, p.mt, p.kblocks, K, p.tapk != 0, p.bres != 0, &sp)) return FVM_ERR_ARG;
+    if (!plan_smem(p.BN, p.mt, p.kblocks, K, p.tapk != 0, p.bres != 0, &sp, halo_bytes)) return FVM_ERR_ARG;
     p.bias_elems = p.n_tiles * p.BN;
     p.stages = sp.stages;
     p.nepi = sp.nepi;
@@ -863,7 +1027,29 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (smem < 120 * 1024) smem = 120 * 1024;
 
     CUtensorMap tmap_a, tmap_b, tmap_r, tmap_y;
-    {
+    if (p.halo) {
+        // output / residual as (K, Q, P, N): 64-channel x 8-column x 16-row boxes (clipped at the image border)
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(Q), static_cast<cuuint64_t>(P),
+                              static_cast<cuuint64_t>(N)};
+        cuuint32_t box[4] = {64, HALO_TW, HALO_TH, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        cuuint64_t ystr[3] = {static_cast<cuuint64_t>(ldy) * 2, static_cast<cuuint64_t>(Q) * ldy * 2,
+                              static_cast<cuuint64_t>(P) * Q * ldy * 2};
+        CUresult r = g_encode_tiled(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, y, dims, ystr, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
+        if (res) {
+            cuuint64_t rstr[3] = {static_cast<cuuint64_t>(ldr) * 2, static_cast<cuuint64_t>(Q) * ldr * 2,
+                                  static_cast<cuuint64_t>(P) * Q * ldr * 2};
+            r = g_encode_tiled(&tmap_r, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(res), dims, rstr, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
+        } else {
+            tmap_r = tmap_y;
+        }
+    } else {
         // output [M, K] (row stride ldy) and residual [M, K] (row stride ldr): 64-channel x 128-row boxes
         cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(p.M)};
         cuuint32_t box[2] = {64, BM};
@@ -896,7 +1082,19 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
     }
-    if (!p.im2col) {
+    if (p.halo) {
+        // NHWC activation as (C, W, H, N): one box = 64 channels x 16 pixels x (16 + 2*dilation) rows, zero outside
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(N)};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(ldx) * 2, static_cast<cuuint64_t>(W) * ldx * 2,
+                                 static_cast<cuuint64_t>(H) * W * ldx * 2};
+        cuuint32_t box[4] = {BK, HALO_PITCH, static_cast<cuuint32_t>(p.halo_rows), 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = g_encode_tiled(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(x), dims, strides,
+                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
+    } else if (!p.im2col) {
         cuuint64_t dims[2] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(p.M)};
         cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldx) * 2};
         cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(p.a_rows)};

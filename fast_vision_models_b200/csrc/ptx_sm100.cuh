@@ -107,6 +107,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* desc, uint
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 // im2col-mode load of NHWC activations: coordinates (c, w, h, n) of the first pixel's filter-window origin, plus the
 // filter tap offset (off_w, off_h) in input pixels (tap index times dilation).
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* desc, uint32_t bar, int c, int w, int h,
@@ -123,6 +129,11 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* des
 __device__ __forceinline__ void tma_store_2d(const void* desc, uint32_t src, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void* desc, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -210,6 +221,54 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a converged warp, the same one on every call (elect.sync over the full mask). The compiler knows that a
+// region guarded by this predicate runs in a single lane and keeps the operands of the single-thread tcgen05 / TMA
+// instructions in uniform registers: measured on B200, a loop of tcgen05.mma issued under `if (elect_one())` costs
+// about 50 cycles per instruction, the same loop under `if (lane == 0)` about 120.
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, e;\n\t"
+        "}\n"
+        : "=r"(pred));
+    return pred;
+}
+// The four tcgen05.mma of one 64-half k-block (K = 16 each) as one instruction sequence. Descriptors come as (low word,
+// high word): the start address lives in the low word, so the steps along K (+32 bytes = +2) are 32-bit adds. The first
+// MMA accumulates iff `acc0` != 0, the other three always do. Call from the single issuing lane.
+__device__ __forceinline__ void umma_f16_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 al, bl;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "add.u32 al, %1, 2;\n\t"
+        "add.u32 bl, %3, 2;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, 1;\n\t"
+        "add.u32 al, %1, 4;\n\t"
+        "add.u32 bl, %3, 4;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, 1;\n\t"
+        "add.u32 al, %1, 6;\n\t"
+        "add.u32 bl, %3, 6;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, 1;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc0)
+        : "memory");
+}
 // Arrive on an mbarrier once every MMA issued so far by this thread has finished (implies fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -247,6 +306,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
     d |= static_cast<uint64_t>(1) << 46;                           // descriptor version 1 (sm_100)
     d |= static_cast<uint64_t>(2) << 61;                           // layout type: SWIZZLE_128B
+    return d;
+}
+// As umma_desc_sw128 for an operand that starts at any 128-byte row of a swizzled block (not only at a 1024-byte
+// boundary) and whose 8-row groups are `sbo` bytes apart. The hardware applies the swizzle to the absolute
+// shared-memory address, so data written by TMA into a 1024-byte-aligned buffer is read back correctly from any row
+// with the base-offset field left at zero (measured on B200: a non-zero base offset gives wrong operands here).
+__device__ __forceinline__ uint64_t umma_desc_sw128_at(uint32_t smem_addr, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
     return d;
 }
 // K-major operand tile whose rows are 32 bytes (16 halves = one MMA K step) wide, written by TMA with the 32-byte

@@ -94,6 +94,12 @@ class FusedConv(nn.Module):
         rows = x.shape[0] * out.shape[2] * out.shape[3]
         if rows >= 148 * 8 * 128 and self.w.shape[2] * self.w.shape[3] * ((self.w.shape[1] + 63) // 64) <= 9:
             cands += [c | (2 << 16) for c in widths if (c or K) <= 128]   # short reductions on large maps: 256-pixel tiles
+        R_, S_ = self.w.shape[2], self.w.shape[3]
+        if (R_ == 3 and S_ == 3 and tuple(self.stride) == (1, 1) and self.dilation[0] == self.dilation[1] <= 4
+                and 8 < self.w.shape[1] <= 64):
+            # 3x3 stride-1 over at most 64 channels: staged input patches (bits 26..27 = 1) against im2col loads (= 2),
+            # per tile width. With one 64-channel chunk both modes add the taps in the same order: same bits.
+            cands += [c | (1 << 26) for c in widths] + [c | (2 << 26) for c in widths]
         best, best_ms = 0, float("inf")
         if len(cands) > 1:
             for c in cands:

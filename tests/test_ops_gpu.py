@@ -127,6 +127,46 @@ def test_conv_weight_resident_mode_matches_streaming_mode(case):
     assert torch.equal(y_on, y_off)
 
 
+HALO_CASES = [
+    # N, H, W, C, K, dil, res, tile, weight-resident (0 choose / 1 on / 2 off)
+    (2, 16, 8, 64, 64, 1, False, 0, 2),        # exactly one patch per image
+    (2, 56, 56, 64, 64, 1, True, 0, 1),        # ResNet layer1 shape: bottom patches half outside the image
+    (3, 17, 13, 64, 64, 1, False, 0, 2),       # ragged: patches clipped on both borders
+    (2, 28, 28, 128, 128, 1, True, 0, 2),      # two 64-channel chunks, weights streamed
+    (2, 20, 24, 256, 256, 2, False, 256, 2),   # dilation 2, four chunks, 256-channel tile
+    (1, 32, 32, 128, 512, 4, True, 128, 2),    # dilation 4, several n-tiles
+    (2, 24, 16, 96, 40, 1, False, 0, 0),       # ragged channels on both sides
+    (64, 14, 14, 64, 64, 1, False, 0, 0),      # many small images
+]
+
+
+@pytest.mark.parametrize("case", HALO_CASES)
+def test_conv_halo_mode_matches_oracle_and_im2col_mode(case):
+    # 3x3 stride-1 convolutions over staged input patches (each input pixel read once per tile) against the oracle
+    # and against the same convolution through im2col loads (above 64 input channels the fp32 summation order differs)
+    N, H, W, C, K, d, res, bn, wr = case
+    x, w, b = gen((N, C, H, W), 11), gen((K, C, 3, 3), 12, 0.05), gen((K,), 13, 0.1)
+    r = gen((N, K, H, W), 14) if res else None
+    ref = R.conv_fused_ref(x, w, b, r, (d, d), (1, 1), 1, dilation=(d, d))
+    args = (cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (d, d), (1, 1), 1)
+    y_halo = ops.conv_fused(*args, dilation=(d, d), tile_n=(1 << 26) | (wr << 24) | bn)
+    assert ops.last_status() == 0
+    y_plain = ops.conv_fused(*args, dilation=(d, d), tile_n=(2 << 26) | (wr << 24) | bn)
+    assert ops.last_status() == 0
+    close(y_halo, ref)
+    close(y_halo, y_plain)
+    if C <= 64:
+        assert torch.equal(y_halo, y_plain)     # one 64-channel chunk: the taps are added in the same order
+
+
+def test_conv_halo_mode_is_refused_where_it_does_not_apply():
+    x, w = cl(gen((1, 64, 16, 16), 1)), cl(gen((64, 64, 3, 3), 2, 0.05))
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x, w, None, None, (1, 1), (2, 2), 0, tile_n=1 << 26)          # stride 2
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x, w, None, None, (8, 8), (1, 1), 0, dilation=(8, 8), tile_n=1 << 26)   # dilation above 4
+
+
 @pytest.mark.parametrize("case", [(2, 20, 22, 16, 64, 3, 3, 1, 1), (2, 17, 19, 16, 48, 7, 4, 3, 1), (3, 12, 12, 16, 96, 2, 2, 0, 2),
                                   (1, 9, 40, 16, 256, 1, 5, 0, 1)])
 def test_conv_sixteen_channel_taps(case):
