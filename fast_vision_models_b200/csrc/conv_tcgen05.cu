@@ -232,6 +232,17 @@ __device__ __forceinline__ bool tile_at(const ConvParams& p, int it, int& m_tile
     return true;
 }
 
+// Number of tiles tile_at() yields for this CTA.
+__device__ __forceinline__ int cta_tile_count(const ConvParams& p) {
+    if (p.bres) {
+        const int per_n = static_cast<int>(fastdiv(gridDim.x, p.div_ntiles));
+        const int q = static_cast<int>(fastdiv(blockIdx.x, p.div_ntiles));
+        return q < p.m_tiles ? (p.m_tiles - q + per_n - 1) / per_n : 0;
+    }
+    const int tiles = p.m_tiles * p.n_tiles;
+    return static_cast<int>(blockIdx.x) < tiles ? (tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
+}
+
 // Shared memory map (after rounding the base up to 1024 bytes):
 //   [stages x (A tile 16 KB | B tile BN*128 B)] [nepi x nsub x 16 KB staging] [barriers] [tmem slot, abort flag]
 //   [bias copy, fp32, zero-padded to n_tiles*BN]
@@ -298,6 +309,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(epi_free_bar(e), 1);
         }
         mbar_init(bres_full_bar, 1);
+#ifdef FVM_CONV_TRACE
+        mbar_init(hfull_bar(2), 1);
+#endif
         for (int h = 0; h < p.nh; ++h) {
             mbar_init(hfull_bar(h), 1);
             mbar_init(hempty_bar(h), 1);
@@ -325,9 +339,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        // The whole warp runs the loop (uniform control flow); lane 0 arms the barriers, then several lanes issue
-        // their bulk loads in the same instruction (one lane per filter tap in tap-packed mode; A and B otherwise).
-        {
+        // One elected lane runs the whole role and issues every bulk load (issuing from several lanes of a warp makes
+        // the compiler serialise them anyway, at a higher cost per load).
+        if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
             int e = 0;
@@ -336,20 +350,19 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int PQ = p.P * p.Q;
             if (p.tapk) {
                 // weights of every tap (taps past R*S are out of bounds of the weight tensor: zero-filled)
-                if (lane == 0) mbar_expect_tx(bres_full_bar, bres_bytes);
-                __syncwarp();
-                for (int t = lane; t < p.kblocks * tpk; t += 32)
+                mbar_expect_tx(bres_full_bar, bres_bytes);
+                for (int t = 0; t < p.kblocks * tpk; ++t)
                     tma_load_3d(bres_base + static_cast<uint32_t>(t) * tap_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
             }
             int m_tile, n_tile;
             if (p.bres && tile_at(p, 0, m_tile, n_tile)) {
                 // this CTA's weight tile, all k-blocks, once: k-block kb = (tap kb / cchunks, channels (kb % cchunks)*64)
-                if (lane == 0) mbar_expect_tx(bres_full_bar, bres_bytes);
-                __syncwarp();
-                for (int kb = lane; kb < p.kblocks; kb += 32) {
-                    const int tp = kb / p.cchunks;
-                    tma_load_3d(bres_base + static_cast<uint32_t>(kb) * b_kb_bytes, &tmap_b, bres_full_bar,
-                                (kb - tp * p.cchunks) * BK, tp, n_tile * p.BN);
+                mbar_expect_tx(bres_full_bar, bres_bytes);
+                int tp = 0, cc = 0;
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    tma_load_3d(bres_base + static_cast<uint32_t>(kb) * b_kb_bytes, &tmap_b, bres_full_bar, cc * BK, tp,
+                                n_tile * p.BN);
+                    if (++cc == p.cchunks) { cc = 0; ++tp; }
                 }
             }
             int hs = 0;
@@ -370,23 +383,50 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (p.has_res) {
                     // residual tile of this output tile -> staging buffer e (free once its previous store was read out)
                     if (!mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag)) {
-                        if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
                         ok = false;
                         break;
                     }
                     e_phase ^= 1u << e;
                     const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
-                    if (lane == 0) mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(p.mt * nsub) * SUB_BYTES);
-                    __syncwarp();
-                    if (lane < p.mt * nsub) {     // one lane per staging sub-tile (at most 16)
-                        const int mt = lane / nsub, sub = lane - mt * nsub;
-                        const uint32_t dst = epi_base + static_cast<uint32_t>(e) * epi_bytes +
-                                             static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES;
-                        if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg);
-                        else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
-                    }
+                    mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(p.mt * nsub) * SUB_BYTES);
+                    for (int mt = 0; mt < p.mt; ++mt)
+                        for (int sub = 0; sub < nsub; ++sub) {
+                            const uint32_t dst = epi_base + static_cast<uint32_t>(e) * epi_bytes +
+                                                 static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES;
+                            if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg);
+                            else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
+                        }
                     if (++e == p.nepi) e = 0;
                     TRACE(0, pit, 1);
+                }
+                if (p.halo) {
+                    // per 64-channel chunk: one staged input patch (rows hy0-ph .., 16 pixels from hx0-pw, zero outside
+                    // the image), then the 9 weight tiles of that chunk through the stage ring (unless resident)
+                    for (int hc = 0; ok && hc < p.cchunks; ++hc) {
+                        if (!mbar_wait(hempty_bar(hs), hphase ^ 1u, abort_flag)) {
+                            atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(hfull_bar(hs), halo_bytes);
+                        tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), hc * BK,
+                                    hx0 - p.pw, hy0 - p.ph, himg);
+                        if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
+                        if (p.bres) continue;
+                        for (int tp = 0; tp < p.taps; ++tp) {
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                                atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                                ok = false;
+                                break;
+                            }
+                            mbar_expect_tx(full_bar(stage), stage_bytes);
+                            tma_load_3d(smem_base + static_cast<uint32_t>(stage) * stage_bytes, &tmap_b, full_bar(stage),
+                                        hc * BK, tp, n0);
+                            if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                        }
+                    }
+                    continue;
                 }
                 int img = 0, h0 = 0, w0 = 0;
                 if (p.im2col) {
@@ -397,56 +437,20 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     h0 = pp * p.sh - p.ph;
                     w0 = qq * p.sw - p.pw;
                 }
-                if (p.halo) {
-                    // per 64-channel chunk: one staged input patch (rows hy0-ph .., 16 pixels from hx0-pw, zero outside
-                    // the image), then the 9 weight tiles of that chunk through the stage ring (unless resident)
-                    for (int hc = 0; ok && hc < p.cchunks; ++hc) {
-                        if (!mbar_wait(hempty_bar(hs), hphase ^ 1u, abort_flag)) {
-                            if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
-                            ok = false;
-                            break;
-                        }
-                        if (lane == 0) {
-                            mbar_expect_tx(hfull_bar(hs), halo_bytes);
-                            tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), hc * BK,
-                                        hx0 - p.pw, hy0 - p.ph, himg);
-                        }
-                        __syncwarp();
-                        if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
-                        if (p.bres) continue;
-                        for (int tp = 0; tp < p.taps; ++tp) {
-                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-                                if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
-                                ok = false;
-                                break;
-                            }
-                            if (lane == 0) {
-                                mbar_expect_tx(full_bar(stage), stage_bytes);
-                                tma_load_3d(smem_base + static_cast<uint32_t>(stage) * stage_bytes, &tmap_b, full_bar(stage),
-                                            hc * BK, tp, n0);
-                            }
-                            __syncwarp();
-                            if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-                        }
-                    }
-                    continue;
-                }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-                        if (lane == 0) atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
                         ok = false;
                         break;
                     }
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     const uint32_t b_dst = a_dst + a_stage_bytes;
-                    if (lane == 0) mbar_expect_tx(full_bar(stage), stage_bytes);
-                    __syncwarp();
+                    mbar_expect_tx(full_bar(stage), stage_bytes);
                     if (p.tapk) {
-                        // 8 taps of 8 channels: each lands as a dense [128*mt pixels][16 B] block (8-row x 16-byte core
-                        // matrices back to back). Taps past the filter re-read the last tap; their weights are zero.
-                        if (lane < tpk) {
-                            const int j = lane;
+                        // 8 (or 4) taps of 8 (16) channels: each lands as a dense [128*mt pixels][16 (32) B] block. Taps
+                        // past the filter re-read the last tap; their weights are zero.
+                        for (int j = 0; j < tpk; ++j) {
                             const int t = min(kb * tpk + j, p.taps - 1);
                             const int tr = t / p.S, ts = t - tr * p.S;
                             tma_load_im2col_4d(a_dst + static_cast<uint32_t>(j) * tap_a_bytes, &tmap_a, full_bar(stage), 0,
@@ -456,16 +460,14 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
-                    if (lane == 0) {
-                        if (!p.bres) tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
-                    } else if (p.im2col) {
-                        if (lane == 1)
-                            tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
-                                               static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
-                    } else if (lane <= p.a_loads) {
-                        const int l = lane - 1;
-                        tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage), cc * BK,
-                                    m0 + l * p.a_rows);
+                    if (!p.bres) tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    if (p.im2col) {
+                        tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
+                                           static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                    } else {
+                        for (int l = 0; l < p.a_loads; ++l)
+                            tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage), cc * BK,
+                                        m0 + l * p.a_rows);
                     }
                     if (++cc == p.cchunks) {
                         cc = 0;
@@ -489,11 +491,15 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        // One elected lane runs the whole role. The descriptors are kept as 32-bit low words (start address) that advance
-        // by constants; the high words (stride, version, swizzle) never change; the four MMAs of a k-block are one
-        // instruction sequence.
+        // One elected lane runs the whole role. Every loop bound and branch of the role depends on kernel parameters
+        // and counters only (a wait that runs out is recorded and the role carries on: once the abort flag is up all
+        // waits of the CTA return at once), so the compiler can keep the counters and descriptors in uniform
+        // registers, which the tcgen05 instructions read their operands from; measured, this halves the issue cost.
+        // Descriptors are kept as 32-bit low words (start address) that advance by constants; the high words (stride,
+        // version, swizzle) never change; the four MMAs of a k-block are one instruction sequence.
         if (elect_one()) {
             const uint32_t idesc = umma_idesc_f16_f32(BM, p.BN);
             const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
@@ -501,67 +507,78 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
             const uint32_t stage_step = stage_bytes >> 4;
             const uint32_t a_lo0 = lo_of(smem_base);
+            const int my_tiles = cta_tile_count(p);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t st_lo = a_lo0;   // low descriptor word of the current stage's first byte
             uint32_t acc_phase = 0;   // one parity bit per accumulator buffer
-            int it = 0;
-            bool ok = true;
+            int acc = -1;
+            bool failed = false;
             int mma_hs = 0;
             uint32_t mma_hphase = 0;
-            int m_tile, n_tile;
-            auto next_stage = [&]() {
-                st_lo += stage_step;
-                if (++stage == p.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }
-            };
-            if ((p.tapk || p.bres) && tile_at(p, 0, m_tile, n_tile) && !mbar_wait(bres_full_bar, 0u, abort_flag)) {
-                atomicExch(p.status, STATUS_WAIT_MMA);
-                ok = false;
-            }
-            for (; ok && tile_at(p, it, m_tile, n_tile); ++it) {
-                const int acc = it % p.nacc;
-                if (!mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag)) {
-                    atomicExch(p.status, STATUS_WAIT_MMA);
-                    ok = false;
-                    break;
+#define NEXT_STAGE()                                                          \
+    do {                                                                      \
+        st_lo += stage_step;                                                  \
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }   \
+    } while (0)
+#ifdef FVM_CONV_TRACE
+            if (p.dbg & 2) {    // issue-rate probe in this kernel's context: 256 MMAs on whatever the buffers hold
+                const long long c0 = clock64();
+                for (int kb = 0; kb < 64; ++kb) {
+                    const int tp = kb % 9, tr = tp / 3, ts = tp - tr * 3;
+                    umma_f16_kblock(tmem_base, lo_of(halo_base) + (tr * 16 + ts) * 8, hi_halo, lo_of(bres_base) + (kb & 3) * (p.BN * 8), hi128, idesc, kb != 0);
                 }
+                const long long c1 = clock64();
+                umma_commit(hfull_bar(2));
+                mbar_wait(hfull_bar(2), 0u, abort_flag);
+                const long long c2 = clock64();
+                if (blockIdx.x == 0) { g_conv_trace[4000] = c1 - c0; g_conv_trace[4001] = c2 - c0; }
+            }
+#endif
+            if ((p.tapk || p.bres) && my_tiles > 0) failed |= !mbar_wait(bres_full_bar, 0u, abort_flag);
+            // Look-ahead: the barrier of the next step (stage, staged patch, accumulator) is tested while the MMAs of
+            // the current step are issued; the blocking wait runs only if that test said "not yet".
+            uint32_t st_ready = 0, acc_ready = 0, h_ready = 0;
+            for (int it = 0; it < my_tiles; ++it) {
+                if (++acc == p.nacc) acc = 0;
+                if (!acc_ready) failed |= !mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag);
                 acc_phase ^= 1u << acc;
+                const int acc_next = acc + 1 == p.nacc ? 0 : acc + 1;
                 tc_fence_after();
                 TRACE(1, it, 0);
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
                 if (p.halo) {
-                    for (int hc = 0; ok && hc < p.cchunks; ++hc) {
-                        if (!mbar_wait(hfull_bar(mma_hs), mma_hphase, abort_flag)) {
-                            atomicExch(p.status, STATUS_WAIT_MMA);
-                            ok = false;
-                            break;
-                        }
+                    for (int hc = 0; hc < p.cchunks; ++hc) {
+                        if (!h_ready) failed |= !mbar_wait(hfull_bar(mma_hs), mma_hphase, abort_flag);
                         tc_fence_after();
                         // tap (tr, ts): the A rows are the staged patch shifted by (tr, ts) * dilation pixels; 8-pixel
                         // groups (one patch row each) are one staged row (16 pixels = 2 KB) apart. The swizzle phase
                         // follows the absolute shared-memory address, so a start at any 128-byte row needs no base offset.
                         uint32_t b_lo_res = lo_of(bres_base + static_cast<uint32_t>(hc) * b_kb_bytes);
                         uint32_t row_lo = lo_of(halo_base + static_cast<uint32_t>(mma_hs) * halo_bytes);
-                        for (int tr = 0; ok && tr < p.R; ++tr) {
+#pragma unroll
+                        for (int tr = 0; tr < 3; ++tr) {        // halo mode is 3x3 only: straight-line code for the 9 taps
                             uint32_t a_lo = row_lo;
-                            for (int ts = 0; ts < p.S; ++ts) {
+#pragma unroll
+                            for (int ts = 0; ts < 3; ++ts) {
                                 uint32_t b_lo = b_lo_res;
                                 if (!p.bres) {
-                                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-                                        atomicExch(p.status, STATUS_WAIT_MMA);
-                                        ok = false;
-                                        break;
-                                    }
+                                    if (!st_ready) failed |= !mbar_wait(full_bar(stage), phase, abort_flag);
                                     tc_fence_after();
+                                    const bool wrap = stage + 1 == p.stages;
+                                    st_ready = mbar_test(full_bar(wrap ? 0 : stage + 1), wrap ? phase ^ 1u : phase);
                                     b_lo = st_lo;
                                 }
+                                if (tr == 2 && ts == 0) {     // before the last row of taps: look at the next patch / accumulator
+                                    const bool hwrap = mma_hs + 1 == p.nh;
+                                    h_ready = mbar_test(hfull_bar(hwrap ? 0 : mma_hs + 1), hwrap ? mma_hphase ^ 1u : mma_hphase);
+                                    if (hc == p.cchunks - 1)
+                                        acc_ready = mbar_test(tempty_bar(acc_next), ((acc_phase >> acc_next) & 1u) ^ 1u);
+                                }
                                 umma_f16_kblock(d_tmem, a_lo, hi_halo, b_lo, hi128, idesc, static_cast<uint32_t>((hc | tr | ts) != 0));
-#ifdef FVM_CONV_TRACE
-                                if (hc == 0) { const int tq = tr * 3 + ts; if (tq == 0) TRACE(1, it, 1); else if (tq < 6) TRACE(1, it, 2 + tq); }
-#endif
                                 if (!p.bres) {
                                     umma_commit(empty_bar(stage));
-                                    next_stage();
+                                    NEXT_STAGE();
                                 }
                                 a_lo += static_cast<uint32_t>(p.dw) * 8u;                          // next tap: dw pixels of 128 B
                                 b_lo_res += static_cast<uint32_t>(p.cchunks) * (b_kb_bytes >> 4);  // resident: next tap's block
@@ -571,18 +588,20 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         umma_commit(hempty_bar(mma_hs));     // the staged patch is free once these MMAs have read it
                         if (++mma_hs == p.nh) { mma_hs = 0; mma_hphase ^= 1u; }
                     }
-                    if (ok) umma_commit(tfull_bar(acc));
+                    umma_commit(tfull_bar(acc));
                     TRACE(1, it, 2);
                     continue;
                 }
                 uint32_t bres_lo = lo_of(bres_base);
                 for (int kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-                        atomicExch(p.status, STATUS_WAIT_MMA);
-                        ok = false;
-                        break;
-                    }
+                    if (!st_ready) failed |= !mbar_wait(full_bar(stage), phase, abort_flag);
                     tc_fence_after();
+                    {
+                        const bool wrap = stage + 1 == p.stages;
+                        st_ready = mbar_test(full_bar(wrap ? 0 : stage + 1), wrap ? phase ^ 1u : phase);
+                    }
+                    if (kb == p.kblocks - 1)
+                        acc_ready = mbar_test(tempty_bar(acc_next), ((acc_phase >> acc_next) & 1u) ^ 1u);
                     if (kb == 0) TRACE(1, it, 1);
                     const uint32_t a_src = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     if (p.tapk == 16) {
@@ -598,11 +617,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                          (kb | k) != 0 ? 1u : 0u);
                             }
                         }
-                        umma_commit(empty_bar(stage));
-                        next_stage();
-                        continue;
-                    }
-                    if (p.tapk) {
+                    } else if (p.tapk) {
                         // K = 16 spans two taps: the two 16-byte K halves are one tap block apart (LBO); 8-row groups
                         // are 128 bytes apart (SBO); no swizzle
                         for (int mt = 0; mt < p.mt; ++mt) {
@@ -618,25 +633,23 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                          (kb | k) != 0 ? 1u : 0u);
                             }
                         }
-                        umma_commit(empty_bar(stage));
-                        next_stage();
-                        continue;
+                    } else {
+                        const uint32_t b_lo = p.bres ? bres_lo : st_lo + (a_stage_bytes >> 4);
+                        bres_lo += b_kb_bytes >> 4;
+                        // sub-tile mt: its own 128 rows of A, the shared B tile, accumulator columns [mt*BN, (mt+1)*BN)
+                        for (int mt = 0; mt < p.mt; ++mt)
+                            umma_f16_kblock(d_tmem + static_cast<uint32_t>(mt * p.BN),
+                                            st_lo + static_cast<uint32_t>(mt) * (A_STAGE_BYTES >> 4), hi128, b_lo, hi128, idesc,
+                                            static_cast<uint32_t>(kb != 0));
                     }
-                    const uint32_t b_lo = p.bres ? bres_lo : st_lo + (a_stage_bytes >> 4);
-                    bres_lo += b_kb_bytes >> 4;
-                    // sub-tile mt: its own 128 rows of A, the shared B tile, accumulator columns [mt*BN, (mt+1)*BN)
-                    for (int mt = 0; mt < p.mt; ++mt)
-                        umma_f16_kblock(d_tmem + static_cast<uint32_t>(mt * p.BN),
-                                        st_lo + static_cast<uint32_t>(mt) * (A_STAGE_BYTES >> 4), hi128, b_lo, hi128, idesc,
-                                        static_cast<uint32_t>(kb != 0));
-                    if (kb == 0) TRACE(1, it, 3);
                     umma_commit(empty_bar(stage));   // frees the stage once these MMAs have read it
-                    if (kb == 0) TRACE(1, it, 4);
-                    next_stage();
+                    NEXT_STAGE();
                 }
-                if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+                umma_commit(tfull_bar(acc));  // accumulator complete
                 TRACE(1, it, 2);
             }
+#undef NEXT_STAGE
+            if (failed) atomicExch(p.status, STATUS_WAIT_MMA);
         }
         __syncwarp();
     } else if (warp < STORE_WARP) {

@@ -46,6 +46,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return done;
 }
+// Non-blocking test of a phase (mbarrier.test_wait): used to look ahead at the barrier of the next step while the
+// current one is being issued, so that the round trip to shared memory is off the critical path.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
 // Bounded wait. `abort_flag` is a word in shared memory shared by all roles of the CTA: the first role that gives up
 // sets it (and the caller records a status code); the other roles see it on their next poll and leave too.
 // BACKOFF_NS > 0 puts the warp to sleep between polls: many-lane waiters (epilogue warps) then leave the issue slots
@@ -53,6 +68,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 template <int BACKOFF_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;      // another wait of this CTA already gave up: do not wait again
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     for (;;) {
