@@ -116,6 +116,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "fvm_se_scale_f16": ([_P] * 3 + [_I] * 3 + [_P], _I),
         "fvm_layernorm_cl_f16": ([_P] * 4 + [_L, _I, _F, _L, _L, _P], _I),
         "fvm_input_nhwc8_f32": ([_P] * 2 + [_I] * 4 + [_P], _I),
+        "fvm_input_nhwc8_split_f32": ([_P] * 2 + [_I] * 4 + [_P], _I),
+        "fvm_stem_conv_s2_f16": ([_P] * 4 + [_I] * 8 + [_L, _I, _P], _I),
         "fvm_bias_act_f16": ([_P] * 3 + [_L, _I, _I, _P], _I),
         "fvm_affine_act_f16": ([_P] * 4 + [_L, _I, _L, _L, _I, _P], _I),
         "fvm_add_act_f16": ([_P] * 3 + [_L, _I, _P], _I),
@@ -138,5 +140,6 @@ OPTIONAL_SIGNATURES: dict = {}
 EXPORTED = ["fvm_init", "fvm_query", "fvm_last_status", "fvm_conv2d_f16", "fvm_conv2d_f16_tile", "fvm_conv2d_f16_pad", "fvm_dwconv_f16", "fvm_maxpool_f16",
             "fvm_avgpool_f16", "fvm_gap_scratch_floats", "fvm_global_avgpool_f16", "fvm_global_avgpool_f16_noalloc",
             "fvm_global_avgpool_f16_noalloc_max_floats", "fvm_se_gate_f16",
-            "fvm_se_scale_f16", "fvm_layernorm_cl_f16", "fvm_input_nhwc8_f32", "fvm_bias_act_f16",
+            "fvm_se_scale_f16", "fvm_layernorm_cl_f16", "fvm_input_nhwc8_f32", "fvm_input_nhwc8_split_f32",
+            "fvm_stem_conv_s2_f16", "fvm_bias_act_f16",
             "fvm_affine_act_f16", "fvm_add_act_f16", "fvm_bilinear_f16", "fvm_up_argmax_f16"]

@@ -72,7 +72,7 @@ def build(name: str, tier: str = "cuda-kernels", spec=None, device: str = "cuda"
     net = clf_fast.compile_model(up).to(device)
     if model.startswith("resnet"):
         def raw(x):
-            return net.trunk(ops.input_nhwc8(x)).float().contiguous()
+            return net.trunk(x).float().contiguous()
     else:
         def raw(x):
             return net.features(x).float().contiguous()

@@ -62,7 +62,8 @@ class ResNetTrunk(nn.Module):
         self.out_channels = self.blocks[-1]["convs"][-1].out_channels
 
     def forward(self, x: torch.Tensor, want_stage3: bool = False):
-        x = self.stem(x)
+        # fp32 NCHW image batch (or an fp16 NHWC8 tensor: the reference's clf::input_nhwc8 output)
+        x = self.stem.forward_image(x) if x.dtype == torch.float32 else self.stem(x)
         k, s, p, ceil = self.pool
         x = ops.maxpool(x, k, s, p, ceil)
         aux = None
@@ -86,7 +87,6 @@ class B200ResNet(nn.Module):
         self.num_classes = m.fc.out_features
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = ops.input_nhwc8(x)
         x = self.trunk(x)
         g = ops.global_avgpool(x)
         y = self.fc(g)
@@ -151,8 +151,7 @@ class B200EfficientNet(nn.Module):
         self.num_classes = lin.out_features
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = ops.input_nhwc8(x)
-        x = self.stem(x)
+        x = self.stem.forward_image(x)
         for blk in self.blocks:
             x = blk(x)
         x = self.head(x)

@@ -94,3 +94,9 @@ extern "C" int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias
     return conv2d_launch(x, w, bias, res, scale, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act,
                          tile_n, ph_hi, pw_hi, static_cast<cudaStream_t>(stream));
 }
+
+// Stride-2 stem on the column-parity-split 8-channel input (see stem_s2_launch).
+extern "C" int fvm_stem_conv_s2_f16(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K,
+                                    int R, int S, int ph, int pw, long long ldy, int act, void* stream) {
+    return stem_s2_launch(x, w, bias, y, N, H, W, K, R, S, ph, pw, ldy, act, static_cast<cudaStream_t>(stream));
+}

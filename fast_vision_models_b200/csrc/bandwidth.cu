@@ -56,6 +56,24 @@ __global__ void input_nhwc8_kernel(const float* __restrict__ x, __half* __restri
     stg16(y + i * 8, from_f8(f));
 }
 
+// The same conversion into two column-parity planes per image row: y[n][h][w & 1][w >> 1][c] (W even). A stride-2
+// convolution then reads consecutive output columns from consecutive plane columns (see the stem mode of the conv kernel).
+__global__ void input_nhwc8_split_kernel(const float* __restrict__ x, __half* __restrict__ y, int C, int W, long long HW,
+                                         long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / HW;
+    const long long hw = i - n * HW;
+    const long long row = hw / W;
+    const int w = static_cast<int>(hw - row * W);
+    const float* src = x + n * C * HW + hw;
+    float f[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) f[c] = c < C ? __ldg(src + c * HW) : 0.f;
+    const long long o = (n * HW + row * W) + static_cast<long long>(w & 1) * (W >> 1) + (w >> 1);
+    stg16(y + o * 8, from_f8(f));
+}
+
 // ------------------------------------------------------------------------------------------- max / avg pool
 // reference: maxpool_nhwc8 (fused_conv.cu:338-356): -inf padding, half2 max over in-image taps only.
 __global__ void maxpool_kernel(const __half* __restrict__ x, __half* __restrict__ y, int H, int W, int C, int kh, int kw,
@@ -491,6 +509,14 @@ extern "C" int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H,
     const long long HW = static_cast<long long>(H) * W, total = HW * N;
     input_nhwc8_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x, static_cast<__half*>(y), C, HW, total);
+    FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
+    if (!x || !y || N <= 0 || C <= 0 || C > 8 || H <= 0 || W <= 0 || (W & 1) || !aligned16(y)) return FVM_ERR_ARG;
+    const long long HW = static_cast<long long>(H) * W, total = HW * N;
+    input_nhwc8_split_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, static_cast<__half*>(y), C, W, HW, total);
     FVM_LAUNCH_CHECK();
 }
 

@@ -6,9 +6,11 @@
 // Arithmetic contract of the reference op this replaces: classification/fast/csrc/fused_conv.cu:81-99 (epilogue order
 // bias -> residual -> activation -> single fp16 rounding); the reference accumulates in fp16 (:50), this kernel in fp32.
 //
-// Roles (19 warps): warp 0 = TMA producer (lane 0 arms the barriers, several lanes issue bulk loads), warp 1 = TMEM
-// owner + MMA issuer (one lane), warps 2..17 = four epilogue groups of 4 warps (TMEM lane group = warp % 4) that finish
-// alternate tiles, warp 18 = TMA store issuer (one lane).
+// Roles (19 warps): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..17 = four epilogue groups of 4
+// warps (TMEM lane group = warp % 4) that finish alternate tiles, warp 18 = TMA store issuer. The three single-thread
+// roles run in one lane chosen by elect.sync, with control flow that depends on kernel parameters only: the compiler
+// then keeps their counters and descriptors in uniform registers, which is what tcgen05.mma / TMA instructions read
+// (measured: about 50 cycles per issued MMA against about 120 under `if (lane == 0)`).
 //   A tiles: 128 output pixels x 64 input channels per k-block. 1x1 stride-1 convs read them with a 2-D tiled tensor
 //            map over [M, C]; every other shape uses an im2col-mode tensor map over the NHWC activation, so padding,
 //            stride and dilation are resolved by the TMA unit and out-of-image taps arrive as zeros.
@@ -17,6 +19,10 @@
 //   Two to four accumulator buffers in TMEM let the epilogues of earlier tiles overlap the main loop of the next.
 //   The residual tile is prefetched by TMA into a swizzled staging buffer, combined in place with the accumulator,
 //   and the finished tile leaves by TMA store: the epilogue threads never touch global memory except for the bias.
+//   Halo mode (3x3, stride 1): a tile is a 16 x 8 patch of output pixels; its input patch with border is staged once
+//   per 64 channels and the nine taps are MMA operands that start at different rows of that patch.
+//   Stem mode (stride 2, 8-channel input stored as two column-parity planes per image row): the same idea without
+//   swizzle; one MMA covers two vertically adjacent taps.
 // No cluster launch and no multicast: every CTA issues its own loads.
 #include <cuda.h>
 
@@ -69,7 +75,12 @@ struct ConvParams {
     int taps;      // R * S
     int halo;      // 1: 3x3 stride-1 'halo' mode: a tile is a 16x8 pixel patch of one image; its input patch (+ border) is
                    // staged once per 64 channels and the 9 taps are shifted views of it (9x fewer L2 reads than im2col)
+                   // 2: stride-2 stem over an 8-channel input stored as two column-parity planes per image row: the
+                   // input patch of a 16x8 output patch is staged once, every filter tap is a shifted view of it
     int halo_rows, nh, tiles_x, tiles_y;   // staged rows (16 + 2*dilation), halo buffers, patches per image row / column
+    uint32_t hbytes, htx;                  // staged-patch buffer stride / bytes per load
+    int stem_taps, stem_xlo;               // stem mode: weight taps held (R rounded up to even, times S); leftmost plane column
+    uint32_t stem_prow;                    // stem mode: bytes per staged input row (two planes)
     FastDiv div_txy, div_tx;
 #ifdef FVM_CONV_TRACE
     int dbg;
@@ -265,10 +276,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // tap-packed mode: all weights of the (single) n-tile stay resident: one [BN x 16 B] block per tap
     const uint32_t tap_b_bytes = static_cast<uint32_t>(p.BN * p.tapk * 2);
     const uint32_t bres_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+    const uint32_t stem_b_bytes = static_cast<uint32_t>(p.BN) * 16u;          // stem mode: one tap of the weights, [BN][8]
     const uint32_t bres_bytes = p.tapk ? static_cast<uint32_t>(p.kblocks * tpk) * tap_b_bytes
-                                       : (p.bres ? static_cast<uint32_t>(p.kblocks) * b_kb_bytes : 0u);
+                                : p.halo == 2 ? static_cast<uint32_t>(p.stem_taps) * stem_b_bytes
+                                : (p.bres ? static_cast<uint32_t>(p.kblocks) * b_kb_bytes : 0u);
     const uint32_t halo_base = bres_base + bres_bytes;
-    const uint32_t halo_bytes = p.halo ? static_cast<uint32_t>(p.halo_rows * HALO_PITCH) * 128u : 0u;   // multiple of 2 KB
+    const uint32_t halo_bytes = p.hbytes;
     const uint32_t epi_base = halo_base + static_cast<uint32_t>(p.nh) * halo_bytes;
     const uint32_t epi_bytes = static_cast<uint32_t>(p.mt * p.nsub) * SUB_BYTES;   // staging: [mt][nsub] sub-tiles
     const uint32_t bar_base = epi_base + static_cast<uint32_t>(p.nepi) * epi_bytes;
@@ -355,7 +368,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tma_load_3d(bres_base + static_cast<uint32_t>(t) * tap_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
             }
             int m_tile, n_tile;
-            if (p.bres && tile_at(p, 0, m_tile, n_tile)) {
+            if (p.halo == 2) {
+                // stem mode: every tap's [BN][8] block (taps past R*S are out of bounds of the weight tensor: zeros)
+                mbar_expect_tx(bres_full_bar, bres_bytes);
+                for (int t = 0; t < p.stem_taps; ++t)
+                    tma_load_3d(bres_base + static_cast<uint32_t>(t) * stem_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
+            } else if (p.bres && tile_at(p, 0, m_tile, n_tile)) {
                 // this CTA's weight tile, all k-blocks, once: k-block kb = (tap kb / cchunks, channels (kb % cchunks)*64)
                 mbar_expect_tx(bres_full_bar, bres_bytes);
                 int tp = 0, cc = 0;
@@ -409,9 +427,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             ok = false;
                             break;
                         }
-                        mbar_expect_tx(hfull_bar(hs), halo_bytes);
-                        tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), hc * BK,
-                                    hx0 - p.pw, hy0 - p.ph, himg);
+                        mbar_expect_tx(hfull_bar(hs), p.htx);
+                        if (p.halo == 2)     // (channel, plane column, plane, input row, image)
+                            tma_load_5d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), 0,
+                                        hx0 + p.stem_xlo, 0, 2 * hy0 - p.ph, himg);
+                        else
+                            tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), hc * BK,
+                                        hx0 - p.pw, hy0 - p.ph, himg);
                         if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
                         if (p.bres) continue;
                         for (int tp = 0; tp < p.taps; ++tp) {
@@ -547,6 +569,42 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 tc_fence_after();
                 TRACE(1, it, 0);
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
+                if (p.halo == 2) {
+                    // Stem mode. Output pixel (oy, ox) of the patch, tap (r, s): input row 2*oy + r, plane (s - pw) & 1,
+                    // plane column ox + (s - pw - plane) / 2. One MMA (K = 16) covers taps (r, s) and (r + 1, s): its two
+                    // K halves are one staged row apart (LBO), its 8-pixel groups (one output row each) two staged rows
+                    // (SBO); no swizzle. Weights: tap blocks [BN][8]; the K halves are S blocks apart.
+                    if (!h_ready) failed |= !mbar_wait(hfull_bar(mma_hs), mma_hphase, abort_flag);
+                    tc_fence_after();
+                    {
+                        const bool hwrap = mma_hs + 1 == p.nh;
+                        h_ready = mbar_test(hfull_bar(hwrap ? 0 : mma_hs + 1), hwrap ? mma_hphase ^ 1u : mma_hphase);
+                        acc_ready = mbar_test(tempty_bar(acc_next), ((acc_phase >> acc_next) & 1u) ^ 1u);
+                    }
+                    const uint32_t prow16 = p.stem_prow >> 4, pplane16 = p.stem_prow >> 5;
+                    const uint32_t a_hi = (2u * prow16) | (1u << 14);                 // SBO, descriptor version
+                    const uint32_t b_hi = (128u >> 4) | (1u << 14);
+                    const uint32_t a_base = (((halo_base + static_cast<uint32_t>(mma_hs) * halo_bytes) & 0x3ffffu) >> 4) | (prow16 << 16);
+                    const uint32_t b_base = ((bres_base & 0x3ffffu) >> 4) | ((static_cast<uint32_t>(p.S) * (stem_b_bytes >> 4)) << 16);
+                    const int rpairs = p.stem_taps / (2 * p.S);
+                    uint32_t first = 0;
+                    for (int ts = 0; ts < p.S; ++ts) {
+                        const int d = ts - p.pw, par = d & 1;
+                        uint32_t a_lo = a_base + static_cast<uint32_t>(par) * pplane16 + static_cast<uint32_t>(((d - par) >> 1) - p.stem_xlo);
+                        uint32_t b_lo = b_base + static_cast<uint32_t>(ts) * (stem_b_bytes >> 4);
+                        for (int rp = 0; rp < rpairs; ++rp) {
+                            umma_f16_words(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, first);
+                            first = 1;
+                            a_lo += 2u * prow16;
+                            b_lo += 2u * static_cast<uint32_t>(p.S) * (stem_b_bytes >> 4);
+                        }
+                    }
+                    umma_commit(hempty_bar(mma_hs));
+                    if (++mma_hs == p.nh) { mma_hs = 0; mma_hphase ^= 1u; }
+                    umma_commit(tfull_bar(acc));
+                    TRACE(1, it, 2);
+                    continue;
+                }
                 if (p.halo) {
                     for (int hc = 0; hc < p.cchunks; ++hc) {
                         if (!h_ready) failed |= !mbar_wait(hfull_bar(mma_hs), mma_hphase, abort_flag);
@@ -741,7 +799,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------------------------------------------ store warp
         if (elect_one()) {
             uint32_t e_phase = 0;   // one parity bit per staging buffer
-            int e = 0;
+            int e = 0, e_prev = -1;
+            const bool defer = p.nepi >= 3;
             bool ok = true;
             int m_tile, n_tile;
             for (int sit = 0; ok && tile_at(p, sit, m_tile, n_tile); ++sit) {
@@ -772,9 +831,19 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      n0 + sub * 64, m0 + mt * BM);
                 tma_store_commit();
                 TRACE(6, sit, 2);
-                tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
+                if (defer) {
+                    // with three or more staging buffers the release trails by one tile: this thread does not sit
+                    // out the read-out of the store it has just issued
+                    if (e_prev >= 0) {
+                        tma_store_wait_read_but_one();
+                        mbar_arrive(epi_free_bar(e_prev));
+                    }
+                    e_prev = e;
+                } else {
+                    tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
+                    mbar_arrive(epi_free_bar(e));
+                }
                 TRACE(6, sit, 3);
-                mbar_arrive(epi_free_bar(e));
                 if (++e == p.nepi) e = 0;
             }
             // Shared memory must outlive the stores' reads of it; the writes themselves complete asynchronously and are
@@ -910,6 +979,126 @@ static int pick_bn(int m_tiles, int K, int kblocks, bool tapk, int sms) {
     return best;
 }
 
+static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_r,
+                              const CUtensorMap& tmap_y, const ConvParams& p, int grid, size_t smem, cudaStream_t stream);
+
+// Stride-2 stem over an 8-channel input held as two column-parity planes per image row (x: [N][H][2][W/2][8], the
+// layout fvm_input_nhwc8_split_f32 writes): y = act(conv(x, w) + bias), w [K][R][S][8], symmetric padding, no residual.
+int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K, int R, int S,
+                   int ph, int pw, long long ldy, int act, cudaStream_t stream) {
+    DeviceState* st = device_state();
+    if (!st) return FVM_ERR_SETUP;
+    if (!x || !w || !y) return FVM_ERR_ARG;
+    if (N <= 0 || H <= 0 || W <= 0 || (W & 1) || K <= 0 || (K & 7) || K > 256 || R <= 0 || S <= 0 || R > 8 || S > 8)
+        return FVM_ERR_ARG;
+    if (ph < 0 || pw < 0 || ph >= R || pw >= S || (ldy & 7) || ldy < K || act < 0 || act > 6) return FVM_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+        (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(bias) & 15))
+        return FVM_ERR_ARG;
+    const int P = (H + 2 * ph - R) / 2 + 1, Q = (W + 2 * pw - S) / 2 + 1;
+    if (H + 2 * ph < R || W + 2 * pw < S || P <= 0 || Q <= 0) return FVM_ERR_ARG;
+    const long long M_ll = static_cast<long long>(N) * P * Q;
+    if (M_ll > 0x7fffff00ll) return FVM_ERR_ARG;
+
+    ConvParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = static_cast<int>(M_ll);
+    p.K = K; p.C = 8; p.R = R; p.S = S; p.P = P; p.Q = Q;
+    p.sh = p.sw = 2; p.ph = ph; p.pw = pw; p.dh = p.dw = 1;
+    p.cchunks = 1;
+    p.taps = R * S;
+    const int RP = (R + 1) & ~1;                   // rows of taps, rounded up to pairs (the extra row has zero weights)
+    p.stem_taps = RP * S;
+    p.kblocks = p.stem_taps / 2;                  // MMAs per tile (reporting only)
+    p.BN = (K + 31) / 32 * 32;
+    p.n_tiles = 1;
+    p.div_ntiles = fastdiv_init(1);
+    p.nsub = (p.BN + 63) / 64;
+    p.mt = 1;
+    p.halo = 2;
+    p.bres = 1;
+    p.tiles_x = (Q + HALO_TW - 1) / HALO_TW;
+    p.tiles_y = (P + HALO_TH - 1) / HALO_TH;
+    p.div_txy = fastdiv_init(static_cast<uint32_t>(p.tiles_x * p.tiles_y));
+    p.div_tx = fastdiv_init(static_cast<uint32_t>(p.tiles_x));
+    p.div_pq = fastdiv_init(static_cast<uint32_t>(P) * Q);
+    p.div_q = fastdiv_init(static_cast<uint32_t>(Q));
+    p.m_tiles = N * p.tiles_x * p.tiles_y;
+    // plane columns a tap column s reaches: (s - pw - parity) / 2 relative to the output column
+    auto xoff = [&](int s_) { const int d = s_ - pw, par = d & 1; return (d - par) / 2; };
+    p.stem_xlo = xoff(0);
+    const int PW = (HALO_TW + xoff(S - 1) - p.stem_xlo + 7) & ~7;      // staged plane columns (rows of whole 128 bytes)
+    const int PR = 2 * (HALO_TH - 1) + RP;                  // staged input rows (incl. the zero-weight tap row)
+    p.stem_prow = static_cast<uint32_t>(2 * PW * 16);
+    p.htx = static_cast<uint32_t>(PR) * p.stem_prow;
+    p.hbytes = (p.htx + 127u) & ~127u;
+    p.nh = 3;
+    p.act = act;
+    p.has_res = 0;
+    p.bias = static_cast<const __half*>(bias);
+    p.scale = nullptr;
+    p.status = st->status_dev;
+    p.bias_elems = p.BN;
+    p.acc_stride = 32;
+    while (p.acc_stride < p.BN) p.acc_stride <<= 1;
+    p.nacc = 512 / p.acc_stride >= 4 ? 4 : 2;
+    p.tmem_cols = p.nacc * p.acc_stride;
+    p.stages = 2;                                  // unused: the stages are empty in this mode
+    const uint32_t bres_bytes = static_cast<uint32_t>(p.stem_taps) * p.BN * 16u;
+    const uint32_t epi_bytes = static_cast<uint32_t>(p.nsub) * SUB_BYTES;
+    uint32_t fixed = 1024 + 8 * NUM_BARRIERS + MISC_BYTES + ((static_cast<uint32_t>(p.BN) * 4 + 15u) & ~15u) +
+                     bres_bytes + static_cast<uint32_t>(p.nh) * p.hbytes;
+    if (fixed + 2 * epi_bytes > 227u * 1024) {       // wide tiles: two staged patches instead of three
+        p.nh = 2;
+        fixed -= p.hbytes;
+    }
+    p.nepi = MAX_EPI;
+    while (p.nepi > 2 && fixed + static_cast<uint32_t>(p.nepi) * epi_bytes > 227u * 1024) --p.nepi;
+    if (fixed + static_cast<uint32_t>(p.nepi) * epi_bytes > 227u * 1024) return FVM_ERR_ARG;
+    if (p.nepi < p.nacc) p.nacc = 2, p.tmem_cols = 2 * p.acc_stride;
+    size_t smem = fixed + static_cast<size_t>(p.nepi) * epi_bytes;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+
+    CUtensorMap tmap_a, tmap_b, tmap_y;
+    {
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(Q), static_cast<cuuint64_t>(P),
+                              static_cast<cuuint64_t>(N)};
+        cuuint32_t box[4] = {64, HALO_TW, HALO_TH, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        cuuint64_t ystr[3] = {static_cast<cuuint64_t>(ldy) * 2, static_cast<cuuint64_t>(Q) * ldy * 2,
+                              static_cast<cuuint64_t>(P) * Q * ldy * 2};
+        if (g_encode_tiled(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, y, dims, ystr, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FVM_ERR_TMAP;
+    }
+    {
+        // weights [K][R*S][8]: one tap of all output channels per load, 16-byte rows, no swizzle
+        cuuint64_t dims[3] = {8, static_cast<cuuint64_t>(R * S), static_cast<cuuint64_t>(K)};
+        cuuint64_t strides[2] = {16, static_cast<cuuint64_t>(R) * S * 16};
+        cuuint32_t box[3] = {8, 1, static_cast<cuuint32_t>(p.BN)};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (g_encode_tiled(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FVM_ERR_TMAP;
+    }
+    {
+        // input as (channel 8, plane column W/2, plane 2, row H, image N); a box = the input of one output patch
+        cuuint64_t dims[5] = {8, static_cast<cuuint64_t>(W / 2), 2, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(N)};
+        cuuint64_t strides[4] = {16, static_cast<cuuint64_t>(W / 2) * 16, static_cast<cuuint64_t>(W) * 16,
+                                 static_cast<cuuint64_t>(H) * W * 16};
+        cuuint32_t box[5] = {8, static_cast<cuuint32_t>(PW), 2, static_cast<cuuint32_t>(PR), 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        if (g_encode_tiled(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(x), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FVM_ERR_TMAP;
+    }
+    int grid = p.m_tiles < st->sms ? p.m_tiles : st->sms;
+    return launch_conv_kernel(tmap_a, tmap_b, tmap_y, tmap_y, p, grid, smem, stream);
+}
+
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
@@ -981,6 +1170,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
             p.div_tx = fastdiv_init(static_cast<uint32_t>(tx));
             p.m_tiles = N * ty * tx;
             halo_bytes = static_cast<uint32_t>(p.halo_rows * HALO_PITCH) * 128u;
+            p.hbytes = p.htx = halo_bytes;
         }
     }
     if (force_halo == 1 && !p.halo) return FVM_ERR_ARG;
@@ -1151,6 +1341,11 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         if (cta_per_n > p.m_tiles) cta_per_n = p.m_tiles;
         grid = cta_per_n * p.n_tiles;
     }
+    return launch_conv_kernel(tmap_a, tmap_b, tmap_r, tmap_y, p, grid, smem, stream);
+}
+
+static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_r,
+                              const CUtensorMap& tmap_y, const ConvParams& p, int grid, size_t smem, cudaStream_t stream) {
     // Programmatic dependent launch: the grid may start (set-up only) while the previous kernel of the stream drains;
     // the kernel itself waits (griddepcontrol.wait) before it touches activations or outputs.
     static int use_pdl = [] { const char* v = getenv("FVM_B200_PDL"); return (v && v[0] == '0') ? 0 : 1; }();

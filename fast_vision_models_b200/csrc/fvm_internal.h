@@ -19,6 +19,8 @@ DeviceState* device_state();
 void count_launch();
 
 int conv_host_init();
+int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K, int R, int S,
+                   int ph, int pw, long long ldy, int act, cudaStream_t stream);
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,

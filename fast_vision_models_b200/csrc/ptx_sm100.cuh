@@ -129,6 +129,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
 // im2col-mode load of NHWC activations: coordinates (c, w, h, n) of the first pixel's filter-window origin, plus the
 // filter tap offset (off_w, off_h) in input pixels (tap index times dilation).
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* desc, uint32_t bar, int c, int w, int h,
@@ -155,6 +161,9 @@ __device__ __forceinline__ void tma_store_4d(const void* desc, uint32_t src, int
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until every committed bulk store of this thread has finished READING shared memory (the source may be reused).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// The same with one committed group still allowed to be reading: the store of the previous tile is then off the
+// critical path of the thread that issues the stores.
+__device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // Orders this thread's generic-proxy writes to shared memory before later async-proxy (TMA) reads of them.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -251,6 +260,21 @@ __device__ __forceinline__ uint32_t elect_one() {
         "}\n"
         : "=r"(pred));
     return pred;
+}
+// One tcgen05.mma with descriptors given as (low word, high word). Call from the single issuing lane.
+__device__ __forceinline__ void umma_f16_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 // The four tcgen05.mma of one 64-half k-block (K = 16 each) as one instruction sequence. Descriptors come as (low word,
 // high word): the start address lives in the low word, so the steps along K (+32 bytes = +2) are 32-bit adds. The first

@@ -15,6 +15,7 @@ from . import fold, ops
 
 AUTOTUNE = os.environ.get("FVM_B200_AUTOTUNE", "1") != "0"
 PAIR_STEMS = os.environ.get("FVM_B200_PAIR_STEMS", "1") != "0"   # run RGB stems over column pairs (16-channel taps)   # kill switch, in the style of the reference's CLF_* variables
+SPLIT_STEMS = os.environ.get("FVM_B200_SPLIT_STEMS", "1") != "0"   # stride-2 RGB stems on column-parity planes
 
 _ACT_CODES = {
     nn.ReLU: ops.ACT_RELU, nn.ReLU6: ops.ACT_RELU6, nn.SiLU: ops.ACT_SILU, nn.Hardswish: ops.ACT_HARDSWISH,
@@ -123,6 +124,18 @@ class FusedConv(nn.Module):
                     best, best_ms = c, ms
         self._tiles[key] = best
         return best
+
+    def forward_image(self, x: torch.Tensor) -> torch.Tensor:
+        """The stem applied to an fp32 NCHW image batch (at most 8 channels). A stride-2 stem with an even image width
+        runs on the column-parity-split input (`ops.input_nhwc8_split` + `ops.stem_conv_s2`), where the input patch of
+        each output tile is staged once; anything else converts to NHWC8 (`ops.input_nhwc8`, the reference's
+        clf::input_nhwc8) and takes the general convolution."""
+        K, C, R, S = self.w.shape
+        if (SPLIT_STEMS and C == 8 and self.stride == (2, 2) and self.dilation == (1, 1) and self.scale is None
+                and R <= 8 and S <= 8 and K <= 256 and self.padding[0] < R and self.padding[1] < S
+                and x.shape[3] % 2 == 0 and (R + R % 2) * S * ((K + 31) // 32 * 32) * 16 <= 96 * 1024):
+            return ops.stem_conv_s2(ops.input_nhwc8_split(x), self.w, self.b, self.padding, self.act)
+        return self.forward(ops.input_nhwc8(x))
 
     @classmethod
     def from_conv_bn(cls, conv: nn.Conv2d, bn: Optional[nn.Module] = None, act: int = 0, **kw) -> "FusedConv":

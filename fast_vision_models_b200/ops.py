@@ -373,6 +373,44 @@ def input_nhwc8(x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def input_nhwc8_split(x: torch.Tensor) -> torch.Tensor:
+    """input_nhwc8 into two column-parity planes per image row: returns fp16 [N, H, 2, W/2, 8] with
+    out[n, h, w & 1, w >> 1, c] = x[n, c, h, w] (channels zero-padded to 8). Input layout of `stem_conv_s2`."""
+    init(x.device)
+    if not x.is_cuda or x.dtype != torch.float32:
+        raise FvmError("input_nhwc8_split: expected an fp32 CUDA tensor")
+    x = x.contiguous()
+    N, C, H, W = x.shape
+    if W % 2:
+        raise FvmError("input_nhwc8_split: the width must be even")
+    y = torch.empty((N, H, 2, W // 2, 8), dtype=torch.float16, device=x.device)
+    _check(lib().fvm_input_nhwc8_split_f32(x.data_ptr(), y.data_ptr(), N, C, H, W, _stream()), "input_nhwc8_split_f32")
+    return y
+
+
+def stem_conv_s2(xs: torch.Tensor, w: torch.Tensor, bias, padding, act: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Stride-2 stem on the split input: xs [N, H, 2, W/2, 8] (from `input_nhwc8_split`), w [K, 8, R, S] channels-last
+    (the KRSC weights of `conv_fused`), same-sided padding (ph, pw). Returns act(conv + bias) as NHWC fp16."""
+    init(xs.device)
+    if xs.dim() != 5 or xs.shape[2] != 2 or xs.shape[4] != 8 or xs.dtype != torch.float16 or not xs.is_contiguous():
+        raise FvmError("stem_conv_s2: xs must be a contiguous fp16 [N, H, 2, W/2, 8] tensor")
+    N, H, _, Wh, _ = xs.shape
+    W = 2 * Wh
+    K, C, R, S = w.shape
+    if C != 8 or w.dtype != torch.float16 or not w.is_contiguous(memory_format=torch.channels_last):
+        raise FvmError("stem_conv_s2: w must be a channels-last fp16 [K, 8, R, S] tensor")
+    ph, pw = padding
+    P, Q = (H + 2 * ph - R) // 2 + 1, (W + 2 * pw - S) // 2 + 1
+    if out is None:
+        out = empty_nhwc(N, K, P, Q, xs.device)
+    ov, oN, oK, oP, oQ, ldy = nhwc_view(out, "out")
+    if ov is not out or (oN, oK, oP, oQ) != (N, K, P, Q):
+        raise FvmError(f"stem_conv_s2: out must be a channels-last [N,K,P,Q]={N, K, P, Q} tensor or channel slice")
+    _check(lib().fvm_stem_conv_s2_f16(xs.data_ptr(), w.data_ptr(), _ptr(bias), ov.data_ptr(), N, H, W, K, R, S, ph, pw,
+                                      ldy, int(act), _stream()), "stem_conv_s2_f16")
+    return out
+
+
 def bias_act_(y, bias=None, res=None, relu: bool = False) -> torch.Tensor:
     """segx::bias_act_(y, bias?, res?, relu) in place (segmentation/fast/csrc/segx_ops.cu:28-42)."""
     init(y.device)

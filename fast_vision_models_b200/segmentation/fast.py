@@ -45,7 +45,6 @@ class B200DeepLabV3(nn.Module):
 
     def logits_nhwc(self, x: torch.Tensor) -> torch.Tensor:
         """fp32 NCHW image batch -> low-resolution fp16 scores [N, round_up(classes, 8), H/8, W/8] (channels-last)."""
-        x = ops.input_nhwc8(x)
         feat = self.trunk(x)
         N, _, h, w = feat.shape
         C = self.branch_channels

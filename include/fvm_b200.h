@@ -133,6 +133,19 @@ int fvm_layernorm_cl_f16(const void* x, const void* gamma, const void* beta, voi
  * (fused_conv.cu:597-620). */
 int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H, int W, void* stream);
 
+/* The same conversion into two column-parity planes per image row, y[n][h][w & 1][w >> 1][8] (W even): the input
+ * layout of fvm_stem_conv_s2_f16. Same bytes as the NHWC8 tensor, columns regrouped. */
+int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, int H, int W, void* stream);
+
+/* Stride-2 stem convolution on that layout: y[N,P,Q,K] (row stride ldy) = act(conv(x, w) + bias), w [K][R][S][8]
+ * (input channels zero-padded to 8), padding (ph, pw) on both sides, stride 2 in both directions, R, S <= 8,
+ * K % 8 == 0 and K <= 256. Replaces the reference's zero-padded 8-channel stem (classification/fast/fused.py:90-105,
+ * run there through clf::conv_fused, fused_conv.cu:229-300): with the parity planes, consecutive output columns read
+ * consecutive plane columns, so the input patch of a 16 x 8 block of outputs is staged once in shared memory and every
+ * filter tap is a shifted view of it. */
+int fvm_stem_conv_s2_f16(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K, int R,
+                         int S, int ph, int pw, long long ldy, int act, void* stream);
+
 /* In place: y = relu?(y + bias[c] + res) -- replaces segx::bias_act_ (segmentation/fast/csrc/segx_ops.cu:28-42). */
 int fvm_bias_act_f16(void* y, const void* bias, const void* res, long long pixels, int C, int relu, void* stream);
 

@@ -212,6 +212,61 @@ def test_rgb_stem_over_column_pairs_matches_the_plain_stem(case):
     close(y_plain, ref)
 
 
+STEM_CASES = [
+    # N, H, W, K, R, S, pad, act
+    (2, 64, 64, 64, 7, 7, 3, 1),        # ResNet stem
+    (1, 224, 224, 64, 7, 7, 3, 1),      # full-size image: 7 x 14 patches
+    (2, 38, 46, 48, 3, 3, 1, 3),        # EfficientNet stem shape: ragged patches, K below one tile
+    (2, 37, 42, 32, 3, 3, 1, 0),        # odd height
+    (2, 30, 34, 32, 5, 5, 2, 1),
+    (2, 32, 32, 96, 7, 7, 3, 5),        # two 64-channel output boxes
+    (3, 20, 24, 64, 4, 4, 1, 1),        # even filter: no zero-weight tap row
+    (2, 16, 16, 256, 3, 3, 1, 1),       # widest tile
+    (2, 18, 20, 64, 7, 7, 0, 0),        # no padding
+]
+
+
+@pytest.mark.parametrize("case", STEM_CASES)
+def test_stem_conv_on_split_input_matches_oracle_and_plain_conv(case):
+    # the stride-2 stem over column-parity planes: same products and sums as the convolution on the NHWC8 tensor
+    N, H, W, K, Rr, S, pad, act = case
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((N, 3, H, W), generator=g)
+    w = torch.zeros((K, 8, Rr, S))
+    w[:, :3] = torch.randn((K, 3, Rr, S), generator=g) * 0.1
+    w, b = w.half(), gen((K,), 6, 0.1)
+    x8 = ops.input_nhwc8(x.to(DEV))
+    ref = R.conv_fused_ref(x8.cpu(), w, b, None, (pad, pad), (2, 2), act)
+    xs = ops.input_nhwc8_split(x.to(DEV))
+    # the split tensor holds the NHWC8 pixels, even columns first
+    assert torch.equal(xs[:, :, 0], x8.permute(0, 2, 3, 1)[:, :, 0::2]) and torch.equal(xs[:, :, 1], x8.permute(0, 2, 3, 1)[:, :, 1::2])
+    y = ops.stem_conv_s2(xs, cl(w), b.to(DEV), (pad, pad), act)
+    assert ops.last_status() == 0
+    close(y, ref)
+    y_plain = ops.conv_fused(x8, cl(w), b.to(DEV), None, (pad, pad), (2, 2), act)
+    close(y, y_plain)
+
+
+def test_stem_conv_without_bias_into_a_channel_slice_and_bad_arguments():
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn((2, 3, 24, 24), generator=g).to(DEV)
+    w = torch.zeros((32, 8, 3, 3))
+    w[:, :3] = torch.randn((32, 3, 3, 3), generator=g) * 0.1
+    w = cl(w.half())
+    xs = ops.input_nhwc8_split(x)
+    big = ops.empty_nhwc(2, 64, 12, 12, DEV).fill_(7.0)
+    ops.stem_conv_s2(xs, w, None, (1, 1), 0, out=big[:, 16:48])
+    ref = R.conv_fused_ref(ops.input_nhwc8(x).cpu(), w.cpu(), None, None, (1, 1), (2, 2), 0)
+    close(big[:, 16:48], ref)
+    assert (big[:, :16] == 7.0).all() and (big[:, 48:] == 7.0).all()
+    with pytest.raises(ops.FvmError):
+        ops.input_nhwc8_split(torch.randn(1, 3, 8, 9, device=DEV))          # odd width
+    with pytest.raises(ops.FvmError):
+        ops.stem_conv_s2(xs, cl(torch.zeros(32, 8, 9, 9).half()), None, (4, 4), 0)   # filter too large
+    with pytest.raises(ops.FvmError):
+        ops.stem_conv_s2(xs.float(), w, None, (1, 1), 0)
+
+
 def test_conv_no_bias_scale_and_sliced_io():
     # input read from a channel slice, output written into a channel slice of a wider buffer (concat-free ASPP),
     # un-folded LayerScale as an fp32 epilogue scale
