@@ -800,7 +800,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (elect_one()) {
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             int e = 0, e_prev = -1;
-            const bool defer = p.nepi >= 3;
+            const bool defer = false;    // measured on B200: releasing one tile late starves the residual prefetch; kept off
             bool ok = true;
             int m_tile, n_tile;
             for (int sit = 0; ok && tile_at(p, sit, m_tile, n_tile); ++sit) {
