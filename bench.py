@@ -137,6 +137,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-window", type=int, default=0,
+                    help="after warm-up, run this many forwards between cudaProfilerStart/Stop and exit (for a "
+                         "profiler started with --profile-from-start off); prints no bench line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -184,6 +187,15 @@ def main():
     # ---------------------------------------------------------------- value: inputs resident in HBM
     for i in range(warmup):
         y = m.model(xs[i % NBUF])
+    if args.profile_window > 0:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for i in range(args.profile_window):
+            y = m.model(xs[i % NBUF])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profile_window": args.profile_window, "status": ops.last_status()}))
+        return
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()

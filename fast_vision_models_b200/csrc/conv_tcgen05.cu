@@ -344,11 +344,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Everything above touches only this CTA's shared memory / TMEM and constant inputs. From here on the kernel reads
-    // activations and writes outputs, which must wait for the preceding kernels of the stream (programmatic dependent
-    // launch: this grid may have been started while its predecessor was still draining).
+    // Everything above touches only this CTA's shared memory / TMEM. Programmatic dependent launch: this grid may have
+    // been started while its predecessor was still draining, so the two threads that touch activations or outputs
+    // (the producer before its first activation / residual load, the store thread before its first store) wait for
+    // the preceding kernels with griddepcontrol.wait; weights and bias are constants and are fetched before that.
     if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -383,6 +383,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (++cc == p.cchunks) { cc = 0; ++tp; }
                 }
             }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int hs = 0;
             uint32_t hphase = 0;
             for (int pit = 0; ok && tile_at(p, pit, m_tile, n_tile); ++pit) {
@@ -801,6 +802,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             int e = 0, e_prev = -1;
             const bool defer = false;    // measured on B200: releasing one tile late starves the residual prefetch; kept off
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int m_tile, n_tile;
             for (int sit = 0; ok && tile_at(p, sit, m_tile, n_tile); ++sit) {
