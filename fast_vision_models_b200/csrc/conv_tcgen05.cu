@@ -383,6 +383,21 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (++cc == p.cchunks) { cc = 0; ++tp; }
                 }
             }
+            // Streamed weights: the B tiles of the first k-blocks (one per pipeline stage) are requested before the wait
+            // as well; their barriers are armed for the whole stage, the A tiles follow after the wait.
+            int pre = 0;
+            if (!p.tapk && !p.bres && !p.halo) {
+                for (int pit = 0; pre < p.stages && tile_at(p, pit, m_tile, n_tile); ++pit) {
+                    int tap = 0, cc = 0;
+                    for (int kb = 0; kb < p.kblocks && pre < p.stages; ++kb, ++pre) {
+                        mbar_expect_tx(full_bar(pre), stage_bytes);
+                        tma_load_3d(smem_base + static_cast<uint32_t>(pre) * stage_bytes + a_stage_bytes, &tmap_b,
+                                    full_bar(pre), cc * BK, tap, n_tile * p.BN);
+                        if (++cc == p.cchunks) { cc = 0; ++tap; }
+                    }
+                }
+            }
+            int issued = 0;       // k-blocks issued so far (the first `pre` have their barrier armed and B on the way)
             asm volatile("griddepcontrol.wait;" ::: "memory");
             int hs = 0;
             uint32_t hphase = 0;
@@ -462,14 +477,16 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                    const bool armed = issued < pre;      // this stage's barrier and B tile were set up before the wait
+                    ++issued;
+                    if (!armed && !mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         atomicExch(p.status, STATUS_WAIT_PRODUCER);
                         ok = false;
                         break;
                     }
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     const uint32_t b_dst = a_dst + a_stage_bytes;
-                    mbar_expect_tx(full_bar(stage), stage_bytes);
+                    if (!armed) mbar_expect_tx(full_bar(stage), stage_bytes);
                     if (p.tapk) {
                         // 8 (or 4) taps of 8 (16) channels: each lands as a dense [128*mt pixels][16 (32) B] block. Taps
                         // past the filter re-read the last tap; their weights are zero.
@@ -483,7 +500,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
-                    if (!p.bres) tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    if (!p.bres && !armed) tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
                     if (p.im2col) {
                         tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
                                            static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
