@@ -7,7 +7,7 @@
 // bias -> residual -> activation -> single fp16 rounding); the reference accumulates in fp16 (:50), this kernel in fp32.
 //
 // Roles (19 warps): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..17 = four epilogue groups of 4
-// warps (TMEM lane group = warp % 4) that finish alternate tiles, warp 18 = TMA store issuer. The three single-thread
+// warps (TMEM lane group = warp % 4) that share every tile by column chunks, warp 18 = TMA store issuer. The three single-thread
 // roles run in one lane chosen by elect.sync, with control flow that depends on kernel parameters only: the compiler
 // then keeps their counters and descriptors in uniform registers, which is what tcgen05.mma / TMA instructions read
 // (measured: about 50 cycles per issued MMA against about 120 under `if (lane == 0)`).
@@ -16,7 +16,7 @@
 //            stride and dilation are resolved by the TMA unit and out-of-image taps arrive as zeros.
 //   B tiles: BN output channels x 64 input channels of one filter tap, 3-D tiled map over [K][R*S][C].
 //   Both land in shared memory in the 128-byte-swizzled K-major layout tcgen05.mma consumes directly.
-//   Two to four accumulator buffers in TMEM let the epilogues of earlier tiles overlap the main loop of the next.
+//   Two to four accumulator buffers in TMEM let the epilogue of a tile overlap the main loop of the next ones.
 //   The residual tile is prefetched by TMA into a swizzled staging buffer, combined in place with the accumulator,
 //   and the finished tile leaves by TMA store: the epilogue threads never touch global memory except for the bias.
 //   Halo mode (3x3, stride 1): a tile is a 16 x 8 patch of output pixels; its input patch with border is staged once
@@ -36,7 +36,7 @@ namespace fvm {
 
 static constexpr int BM = 128;        // output pixels per tile (= TMEM lanes)
 static constexpr int BK = 64;         // input channels per k-block (128 bytes of fp16 = one swizzle row)
-static constexpr int EPI_GROUPS = 4;         // epilogue groups of 4 warps; group g finishes the tiles with it % nacc == g
+static constexpr int EPI_GROUPS = 4;         // epilogue groups of 4 warps; group g finishes the 32-column chunks g, g+4, .. of every tile
 static constexpr int MAX_ACC = 4;            // TMEM accumulator buffers (4 when a tile is at most 128 columns wide, else 2)
 static constexpr int EPI_WARPS = 4 * EPI_GROUPS;
 static constexpr int STORE_WARP = 2 + EPI_WARPS;
@@ -127,16 +127,19 @@ __device__ __forceinline__ float2 unpack_h2(uint32_t u) {
 // activation -> fp16, combined in place with the staged residual chunk. `stage_row` points at this row inside the
 // 64-channel staging sub-tile (128-byte swizzle: 16-byte chunk index XOR (row & 7)); `bias_s` at the chunk's bias.
 // ACT: 0 none, 1 relu, 3 silu, 5 gelu (erf), 2 = read p.act at run time. All loads are issued before the arithmetic.
-template <int ACT, bool RES>
+template <int ACT, bool RES, int W>
 __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t taddr, uint32_t stage_row, uint32_t ch0,
                                                uint32_t row_xor, uint32_t bias_s, int n, int left) {
-    uint32_t v[32];
+    static_assert(W == 32 || W == 16, "chunks of 32 or 16 columns");
+    uint32_t v[W];
     __syncwarp();
-    tmem_ld_32x32b_x32(taddr, v);     // in flight while the bias and residual chunks are fetched from shared memory
-    uint4 rw[4];
+    // in flight while the bias and residual chunks are fetched from shared memory
+    if constexpr (W == 32) tmem_ld_32x32b_x32(taddr, v);
+    else tmem_ld_32x32b_x16(taddr, v);
+    uint4 rw[W / 8];
     if (RES) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) rw[j] = lds128(stage_row + (((ch0 + j) ^ row_xor) << 4));
+        for (int j = 0; j < W / 8; ++j) rw[j] = lds128(stage_row + (((ch0 + j) ^ row_xor) << 4));
     }
 #ifdef FVM_CONV_TRACE
     const long long tr0 = clock64();
@@ -147,7 +150,7 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
     const long long tr1 = clock64();
 #endif
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < W / 8; ++j) {
         if (8 * j < left) {
             const uint32_t r4[4] = {rw[j].x, rw[j].y, rw[j].z, rw[j].w};
             uint32_t o[4];
@@ -214,16 +217,24 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
 #endif
 }
 
-// All columns of this thread's row of one tile. BN is a multiple of 32, so every TMEM read is a full 32-column load
-// inside the accumulator buffer.
-template <int ACT, bool RES>
-__device__ __forceinline__ void epilogue_rows(const ConvParams& p, uint32_t t_row, uint32_t stage_row0, uint32_t row_xor,
-                                              uint32_t bias_s, int n0, int ncols) {
-    for (int c0 = 0; c0 < ncols; c0 += 32) {
+// This thread's row of one tile, the 32-column chunks of its epilogue group (group, group + 4, ..). BN is a multiple
+// of 32, so every TMEM read is a full 32-column load inside the accumulator buffer.
+template <int ACT, bool RES, int W>
+__device__ __forceinline__ void epilogue_cols(const ConvParams& p, uint32_t t_row, uint32_t stage_row0, uint32_t row_xor,
+                                              uint32_t bias_s, int n0, int ncols, int group) {
+    for (int c0 = W * group; c0 < ncols; c0 += W * EPI_GROUPS) {
         const uint32_t sub = stage_row0 + static_cast<uint32_t>(c0 >> 6) * SUB_BYTES;
-        epilogue_chunk<ACT, RES>(p, t_row + static_cast<uint32_t>(c0), sub, static_cast<uint32_t>((c0 & 63) >> 3), row_xor,
+        epilogue_chunk<ACT, RES, W>(p, t_row + static_cast<uint32_t>(c0), sub, static_cast<uint32_t>((c0 & 63) >> 3), row_xor,
                                  bias_s + 4u * static_cast<uint32_t>(n0 + c0), n0 + c0, ncols - c0);
     }
+}
+
+// Tiles of up to 64 columns are cut into 16-column chunks so that all four groups have work.
+template <int ACT, bool RES>
+__device__ __forceinline__ void epilogue_rows(const ConvParams& p, uint32_t t_row, uint32_t stage_row0, uint32_t row_xor,
+                                              uint32_t bias_s, int n0, int ncols, int group) {
+    if (p.BN <= 64) epilogue_cols<ACT, RES, 16>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group);
+    else epilogue_cols<ACT, RES, 32>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group);
 }
 
 // Tile number `it` of this CTA. Default: tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the n-tile fastest.
@@ -314,11 +325,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         for (int a = 0; a < p.nacc; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);   // one arrival per warp of the owning epilogue group
+            mbar_init(tempty_bar(a), EPI_WARPS);   // one arrival per epilogue warp
         }
         for (int e = 0; e < p.nepi; ++e) {
             mbar_init(res_full_bar(e), 1);
-            mbar_init(epi_done_bar(e), 4);
+            mbar_init(epi_done_bar(e), EPI_WARPS);
             mbar_init(epi_free_bar(e), 1);
         }
         mbar_init(bres_full_bar, 1);
@@ -730,8 +741,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         __syncwarp();
     } else if (warp < STORE_WARP) {
         // ------------------------------------------------------------------ epilogue
-        // EPI_GROUPS groups of 4 warps (one warp per TMEM lane group). Group g owns accumulator buffer g and takes the
-        // tiles with (iteration % EPI_GROUPS) == g, so consecutive tiles are finished concurrently.
+        // EPI_GROUPS groups of 4 warps (one warp per TMEM lane group). All groups work on every tile: group g takes the
+        // 32-column chunks g, g + 4, .. of the accumulator, so a tile is finished in a quarter of the time one group
+        // would need (short tail at the end of the kernel, two accumulators and two or three staging buffers suffice).
         const int lane_group = warp & 3;
         const int group = (warp - 2) >> 2;
         const int row = lane_group * 32 + lane;       // row of the tile = TMEM lane
@@ -746,32 +758,28 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 bias_f[i] = (p.bias != nullptr && i < p.K) ? __half2float(p.bias[i]) : 0.f;
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
         }
-        uint32_t acc_phase = 0;   // parity of this group's accumulator buffer
-        uint32_t e_phase = 0;     // one parity bit per staging buffer (advanced for every tile, also the other groups')
+        uint32_t acc_phase = 0;   // one parity bit per accumulator buffer
+        uint32_t e_phase = 0;     // one parity bit per staging buffer
         int e = 0;
+        int acc = -1;
         int it = 0;
         bool ok = true;
         int m_tile, n_tile;
         for (; ok && tile_at(p, it, m_tile, n_tile); ++it) {
-            const int acc = it % p.nacc;
-            if (acc != group) {       // another group's tile: only keep the staging-buffer bookkeeping in step
-                e_phase ^= 1u << e;
-                if (++e == p.nepi) e = 0;
-                continue;
-            }
+            if (++acc == p.nacc) acc = 0;
             const int n0 = n_tile * p.BN;
             TRACE(2 + group, it, 0);
             // staging buffer: with a residual it is filled by TMA (res_full); without, wait until it is free
             const bool got_buf = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(e), (e_phase >> e) & 1u, abort_flag)
                                            : mbar_wait<EPI_BACKOFF_NS>(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag);
             TRACE(2 + group, it, 1);
-            if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), acc_phase, abort_flag)) {
+            if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag)) {
                 if (lane == 0) atomicExch(p.status, STATUS_WAIT_EPILOGUE);
                 ok = false;
                 break;
             }
             e_phase ^= 1u << e;
-            acc_phase ^= 1u;
+            acc_phase ^= 1u << acc;
             tc_fence_after();
             TRACE(2 + group, it, 2);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
@@ -788,16 +796,16 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const uint32_t t_sub = t_row + static_cast<uint32_t>(mt * p.BN);
                 const uint32_t s_sub = stage_row0 + static_cast<uint32_t>(mt * p.nsub) * SUB_BYTES;
                 switch (variant) {
-                    case 0: epilogue_rows<0, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 1: epilogue_rows<0, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 2: epilogue_rows<1, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 3: epilogue_rows<1, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 4: epilogue_rows<2, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 5: epilogue_rows<2, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 6: epilogue_rows<3, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 7: epilogue_rows<3, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    case 10: epilogue_rows<5, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
-                    default: epilogue_rows<5, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols); break;
+                    case 0: epilogue_rows<0, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 1: epilogue_rows<0, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 2: epilogue_rows<1, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 3: epilogue_rows<1, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 4: epilogue_rows<2, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 5: epilogue_rows<2, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 6: epilogue_rows<3, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 7: epilogue_rows<3, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    case 10: epilogue_rows<5, false>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
+                    default: epilogue_rows<5, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
                 }
             }
             TRACE(2 + group, it, 3);
@@ -942,19 +950,18 @@ static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, 
     const int floor_epi = kblocks >= 16 ? 1 : 2;
     if (fixed + static_cast<uint32_t>(floor_epi) * epi_bytes + 2 * stage_bytes > total) return false;
     const uint32_t budget = total - fixed;
-    // Short reductions are epilogue-dominated: 4 accumulators and one staging buffer per epilogue group plus spares for
-    // stores in flight. Deep reductions keep 2 accumulators / 2-3 staging buffers and give the pipeline the memory.
+    // All epilogue warps work on one tile at a time, so two accumulators already overlap a tile's epilogue with the
+    // next tile's MMAs (TMEM is not scarce: up to 4 are used when they fit the 512 columns) and three staging buffers
+    // cover "residual arriving / being combined / being stored"; the rest of the shared memory goes to the pipeline.
     int acc_stride = 32;
     while (acc_stride < MT * BN) acc_stride <<= 1;
     if (acc_stride > 256) return false;    // at least two accumulator buffers in the 512 TMEM columns
-    const int max_acc = 512 / acc_stride < MAX_ACC ? 512 / acc_stride : MAX_ACC;
-    int nacc = (kblocks <= 8 && max_acc >= 4) ? 4 : 2;
+    const int nacc = 512 / acc_stride < MAX_ACC ? 512 / acc_stride : MAX_ACC;
     const int min_stages = 4;   // loads in flight span tiles of this persistent CTA, also when one tile has a single k-block
-    int nepi = nacc == 4 ? MAX_EPI : 3;
+    int nepi = kblocks <= 2 ? 4 : 3;
     while (nepi > floor_epi &&
            static_cast<uint32_t>(nepi) * epi_bytes + static_cast<uint32_t>(min_stages) * stage_bytes > budget)
         --nepi;
-    if (nepi < nacc) nacc = 2;
     int stages = stage_bytes ? static_cast<int>((budget - static_cast<uint32_t>(nepi) * epi_bytes) / stage_bytes) : 2;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
@@ -1071,10 +1078,9 @@ int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int 
         p.nh = 2;
         fixed -= p.hbytes;
     }
-    p.nepi = MAX_EPI;
+    p.nepi = 4;
     while (p.nepi > 2 && fixed + static_cast<uint32_t>(p.nepi) * epi_bytes > 227u * 1024) --p.nepi;
     if (fixed + static_cast<uint32_t>(p.nepi) * epi_bytes > 227u * 1024) return FVM_ERR_ARG;
-    if (p.nepi < p.nacc) p.nacc = 2, p.tmem_cols = 2 * p.acc_stride;
     size_t smem = fixed + static_cast<size_t>(p.nepi) * epi_bytes;
     if (smem < 120 * 1024) smem = 120 * 1024;
 
