@@ -621,11 +621,17 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         const int d = ts - p.pw, par = d & 1;
                         uint32_t a_lo = a_base + static_cast<uint32_t>(par) * pplane16 + static_cast<uint32_t>(((d - par) >> 1) - p.stem_xlo);
                         uint32_t b_lo = b_base + static_cast<uint32_t>(ts) * (stem_b_bytes >> 4);
+                        const uint32_t b_step = 2u * static_cast<uint32_t>(p.S) * (stem_b_bytes >> 4);
+                        if (rpairs == 4) {       // 7- and 8-row filters: the column's four tap pairs as one sequence
+                            umma_f16_stepped4(d_tmem, a_lo, a_hi, 2u * prow16, b_lo, b_hi, b_step, idesc, first);
+                            first = 1;
+                            continue;
+                        }
                         for (int rp = 0; rp < rpairs; ++rp) {
                             umma_f16_words(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, first);
                             first = 1;
                             a_lo += 2u * prow16;
-                            b_lo += 2u * static_cast<uint32_t>(p.S) * (stem_b_bytes >> 4);
+                            b_lo += b_step;
                         }
                     }
                     umma_commit(hempty_bar(mma_hs));

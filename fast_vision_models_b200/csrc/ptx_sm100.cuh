@@ -276,6 +276,38 @@ __device__ __forceinline__ void umma_f16_words(uint32_t d_tmem, uint32_t a_lo, u
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Four tcgen05.mma whose A and B descriptors advance by constant steps (low words): the four tap pairs of one filter
+// column in stem mode. The first accumulates iff `acc0` != 0. Call from the single issuing lane.
+__device__ __forceinline__ void umma_f16_stepped4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t a_step, uint32_t b_lo,
+                                                  uint32_t b_hi, uint32_t b_step, uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 al, bl;\n\t"
+        "setp.ne.b32 p, %8, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%4, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+        "add.u32 al, %1, %3;\n\t"
+        "add.u32 bl, %4, %6;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, 1;\n\t"
+        "add.u32 al, al, %3;\n\t"
+        "add.u32 bl, bl, %6;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, 1;\n\t"
+        "add.u32 al, al, %3;\n\t"
+        "add.u32 bl, bl, %6;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, 1;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(a_step), "r"(b_lo), "r"(b_hi), "r"(b_step), "r"(idesc), "r"(acc0)
+        : "memory");
+}
 // The four tcgen05.mma of one 64-half k-block (K = 16 each) as one instruction sequence. Descriptors come as (low word,
 // high word): the start address lives in the low word, so the steps along K (+32 bytes = +2) are 32-bit adds. The first
 // MMA accumulates iff `acc0` != 0, the other three always do. Call from the single issuing lane.

@@ -101,6 +101,10 @@ class FusedConv(nn.Module):
             # 3x3 stride-1 over at most 64 channels: staged input patches (bits 26..27 = 1) against im2col loads (= 2),
             # per tile width. With one 64-channel chunk both modes add the taps in the same order: same bits.
             cands += [c | (1 << 26) for c in widths] + [c | (2 << 26) for c in widths]
+        if self.w.shape[1] != 8:
+            # weight tile resident in shared memory (bits 24..25 = 1) or streamed per k-block (= 2), per tile width
+            base = list(widths)
+            cands += [c | (1 << 24) for c in base] + [c | (2 << 24) for c in base]
         best, best_ms = 0, float("inf")
         if len(cands) > 1:
             for c in cands:
