@@ -208,7 +208,8 @@ static int gap_splits(int N, int HW, int C, int sms) {
 }
 
 // ------------------------------------------------------------------------------------------- squeeze-excite gate
-// One block per image. h = half(act(W1 g + b1)) (warp per output, lanes stride over C); s = half(W2 h + b2)
+// gridDim.y blocks per image: each computes h = half(act(W1 g + b1)) (warp per output, lanes stride over C; the
+// squeeze FC is small, so it is recomputed per block rather than exchanged) and its slice of s = half(W2 h + b2)
 // (thread per output). Rounding points follow the two conv_fused calls the reference issues on [N,C,1,1] tensors.
 __global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __restrict__ w1,
                                const __half* __restrict__ b1, const __half* __restrict__ w2,
@@ -231,7 +232,8 @@ __global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __re
     for (int j = warp; j < Cs; j += nwarps) {
         const __half* row = w1 + static_cast<long long>(j) * C;
         float acc = 0.f;
-        for (int v = lane; v < cv; v += 32) {
+#pragma unroll 4
+        for (int v = lane; v < cv; v += 32) {     // unrolled: several 16-byte weight loads in flight per lane
             float f[8];
             to_f8(ldg16(row + v * 8), f);
 #pragma unroll
@@ -246,9 +248,11 @@ __global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __re
     }
     __syncthreads();
     const int sv = Cs >> 3;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int per = (C + gridDim.y - 1) / gridDim.y, c_end = min(C, static_cast<int>(blockIdx.y + 1) * per);
+    for (int c = blockIdx.y * per + threadIdx.x; c < c_end; c += blockDim.x) {
         const __half* row = w2 + static_cast<long long>(c) * Cs;
         float acc = 0.f;
+#pragma unroll 4
         for (int v = 0; v < sv; ++v) {
             float f[8];
             to_f8(ldg16(row + v * 8), f);
@@ -576,7 +580,11 @@ extern "C" int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, co
         return FVM_ERR_ARG;
     const size_t smem = static_cast<size_t>(C + Cs) * sizeof(float);
     if (smem > 48 * 1024) return FVM_ERR_ARG;
-    se_gate_kernel<<<N, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+    DeviceState* st = device_state();
+    const int sms = st ? st->sms : 148;
+    int split = 1;                       // blocks per image: fill the GPU when the batch alone does not
+    while (split < 4 && N * split * 2 <= 2 * sms && C / (split * 2) >= 256) split *= 2;
+    se_gate_kernel<<<dim3(N, split), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         g, static_cast<const __half*>(w1), static_cast<const __half*>(b1), static_cast<const __half*>(w2),
         static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale);
     FVM_LAUNCH_CHECK();
