@@ -58,19 +58,19 @@ __global__ void input_nhwc8_kernel(const float* __restrict__ x, __half* __restri
 
 // The same conversion into two column-parity planes per image row: y[n][h][w & 1][w >> 1][c] (W even). A stride-2
 // convolution then reads consecutive output columns from consecutive plane columns (see the stem mode of the conv kernel).
-__global__ void input_nhwc8_split_kernel(const float* __restrict__ x, __half* __restrict__ y, int C, int W, long long HW,
-                                         long long total) {
-    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const long long n = i / HW;
-    const long long hw = i - n * HW;
-    const long long row = hw / W;
-    const int w = static_cast<int>(hw - row * W);
-    const float* src = x + n * C * HW + hw;
+__global__ void input_nhwc8_split_kernel(const float* __restrict__ x, __half* __restrict__ y, int C, int H, int W) {
+    // blockIdx.x = image row (n * H + h), blockIdx.y = chunk of columns: one division per thread
+    const int w = blockIdx.y * blockDim.x + threadIdx.x;
+    if (w >= W) return;
+    const long long HW = static_cast<long long>(H) * W;
+    const long long nh = blockIdx.x;
+    const long long n = nh / H;
+    const long long hrow = nh - n * H;
+    const float* src = x + n * C * HW + hrow * W + w;
     float f[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) f[c] = c < C ? __ldg(src + c * HW) : 0.f;
-    const long long o = (n * HW + row * W) + static_cast<long long>(w & 1) * (W >> 1) + (w >> 1);
+    const long long o = nh * W + static_cast<long long>(w & 1) * (W >> 1) + (w >> 1);
     stg16(y + o * 8, from_f8(f));
 }
 
@@ -518,9 +518,11 @@ extern "C" int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H,
 
 extern "C" int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
     if (!x || !y || N <= 0 || C <= 0 || C > 8 || H <= 0 || W <= 0 || (W & 1) || !aligned16(y)) return FVM_ERR_ARG;
-    const long long HW = static_cast<long long>(H) * W, total = HW * N;
-    input_nhwc8_split_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, static_cast<__half*>(y), C, W, HW, total);
+    const long long rows = static_cast<long long>(N) * H;
+    if (rows > 2147483647ll) return FVM_ERR_ARG;
+    const int tpb = W >= 256 ? 256 : (W >= 128 ? 128 : 64);
+    const dim3 grid(static_cast<unsigned>(rows), static_cast<unsigned>((W + tpb - 1) / tpb), 1);
+    input_nhwc8_split_kernel<<<grid, tpb, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<__half*>(y), C, H, W);
     FVM_LAUNCH_CHECK();
 }
 
