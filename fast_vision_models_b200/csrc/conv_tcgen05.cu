@@ -82,9 +82,6 @@ struct ConvParams {
     int stem_taps, stem_xlo;               // stem mode: weight taps held (R rounded up to even, times S); leftmost plane column
     uint32_t stem_prow;                    // stem mode: bytes per staged input row (two planes)
     FastDiv div_txy, div_tx;
-#ifdef FVM_CONV_TRACE
-    int dbg;
-#endif
     int bres;      // 1: the weights of this CTA's n-tile stay resident in shared memory (loaded once); each CTA keeps one
                    // n-tile and walks the m-tiles; pipeline stages then hold A only
     int act;
@@ -333,9 +330,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(epi_free_bar(e), 1);
         }
         mbar_init(bres_full_bar, 1);
-#ifdef FVM_CONV_TRACE
-        mbar_init(hfull_bar(2), 1);
-#endif
         for (int h = 0; h < p.nh; ++h) {
             mbar_init(hfull_bar(h), 1);
             mbar_init(hempty_bar(h), 1);
@@ -572,20 +566,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         st_lo += stage_step;                                                  \
         if (++stage == p.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }   \
     } while (0)
-#ifdef FVM_CONV_TRACE
-            if (p.dbg & 2) {    // issue-rate probe in this kernel's context: 256 MMAs on whatever the buffers hold
-                const long long c0 = clock64();
-                for (int kb = 0; kb < 64; ++kb) {
-                    const int tp = kb % 9, tr = tp / 3, ts = tp - tr * 3;
-                    umma_f16_kblock(tmem_base, lo_of(halo_base) + (tr * 16 + ts) * 8, hi_halo, lo_of(bres_base) + (kb & 3) * (p.BN * 8), hi128, idesc, kb != 0);
-                }
-                const long long c1 = clock64();
-                umma_commit(hfull_bar(2));
-                mbar_wait(hfull_bar(2), 0u, abort_flag);
-                const long long c2 = clock64();
-                if (blockIdx.x == 0) { g_conv_trace[4000] = c1 - c0; g_conv_trace[4001] = c2 - c0; }
-            }
-#endif
             if ((p.tapk || p.bres) && my_tiles > 0) failed |= !mbar_wait(bres_full_bar, 0u, abort_flag);
             // Look-ahead: the barrier of the next step (stage, staged patch, accumulator) is tested while the MMAs of
             // the current step are issued; the blocking wait runs only if that test said "not yet".
@@ -795,9 +775,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // activation as a template argument for the common ones (0 none, 1 relu, 3 silu, 5 gelu-erf); 2 = read at run time
             const int act_t = (p.act == 0 || p.act == 1 || p.act == 3 || p.act == 5) ? p.act : 2;
             const int variant = act_t * 2 + (p.has_res ? 1 : 0);
-#ifdef FVM_CONV_TRACE
-            if (!(p.dbg & 1))
-#endif
             for (int mt = 0; mt < p.mt; ++mt) {
                 const uint32_t t_sub = t_row + static_cast<uint32_t>(mt * p.BN);
                 const uint32_t s_sub = stage_row0 + static_cast<uint32_t>(mt * p.nsub) * SUB_BYTES;
@@ -831,8 +808,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------------------------------------------ store warp
         if (elect_one()) {
             uint32_t e_phase = 0;   // one parity bit per staging buffer
-            int e = 0, e_prev = -1;
-            const bool defer = false;    // measured on B200: releasing one tile late starves the residual prefetch; kept off
+            int e = 0;
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int m_tile, n_tile;
@@ -864,18 +840,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      n0 + sub * 64, m0 + mt * BM);
                 tma_store_commit();
                 TRACE(6, sit, 2);
-                if (defer) {
-                    // with three or more staging buffers the release trails by one tile: this thread does not sit
-                    // out the read-out of the store it has just issued
-                    if (e_prev >= 0) {
-                        tma_store_wait_read_but_one();
-                        mbar_arrive(epi_free_bar(e_prev));
-                    }
-                    e_prev = e;
-                } else {
-                    tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
-                    mbar_arrive(epi_free_bar(e));
-                }
+                tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
+                mbar_arrive(epi_free_bar(e));
                 TRACE(6, sit, 3);
                 if (++e == p.nepi) e = 0;
             }
@@ -1211,9 +1177,6 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.div_ntiles = fastdiv_init(static_cast<uint32_t>(p.n_tiles));
     if (p.n_tiles > 1 && (p.BN & 63)) return FVM_ERR_ARG;   // split K only in whole 64-channel store boxes
     p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && ph_hi == 0 && pw_hi == 0);
-#ifdef FVM_CONV_TRACE
-    p.dbg = getenv("FVM_DBG") ? atoi(getenv("FVM_DBG")) : 0;
-#endif
     p.act = act;
     p.has_res = res != nullptr;
     p.bias = static_cast<const __half*>(bias);

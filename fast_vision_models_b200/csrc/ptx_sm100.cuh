@@ -161,9 +161,6 @@ __device__ __forceinline__ void tma_store_4d(const void* desc, uint32_t src, int
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until every committed bulk store of this thread has finished READING shared memory (the source may be reused).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// The same with one committed group still allowed to be reading: the store of the previous tile is then off the
-// critical path of the thread that issues the stores.
-__device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // Orders this thread's generic-proxy writes to shared memory before later async-proxy (TMA) reads of them.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
