@@ -161,17 +161,10 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
                 for (int k = 0; k < 4; ++k) {
                     unsigned long long t = f2_add(f2_pack(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]), bw[k]);
                     if (RES) t = f2_add(t, h2_to_f2(r4[k]));
-                    if (ACT == 3 || ACT == 5) {
-                        float lo, hi;
-                        f2_unpack(t, lo, hi);
-                        if (ACT == 3) {
-                            lo = __fdividef(lo, 1.f + __expf(-lo));
-                            hi = __fdividef(hi, 1.f + __expf(-hi));
-                        } else {
-                            lo = 0.5f * lo * (1.f + erff(lo * 0.70710678118654752f));
-                            hi = 0.5f * hi * (1.f + erff(hi * 0.70710678118654752f));
-                        }
-                        o[k] = pack_h2(lo, hi);
+                    if (ACT == 3) {
+                        o[k] = f2_to_h2(f2_silu(t));
+                    } else if (ACT == 5) {
+                        o[k] = f2_to_h2(f2_gelu_erf(t));
                     } else {
                         o[k] = f2_to_h2(t);
                         if (ACT == 1) o[k] = h2_relu(o[k]);
