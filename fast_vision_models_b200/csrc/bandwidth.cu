@@ -279,7 +279,9 @@ __global__ void se_scale_kernel(const __half* __restrict__ x, const __half* __re
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         float2 t = __half22float2(g.h2[j]);
-        __half2 sg = __floats2half2_rn(1.f / (1.f + __expf(-t.x)), 1.f / (1.f + __expf(-t.y)));
+        // sigmoid as rcp(1 + 2^(-t log2 e)) with the approximate reciprocal (1-2 fp32 ulp, far inside the fp16 rounding
+        // that follows): the IEEE division made this kernel issue-bound
+        __half2 sg = __floats2half2_rn(__fdividef(1.f, 1.f + __expf(-t.x)), __fdividef(1.f, 1.f + __expf(-t.y)));
         o.h2[j] = __hmul2(a.h2[j], sg);
     }
     stg16(y + i * 8, o.u);

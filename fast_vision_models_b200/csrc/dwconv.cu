@@ -432,7 +432,10 @@ dwconv_tile_kernel(const __half* __restrict__ x, const __half* __restrict__ w, c
                         o[k] = __hmax2(o[k], __float2half2_rn(0.f));
                     } else if (ACT != 0) {
                         const float2 f = __half22float2(o[k]);
-                        if (ACT == 3) o[k] = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+                        if (ACT == 3) {      // SiLU on the pair: packed multiplies, ex2 / rcp per element (no IEEE division)
+                            const uint32_t sv = f2_to_h2(f2_silu(f2_pack(__float_as_uint(f.x), __float_as_uint(f.y))));
+                            o[k] = *reinterpret_cast<const __half2*>(&sv);
+                        }
                         else o[k] = __floats2half2_rn(act_f(f.x, act), act_f(f.y, act));
                     }
                     if (pool_sums) {
