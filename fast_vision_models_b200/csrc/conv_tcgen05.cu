@@ -219,11 +219,15 @@ __device__ __forceinline__ void epilogue_cols(const ConvParams& p, uint32_t t_ro
     }
 }
 
-// Tiles of up to 64 columns are cut into 16-column chunks so that all four groups have work.
+// The chunk width (32 or 16 columns) is the one with which the busiest of the four groups has fewer columns to do:
+// 16 for tiles of up to 64 columns and for widths like 144, 160 or 192 (5 or 6 chunks of 32 would leave one group
+// with two chunks while the others have one).
 template <int ACT, bool RES>
 __device__ __forceinline__ void epilogue_rows(const ConvParams& p, uint32_t t_row, uint32_t stage_row0, uint32_t row_xor,
                                               uint32_t bias_s, int n0, int ncols, int group) {
-    if (p.BN <= 64) epilogue_cols<ACT, RES, 16>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group);
+    const int rounds32 = ((ncols + 31) / 32 + EPI_GROUPS - 1) / EPI_GROUPS;
+    const int rounds16 = ((ncols + 15) / 16 + EPI_GROUPS - 1) / EPI_GROUPS;
+    if (rounds16 * 16 < rounds32 * 32) epilogue_cols<ACT, RES, 16>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group);
     else epilogue_cols<ACT, RES, 32>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group);
 }
 
