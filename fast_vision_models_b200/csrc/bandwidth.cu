@@ -528,11 +528,52 @@ extern "C" int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, 
     FVM_LAUNCH_CHECK();
 }
 
+// 3x3 window with the loops unrolled: the (up to) nine 16-byte loads of a thread are independent and all in flight
+// together; the general kernel above issues them one by one behind its bounds checks. Same mapping, same bits.
+__global__ void maxpool3x3_kernel(const __half* __restrict__ x, __half* __restrict__ y, int H, int W, int C, int sh, int sw,
+                                  int ph, int pw, int P, int Q, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    long long t = i / cv;
+    const int q = static_cast<int>(t % Q);
+    t /= Q;
+    const int pp = static_cast<int>(t % P);
+    const long long n = t / P;
+    const int h0 = pp * sh - ph, w0 = q * sw - pw;
+    const uint4 ninf4 = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);
+    V8 a[9];
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+            const int h = h0 + r, w = w0 + s;
+            const bool ok = h >= 0 && h < H && w >= 0 && w < W;
+            a[r * 3 + s].u = ok ? ldg16(x + ((n * H + h) * W + w) * C + v * 8) : ninf4;
+        }
+    }
+    V8 m;
+    m.u = a[0].u;
+#pragma unroll
+    for (int k = 1; k < 9; ++k) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m.h2[j] = __hmax2(m.h2[j], a[k].h2[j]);
+    }
+    stg16(y + i * 8, m.u);
+}
+
 extern "C" int fvm_maxpool_f16(const void* x, void* y, int N, int H, int W, int C, int kh, int kw, int sh, int sw,
                                int ph, int pw, int P, int Q, void* stream) {
     if (!x || !y || N <= 0 || H <= 0 || W <= 0 || C <= 0 || (C & 7) || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
         P <= 0 || Q <= 0 || !aligned16(x) || !aligned16(y))
         return FVM_ERR_ARG;
+    if (kh == 3 && kw == 3) {
+        const long long total3 = static_cast<long long>(N) * P * Q * (C >> 3);
+        maxpool3x3_kernel<<<blocks_for(total3, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const __half*>(x), static_cast<__half*>(y), H, W, C, sh, sw, ph, pw, P, Q, total3);
+        FVM_LAUNCH_CHECK();
+    }
     const long long total = static_cast<long long>(N) * P * Q * (C >> 3);
     maxpool_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(x), static_cast<__half*>(y), H, W, C, kh, kw, sh, sw, ph, pw, P, Q, total);
