@@ -34,6 +34,17 @@ def act_code(m: Optional[nn.Module]) -> int:
     raise ValueError(f"activation {type(m).__name__} has no fused code")
 
 
+_FLUSH = {}
+
+
+def _l2_flush_buffer(device) -> torch.Tensor:
+    """A scratch buffer larger than the 126 MB L2 (one per device, allocated at the first tuning)."""
+    key = torch.device(device).index
+    if key not in _FLUSH:
+        _FLUSH[key] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    return _FLUSH[key]
+
+
 class FusedConv(nn.Module):
     """y = act((conv(x, w) + b) * scale + res): one launch of the tcgen05 implicit-GEMM kernel."""
 
@@ -105,26 +116,38 @@ class FusedConv(nn.Module):
             # weight tile resident in shared memory (bits 24..25 = 1) or streamed per k-block (= 2), per tile width
             base = list(widths)
             cands += [c | (1 << 24) for c in base] + [c | (2 << 24) for c in base]
-        best, best_ms = 0, float("inf")
+        best = 0
         if len(cands) > 1:
+            # Candidates are timed in rounds (every candidate once per round, best burst kept), so that a drift of the
+            # clocks during tuning hits all of them alike; a candidate the library refuses is dropped.
+            cands = list(dict.fromkeys(cands))
+            times = {}
             for c in cands:
                 try:
                     for _ in range(2):
                         ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
                                             dilation=self.dilation, scale=self.scale, tile_n=c)
-                    ms = float("inf")
-                    for _rep in range(3):          # best of three short bursts: robust against a stray stall
-                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        e0.record()
-                        for _ in range(6):
-                            ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
-                                                dilation=self.dilation, scale=self.scale, tile_n=c)
-                        e1.record()
-                        e1.synchronize()
-                        ms = min(ms, e0.elapsed_time(e1))
+                    times[c] = float("inf")
                 except ops.FvmError:
                     continue
-                if ms < best_ms * 0.97:      # a different tile must be clearly faster than the default
+            # Each timed launch sees the cache state it has inside a forward pass: weights, residual and output cold
+            # (a buffer larger than L2 is overwritten first), the input freshly written (as by the previous layer).
+            flush = _l2_flush_buffer(x.device)
+            for _round in range(4):
+                for c in times:
+                    for _ in range(2):
+                        flush.zero_()
+                        x.mul_(1)           # exact identity: rewrites the input, which puts it back into L2
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        ops.conv_fused_into(x, self.w, self.b, res, self.padding, self.stride, act, out,
+                                            dilation=self.dilation, scale=self.scale, tile_n=c)
+                        e1.record()
+                        e1.synchronize()
+                        times[c] = min(times[c], e0.elapsed_time(e1))
+            best_ms = times.get(0, float("inf"))
+            for c, ms in times.items():
+                if ms < best_ms * 0.97:      # a different tile must be clearly faster than the incumbent
                     best, best_ms = c, ms
         self._tiles[key] = best
         return best
