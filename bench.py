@@ -37,7 +37,7 @@ ALGO_BYTES_PER_IMAGE = {"resnet50": 59.52e6}
 ALGO_FLOPS_PER_IMAGE = {"resnet50": 8.178e9}
 # DRAM traffic of one 64-image forward from an ncu capture of the replayed graph (dram__bytes_read.sum +
 # dram__bytes_write.sum summed over its 59 launches; profiles/resnet50_b64_forward_launches.md).
-NCU_TRAFFIC_PER_STEP = {("resnet50", 64): 2493.1e6}
+NCU_TRAFFIC_PER_STEP = {("resnet50", 64): 2486.9e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
