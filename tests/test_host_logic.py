@@ -79,3 +79,15 @@ def test_bilinear_oracle_matches_torch_interpolate():
     am = ops_ref.up_argmax_ref(x, 20, 28)
     ref = torch.nn.functional.interpolate(x.float(), size=(20, 28), mode="bilinear", align_corners=False).argmax(1)
     assert (am.long() == ref).float().mean() > 0.999
+
+
+def test_stem_entry_points_refuse_cpu_tensors_and_opbench_parses():
+    # the split-input stem has no CPU path either: it raises instead of falling back
+    with pytest.raises(ops.FvmError):
+        ops.input_nhwc8_split(torch.zeros(1, 3, 8, 8))
+    with pytest.raises(ops.FvmError):
+        ops.stem_conv_s2(torch.zeros(1, 8, 2, 4, 8, dtype=torch.float16), torch.zeros(8, 8, 3, 3, dtype=torch.float16),
+                         None, (1, 1), 0)
+    import importlib
+    mod = importlib.import_module("fast_vision_models_b200.opbench")
+    assert callable(mod.main)
