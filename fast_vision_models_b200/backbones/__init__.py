@@ -68,6 +68,7 @@ def build(name: str, tier: str = "cuda-kernels", spec=None, device: str = "cuda"
         return Backbone(fn, IMNET_MEAN, IMNET_STD, 32, up, {"tier": tier})
     from .. import ops
     from ..classification import fast as clf_fast
+    from ..classification.fast import as_image
     from ..runtime import GraphRunner
     net = clf_fast.compile_model(up).to(device)
     if model.startswith("resnet"):
@@ -76,9 +77,9 @@ def build(name: str, tier: str = "cuda-kernels", spec=None, device: str = "cuda"
     else:
         def raw(x):
             return net.features(x).float().contiguous()
-    runner = GraphRunner(raw, enabled=graphs)
+    runner = GraphRunner(raw, enabled=graphs, chainable=True)
 
     def fn(x):
         with torch.no_grad():
-            return runner(x.float().contiguous())
+            return runner(as_image(x))
     return Backbone(fn, IMNET_MEAN, IMNET_STD, 32, up, {"tier": "b200", "compiled": type(net).__name__})

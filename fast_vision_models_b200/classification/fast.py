@@ -62,8 +62,8 @@ class ResNetTrunk(nn.Module):
         self.out_channels = self.blocks[-1]["convs"][-1].out_channels
 
     def forward(self, x: torch.Tensor, want_stage3: bool = False):
-        # fp32 NCHW image batch (or an fp16 NHWC8 tensor: the reference's clf::input_nhwc8 output)
-        x = self.stem.forward_image(x) if x.dtype == torch.float32 else self.stem(x)
+        # fp32 / fp16 NCHW image batch (fewer than 8 channels), or an fp16 NHWC8 tensor (clf::input_nhwc8's output)
+        x = self.stem.forward_image(x) if x.shape[1] < 8 else self.stem(x)
         k, s, p, ceil = self.pool
         x = ops.maxpool(x, k, s, p, ceil)
         aux = None
@@ -223,14 +223,22 @@ class B200ConvNeXt(nn.Module):
 
 
 # ------------------------------------------------------------------------------------------------ wrappers
+def as_image(x: torch.Tensor) -> torch.Tensor:
+    """Network input as the kernels take it: contiguous NCHW, fp32 or fp16 (an fp16 host batch halves the bytes that
+    cross PCIe; the first kernel converts either type to fp16 NHWC, as the reference's templated input kernel does)."""
+    if x.dtype not in (torch.float32, torch.float16):
+        x = x.float()
+    return x.contiguous()
+
+
 class Fast(nn.Module):
-    """fp32 NCHW in -> compiled fp16 NHWC network -> fp32 out, replayed as one CUDA graph per input shape
+    """fp32 (or fp16) NCHW in -> compiled fp16 NHWC network -> fp32 out, replayed as one CUDA graph per input shape
     (counterpart of the reference's `Fast`, classification/fast/__init__.py:45-95)."""
 
     def __init__(self, net: nn.Module, graphs: bool = True):
         super().__init__()
         self.net = net
-        self._runner = GraphRunner(self._run, enabled=graphs)
+        self._runner = GraphRunner(self._run, enabled=graphs, chainable=True)
 
     def _run(self, x: torch.Tensor) -> torch.Tensor:
         return self.net(x)
@@ -239,7 +247,7 @@ class Fast(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not x.is_cuda:
             raise ops.FvmError("the b200 tier runs on a CUDA device only (no CPU path)")
-        return self._runner(x.float().contiguous())
+        return self._runner(as_image(x))
 
     @property
     def runner(self) -> GraphRunner:
@@ -279,8 +287,9 @@ def compile_model(model: nn.Module, family_hint: Optional[str] = None, **kw) -> 
         return B200EfficientNet(model)
     if name == "ConvNeXt":
         return B200ConvNeXt(model, **kw)
-    raise NotImplementedError(f"b200 tier: no compiler for {name}; supported: ResNet, EfficientNet, ConvNeXt "
-                              f"(DeepLabV3 through the segmentation registry)")
+    # every other architecture: the generic graph pass (conv -> [add] -> [act] chains, depthwise, pools, ...)
+    from .fused import fuse_graph
+    return fuse_graph(model)
 
 
 def optimize(model: nn.Module, spec=None, mode: str = "max", graphs: bool = True, **kw) -> nn.Module:

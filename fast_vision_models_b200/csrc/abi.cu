@@ -3,6 +3,7 @@
 #include <mutex>
 
 #include "fvm_internal.h"
+#include "ptx_sm100.cuh"
 
 namespace fvm {
 
@@ -20,9 +21,35 @@ DeviceState* device_state() {
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+// Self-test of the bounded-wait path every kernel role relies on: one thread waits on an mbarrier that nothing ever
+// arrives at, with a limit of `limit_ns`; the wait gives up, the status word receives 0x1ff and the kernel returns by
+// itself. No trap, no unbounded spin: the context stays usable.
+static constexpr int STATUS_SELFTEST_WAIT = 0x1ff;
+__global__ void wait_expiry_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait<32>(smem_u32(&bar), 0u, &abort_flag, limit_ns)) atomicExch(status, STATUS_SELFTEST_WAIT);
+}
+
 }  // namespace fvm
 
 using namespace fvm;
+
+extern "C" int fvm_selftest_wait_expiry(int limit_us, void* stream) {
+    DeviceState* st = device_state();
+    if (!st) return FVM_ERR_SETUP;
+    if (limit_us <= 0 || limit_us > 100000) return FVM_ERR_ARG;      // at most 0.1 s
+    wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st->status_dev,
+                                                                        static_cast<unsigned long long>(limit_us) * 1000ull);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
+}
 
 extern "C" int fvm_init(void) {
     int dev = -1;

@@ -2,6 +2,7 @@
 // squeeze-excite gate and scale, channels-last LayerNorm, elementwise epilogues, bilinear resize and fused
 // upsample+argmax. All of them move 16 bytes (8 channels) per thread per access, accumulate in fp32 and round once.
 #include <cstdint>
+#include <mutex>
 
 #include "fvm_internal.h"
 #include "ptx_sm100.cuh"
@@ -43,22 +44,28 @@ static inline int blocks_for(long long items, int threads) {
 
 // ------------------------------------------------------------------------------------------- input fp32 NCHW -> NHWC8
 // y[n,h,w,c] = c < C ? half(x[n,c,h,w]) : 0   (reference: classification/fast/csrc/fused_conv.cu:597-606)
-__global__ void input_nhwc8_kernel(const float* __restrict__ x, __half* __restrict__ y, int C, long long HW,
+__device__ __forceinline__ float in_f32(float v) { return v; }
+__device__ __forceinline__ float in_f32(__half v) { return __half2float(v); }
+
+// T = float or __half: the reference's kernel is a template over both input types (fused_conv.cu:597-620).
+template <class T>
+__global__ void input_nhwc8_kernel(const T* __restrict__ x, __half* __restrict__ y, int C, long long HW,
                                    long long total) {
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long n = i / HW;
     const long long hw = i - n * HW;
-    const float* src = x + n * C * HW + hw;
+    const T* src = x + n * C * HW + hw;
     float f[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) f[c] = c < C ? __ldg(src + c * HW) : 0.f;
+    for (int c = 0; c < 8; ++c) f[c] = c < C ? in_f32(__ldg(src + c * HW)) : 0.f;
     stg16(y + i * 8, from_f8(f));
 }
 
 // The same conversion into two column-parity planes per image row: y[n][h][w & 1][w >> 1][c] (W even). A stride-2
 // convolution then reads consecutive output columns from consecutive plane columns (see the stem mode of the conv kernel).
-__global__ void input_nhwc8_split_kernel(const float* __restrict__ x, __half* __restrict__ y, int C, int H, int W) {
+template <class T>
+__global__ void input_nhwc8_split_kernel(const T* __restrict__ x, __half* __restrict__ y, int C, int H, int W) {
     // blockIdx.x = image row (n * H + h), blockIdx.y = chunk of columns: one division per thread
     const int w = blockIdx.y * blockDim.x + threadIdx.x;
     if (w >= W) return;
@@ -66,10 +73,10 @@ __global__ void input_nhwc8_split_kernel(const float* __restrict__ x, __half* __
     const long long nh = blockIdx.x;
     const long long n = nh / H;
     const long long hrow = nh - n * H;
-    const float* src = x + n * C * HW + hrow * W + w;
+    const T* src = x + n * C * HW + hrow * W + w;
     float f[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) f[c] = c < C ? __ldg(src + c * HW) : 0.f;
+    for (int c = 0; c < 8; ++c) f[c] = c < C ? in_f32(__ldg(src + c * HW)) : 0.f;
     const long long o = nh * W + static_cast<long long>(w & 1) * (W >> 1) + (w >> 1);
     stg16(y + o * 8, from_f8(f));
 }
@@ -510,22 +517,37 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 
 using namespace fvm;
 
-extern "C" int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
+template <class T>
+static int input_nhwc8_launch(const T* x, void* y, int N, int C, int H, int W, void* stream) {
     if (!x || !y || N <= 0 || C <= 0 || C > 8 || H <= 0 || W <= 0 || !aligned16(y)) return FVM_ERR_ARG;
     const long long HW = static_cast<long long>(H) * W, total = HW * N;
-    input_nhwc8_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    input_nhwc8_kernel<T><<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x, static_cast<__half*>(y), C, HW, total);
     FVM_LAUNCH_CHECK();
 }
 
-extern "C" int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
+template <class T>
+static int input_nhwc8_split_launch(const T* x, void* y, int N, int C, int H, int W, void* stream) {
     if (!x || !y || N <= 0 || C <= 0 || C > 8 || H <= 0 || W <= 0 || (W & 1) || !aligned16(y)) return FVM_ERR_ARG;
     const long long rows = static_cast<long long>(N) * H;
     if (rows > 2147483647ll) return FVM_ERR_ARG;
     const int tpb = W >= 256 ? 256 : (W >= 128 ? 128 : 64);
     const dim3 grid(static_cast<unsigned>(rows), static_cast<unsigned>((W + tpb - 1) / tpb), 1);
-    input_nhwc8_split_kernel<<<grid, tpb, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<__half*>(y), C, H, W);
+    input_nhwc8_split_kernel<T><<<grid, tpb, 0, static_cast<cudaStream_t>(stream)>>>(x, static_cast<__half*>(y), C, H, W);
     FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
+    return input_nhwc8_launch(x, y, N, C, H, W, stream);
+}
+extern "C" int fvm_input_nhwc8_f16(const void* x, void* y, int N, int C, int H, int W, void* stream) {
+    return input_nhwc8_launch(static_cast<const __half*>(x), y, N, C, H, W, stream);
+}
+extern "C" int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, int H, int W, void* stream) {
+    return input_nhwc8_split_launch(x, y, N, C, H, W, stream);
+}
+extern "C" int fvm_input_nhwc8_split_f16(const void* x, void* y, int N, int C, int H, int W, void* stream) {
+    return input_nhwc8_split_launch(static_cast<const __half*>(x), y, N, C, H, W, stream);
 }
 
 // 3x3 window with the loops unrolled: the (up to) nine 16-byte loads of a thread are independent and all in flight
@@ -746,6 +768,7 @@ struct NoAllocGapState {
     bool ready = false;
 };
 NoAllocGapState g_noalloc_gap[64];
+std::mutex g_noalloc_gap_mutex;
 }  // namespace
 
 extern "C" long long fvm_global_avgpool_f16_noalloc_max_floats(void) { return FVM_GAP_NOALLOC_MAX_FLOATS; }
@@ -757,18 +780,22 @@ extern "C" int fvm_global_avgpool_f16_noalloc(const void* x, void* y, int N, int
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FVM_ERR_SETUP;
     NoAllocGapState& st = g_noalloc_gap[dev];
-    if (!st.ready) {
-        // First call on this device (it is the current device): in host code the array's name is only a handle, the
-        // address a kernel can use comes from the runtime. Nothing is allocated here.
-        float* ptr = nullptr;
-        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gap_noalloc_scratch) != cudaSuccess || !ptr)
-            return FVM_ERR_SETUP;
-        int sms = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            return FVM_ERR_SETUP;
-        st.scratch = ptr;
-        st.sms = sms;
-        st.ready = true;
+    {
+        // the first call on a device publishes {scratch, sms, ready} under a lock: two host threads may make it at once
+        std::lock_guard<std::mutex> lock(g_noalloc_gap_mutex);
+        if (!st.ready) {
+            // First call on this device (it is the current device): in host code the array's name is only a handle,
+            // the address a kernel can use comes from the runtime. Nothing is allocated here.
+            float* ptr = nullptr;
+            if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gap_noalloc_scratch) != cudaSuccess || !ptr)
+                return FVM_ERR_SETUP;
+            int sms = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+                return FVM_ERR_SETUP;
+            st.scratch = ptr;
+            st.sms = sms;
+            st.ready = true;
+        }
     }
     const int splits = gap_splits(N, HW, C, st.sms);
     if (static_cast<long long>(N) * splits * C > FVM_GAP_NOALLOC_MAX_FLOATS) return FVM_ERR_ARG;   // beyond the fixed scratch

@@ -93,19 +93,6 @@ struct ConvParams {
     int* status;
 };
 
-// Optional timeline trace for tuning builds (-DFVM_CONV_TRACE): CTA 0 records SM clock stamps per role and tile.
-#ifdef FVM_CONV_TRACE
-__device__ long long g_conv_trace[4096];
-#define TRACE(role, it, kind)                                                                         \
-    do {                                                                                              \
-        if (blockIdx.x == 0 && (it) < 24) g_conv_trace[(role) * 256 + (it) * 8 + (kind)] = clock64(); \
-    } while (0)
-#else
-#define TRACE(role, it, kind) \
-    do {                      \
-    } while (0)
-#endif
-
 // status codes written by the device when a bounded wait ran out: 0x100 + role
 static constexpr int STATUS_WAIT_PRODUCER = 0x101;
 static constexpr int STATUS_WAIT_MMA = 0x102;
@@ -138,14 +125,7 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
 #pragma unroll
         for (int j = 0; j < W / 8; ++j) rw[j] = lds128(stage_row + (((ch0 + j) ^ row_xor) << 4));
     }
-#ifdef FVM_CONV_TRACE
-    const long long tr0 = clock64();
-#endif
     tmem_ld_wait();
-#ifdef FVM_CONV_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 64) { g_conv_trace[2048 + g_conv_trace[2047] % 512] = clock64() - tr0; g_conv_trace[2047]++; }
-    const long long tr1 = clock64();
-#endif
 #pragma unroll
     for (int j = 0; j < W / 8; ++j) {
         if (8 * j < left) {
@@ -202,9 +182,6 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
             sts128(stage_row + (((ch0 + j) ^ row_xor) << 4), make_uint4(o[0], o[1], o[2], o[3]));
         }
     }
-#ifdef FVM_CONV_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 64) { g_conv_trace[2560 + g_conv_trace[2046] % 512] = clock64() - tr1; g_conv_trace[2046]++; }
-#endif
 }
 
 // This thread's row of one tile, the 32-column chunks of its epilogue group (group, group + 4, ..). BN is a multiple
@@ -415,7 +392,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     hy0 = ty * HALO_TH;
                     hx0 = (rem - ty * p.tiles_x) * HALO_TW;
                 }
-                TRACE(0, pit, 0);
                 if (p.has_res) {
                     // residual tile of this output tile -> staging buffer e (free once its previous store was read out)
                     if (!mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag)) {
@@ -434,7 +410,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
                         }
                     if (++e == p.nepi) e = 0;
-                    TRACE(0, pit, 1);
                 }
                 if (p.halo) {
                     // per 64-channel chunk: one staged input patch (rows hy0-ph .., 16 pixels from hx0-pw, zero outside
@@ -573,7 +548,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 acc_phase ^= 1u << acc;
                 const int acc_next = acc + 1 == p.nacc ? 0 : acc + 1;
                 tc_fence_after();
-                TRACE(1, it, 0);
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
                 if (p.halo == 2) {
                     // Stem mode. Output pixel (oy, ox) of the patch, tap (r, s): input row 2*oy + r, plane (s - pw) & 1,
@@ -614,7 +588,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     umma_commit(hempty_bar(mma_hs));
                     if (++mma_hs == p.nh) { mma_hs = 0; mma_hphase ^= 1u; }
                     umma_commit(tfull_bar(acc));
-                    TRACE(1, it, 2);
                     continue;
                 }
                 if (p.halo) {
@@ -659,7 +632,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         if (++mma_hs == p.nh) { mma_hs = 0; mma_hphase ^= 1u; }
                     }
                     umma_commit(tfull_bar(acc));
-                    TRACE(1, it, 2);
                     continue;
                 }
                 uint32_t bres_lo = lo_of(bres_base);
@@ -672,7 +644,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     if (kb == p.kblocks - 1)
                         acc_ready = mbar_test(tempty_bar(acc_next), ((acc_phase >> acc_next) & 1u) ^ 1u);
-                    if (kb == 0) TRACE(1, it, 1);
                     const uint32_t a_src = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     if (p.tapk == 16) {
                         // one MMA (K = 16) per tap: rows of 32 bytes in the 32-byte-swizzled layout
@@ -716,7 +687,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     NEXT_STAGE();
                 }
                 umma_commit(tfull_bar(acc));  // accumulator complete
-                TRACE(1, it, 2);
             }
 #undef NEXT_STAGE
             if (failed) atomicExch(p.status, STATUS_WAIT_MMA);
@@ -751,11 +721,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (; ok && tile_at(p, it, m_tile, n_tile); ++it) {
             if (++acc == p.nacc) acc = 0;
             const int n0 = n_tile * p.BN;
-            TRACE(2 + group, it, 0);
             // staging buffer: with a residual it is filled by TMA (res_full); without, wait until it is free
             const bool got_buf = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(e), (e_phase >> e) & 1u, abort_flag)
                                            : mbar_wait<EPI_BACKOFF_NS>(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag);
-            TRACE(2 + group, it, 1);
             if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag)) {
                 if (lane == 0) atomicExch(p.status, STATUS_WAIT_EPILOGUE);
                 ok = false;
@@ -764,7 +732,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             e_phase ^= 1u << e;
             acc_phase ^= 1u << acc;
             tc_fence_after();
-            TRACE(2 + group, it, 2);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                    static_cast<uint32_t>(acc * p.acc_stride);
             const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
@@ -788,7 +755,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     default: epilogue_rows<5, true>(p, t_sub, s_sub, row_xor, bias_s, n0, ncols, group); break;
                 }
             }
-            TRACE(2 + group, it, 3);
             // all TMEM reads of this warp are done: hand the accumulator back; publish this warp's rows of the staged
             // tile to the async proxy, then tell the store warp
             tc_fence_before();
@@ -798,7 +764,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 mbar_arrive(tempty_bar(acc));
                 mbar_arrive(epi_done_bar(e));
             }
-            TRACE(2 + group, it, 4);
             if (++e == p.nepi) e = 0;
         }
     } else {
@@ -812,14 +777,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int sit = 0; ok && tile_at(p, sit, m_tile, n_tile); ++sit) {
                 const int m0 = m_tile * BM * p.mt;
                 const int n0 = n_tile * p.BN;
-                TRACE(6, sit, 0);
                 if (!mbar_wait<EPI_BACKOFF_NS>(epi_done_bar(e), (e_phase >> e) & 1u, abort_flag)) {
                     atomicExch(p.status, STATUS_WAIT_STORE);
                     ok = false;
                     break;
                 }
                 e_phase ^= 1u << e;
-                TRACE(6, sit, 1);
                 const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
                 if (p.halo) {
                     const int himg = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_txy));
@@ -836,10 +799,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                          static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES,
                                      n0 + sub * 64, m0 + mt * BM);
                 tma_store_commit();
-                TRACE(6, sit, 2);
                 tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
                 mbar_arrive(epi_free_bar(e));
-                TRACE(6, sit, 3);
                 if (++e == p.nepi) e = 0;
             }
             // Shared memory must outlive the stores' reads of it; the writes themselves complete asynchronously and are
@@ -871,26 +832,25 @@ static PFN_encodeTiled g_encode_tiled = nullptr;
 static PFN_encodeIm2col g_encode_im2col = nullptr;
 static int g_driver_version = 0;
 
-#ifdef FVM_CONV_TRACE
-extern "C" int fvm_conv_trace_read(long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_conv_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 3;
-}
-#endif
 
 // The driver API is reached through the runtime's entry-point query, so the library has no link-time dependency on
 // libcuda and still loads on a machine without a driver (where only symbol checks run).
 int conv_host_init() {
-    if (g_encode_tiled && g_encode_im2col) return FVM_OK;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
-        return FVM_ERR_SETUP;
-    g_encode_tiled = reinterpret_cast<PFN_encodeTiled>(fn);
-    fn = nullptr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
-        return FVM_ERR_SETUP;
-    g_encode_im2col = reinterpret_cast<PFN_encodeIm2col>(fn);
-    cudaDriverGetVersion(&g_driver_version);
+    // Called by fvm_init() once per device, with that device current and under the library's mutex. The driver entry
+    // points are looked up once per process; the shared-memory opt-in is a per-device attribute of the kernel and is
+    // set for every device that is initialised.
+    if (!g_encode_tiled || !g_encode_im2col) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+            return FVM_ERR_SETUP;
+        g_encode_tiled = reinterpret_cast<PFN_encodeTiled>(fn);
+        fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+            return FVM_ERR_SETUP;
+        g_encode_im2col = reinterpret_cast<PFN_encodeIm2col>(fn);
+        cudaDriverGetVersion(&g_driver_version);
+    }
     if (cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess)
         return FVM_ERR_SETUP;
@@ -1115,8 +1075,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (ldx < C || ldy < K || (res && ldr < K)) return FVM_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
         (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(res) & 15) ||
-        (reinterpret_cast<uintptr_t>(bias) & 15))
-        return FVM_ERR_ARG;
+        (reinterpret_cast<uintptr_t>(bias) & 15) || (reinterpret_cast<uintptr_t>(scale) & 15))
+        return FVM_ERR_ARG;      // bias is read as 16-byte vectors, scale as float4
     if (act < 0 || act > 6) return FVM_ERR_ARG;
     const int P = (H + ph + ph_hi - dh * (R - 1) - 1) / sh + 1;
     const int Q = (W + pw + pw_hi - dw * (S - 1) - 1) / sw + 1;

@@ -66,7 +66,8 @@ __device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
 // BACKOFF_NS > 0 puts the warp to sleep between polls: many-lane waiters (epilogue warps) then leave the issue slots
 // of their scheduler to the single-thread producer / MMA roles instead of spinning next to them.
 template <int BACKOFF_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;      // another wait of this CTA already gave up: do not wait again
     unsigned long long t0 = 0;
@@ -78,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             unsigned long long now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+            else if (now - t0 > limit_ns) { *abort_flag = 1; return false; }
         }
     }
 }

@@ -59,6 +59,21 @@ def last_status() -> int:
     return code.value
 
 
+def poll_status() -> int:
+    """The status word as it stands now, without synchronising (reads and clears it): non-zero means a kernel that has
+    already finished reported a fault. Cheap enough to call before every graph replay."""
+    code = ctypes.c_int(0)
+    _check(lib().fvm_last_status(ctypes.byref(code)), "last_status")
+    return code.value
+
+
+def selftest_wait_expiry(limit_us: int = 1000) -> None:
+    """Launches the library's fault-path self-test: a kernel whose bounded wait runs out after `limit_us` microseconds
+    and reports 0x1ff through the status word (read it with `last_status()`)."""
+    init()
+    _check(lib().fvm_selftest_wait_expiry(int(limit_us), _stream()), "selftest_wait_expiry")
+
+
 def launches() -> int:
     """Number of kernels this library has launched since it was loaded."""
     return int(lib().fvm_query(3))
@@ -191,9 +206,29 @@ def conv_fused_d(x, w, bias, res, padding, stride, dilation, act: int) -> torch.
     return conv_fused(x, w, bias, res, padding, stride, act, dilation=dilation)
 
 
-def pw(x, w, bias, act: int) -> torch.Tensor:
-    """clfr3::pw (classification/fast/csrc/r3.cu:758-765): 1x1 stride-1 conv; here the same tcgen05 kernel."""
-    return conv_fused(x, w, bias, None, (0, 0), (1, 1), act)
+def pw(x, w, bias=None, res=None, act: int = 0, force: int = 0) -> torch.Tensor:
+    """clfr3::pw(x, w, bias?, res?, act, force=0) (classification/fast/csrc/r3.cu:758-761, schema :797): 1x1 stride-1
+    conv, y = act(x . w^T + bias + res). The reference runs it as a cublasLt GEMM and uses `force` to pick between that
+    and its CUTLASS kernel; here it is the tcgen05 kernel either way and `force` is accepted and ignored."""
+    return conv_fused(x, w, bias, res, (0, 0), (1, 1), act)
+
+
+def pw_into(x, w, bias, res, act: int, out: torch.Tensor, force: int = 0) -> None:
+    """clfr3::pw_into(x, w, bias?, res?, act, out, force=0) (r3.cu:762-765): pw written into `out`, which may be a
+    channel slice of a wider channels-last buffer."""
+    conv_fused_into(x, w, bias, res, (0, 0), (1, 1), act, out)
+
+
+def conv_tc(x, w, bias=None, stride=(1, 1), pad=(0, 0), act: int = 0, cfg: int = -1) -> torch.Tensor:
+    """clfr3::conv_tc(x, w, bias?, stride, pad, act, cfg=-1) (r3.cu:801): dense KxK conv over few input channels
+    (C <= 48, C % 16 == 0 in the reference, which runs it on its grouped-conv kernel). Note the argument order: stride
+    before pad. Here every dense conv is the same kernel; 8- and 16-channel inputs take its tap-packed mode."""
+    return conv_fused(x, w, bias, None, pad, stride, act)
+
+
+def conv_tc_into(x, w, bias, stride, pad, act: int, out: torch.Tensor) -> None:
+    """clfr3::conv_tc_into(x, w, bias?, stride, pad, act, out) (r3.cu:802)."""
+    conv_fused_into(x, w, bias, None, pad, stride, act, out)
 
 
 def linear(x2d: torch.Tensor, w: torch.Tensor, bias=None, res2d=None, act: int = 0, scale=None) -> torch.Tensor:
@@ -237,7 +272,21 @@ def dwconv(x, w_rsc, bias=None, stride=(1, 1), padding=(0, 0), act: int = 0, dil
     return y
 
 
-dwconv2 = dwconv
+dwconv2 = dwconv      # clfr3::dwconv2(x, w_rsc, bias?, stride, padding, act): same schema (r3.cu:803)
+dwconv8 = dwconv      # segx::dwconv8(x, w_rsc, bias?, stride, padding, act) (segmentation/fast/csrc/segx_conv.cu:624)
+
+
+def segx_dwconv(x, wt, bias, kh: int, kw: int, stride, padding, dilation, act: int) -> torch.Tensor:
+    """segx::dwconv(x, wt, bias?, kh, kw, stride, padding, dilation, act) (segmentation/fast/csrc/segx_ops.cu:45-57):
+    depthwise conv with any kernel size / stride / padding / dilation; `wt` is fp16 [kh*kw, C] tap-major. In this op
+    `act` is 0 = none, 1 = GELU (erf) (segmentation/fast/seg_kernels.cu:151-154), not the clf activation table."""
+    if act not in (0, 1):
+        raise FvmError("segx::dwconv: act is 0 (none) or 1 (erf GELU)")
+    C = x.shape[1]
+    if wt.dim() != 2 or tuple(wt.shape) != (int(kh) * int(kw), C):
+        raise FvmError(f"segx::dwconv: wt must be [kh*kw, C] = {(int(kh) * int(kw), C)}, got {tuple(wt.shape)}")
+    return dwconv(x, wt.contiguous().view(int(kh), int(kw), C), bias, stride, padding, ACT_GELU_ERF if act == 1 else ACT_NONE,
+                  dilation=dilation)
 
 
 # ------------------------------------------------------------------------------------------------ pooling
@@ -267,8 +316,10 @@ def maxpool(x, k, stride, pad, ceil: bool = False) -> torch.Tensor:
     return y
 
 
-def avgpool(x, k, stride, pad, ceil: bool = False, count_include_pad: bool = True) -> torch.Tensor:
-    """clf::avgpool(x, k, stride, pad, ceil, count_include_pad) (fused_conv.cu:584-594)."""
+def avgpool(x, k, stride, pad, count_include_pad: bool = True, *, ceil: bool = False) -> torch.Tensor:
+    """clf::avgpool(x, k, stride, pad, count_include_pad=True) (fused_conv.cu:584-594, schema :626): the fifth
+    positional argument is count_include_pad, as in the reference, whose op always uses the floor rule for the output
+    size; `ceil` (keyword only) is this library's extension for ceil-mode pools."""
     init(x.device)
     x, N, C, H, W, ldx = nhwc_view(x, "x")
     if ldx != C:
@@ -279,7 +330,7 @@ def avgpool(x, k, stride, pad, ceil: bool = False, count_include_pad: bool = Tru
     P, Q = _pool_out(H, kh, sh, ph, ceil), _pool_out(W, kw, sw, pw_, ceil)
     y = empty_nhwc(N, C, P, Q, x.device)
     _check(lib().fvm_avgpool_f16(x.data_ptr(), y.data_ptr(), N, H, W, C, kh, kw, sh, sw, ph, pw_, P, Q,
-                                 int(count_include_pad), _stream()), "avgpool_f16")
+                                 int(bool(count_include_pad)), _stream()), "avgpool_f16")
     return y
 
 
@@ -362,14 +413,15 @@ def layernorm_cl(x, weight, bias, eps: float = 1e-6) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------------ elementwise
 def input_nhwc8(x: torch.Tensor) -> torch.Tensor:
-    """clf::input_nhwc8(x) (fused_conv.cu:608-620): fp32 NCHW (C<=8) -> fp16 channels-last with C padded to 8."""
+    """clf::input_nhwc8(x) (fused_conv.cu:608-620): fp32 or fp16 NCHW (C<=8) -> fp16 channels-last, C padded to 8."""
     init(x.device)
-    if not x.is_cuda or x.dtype != torch.float32:
-        raise FvmError("input_nhwc8: expected an fp32 CUDA tensor")
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.float16):
+        raise FvmError("input_nhwc8: expected an fp32 or fp16 CUDA tensor")
     x = x.contiguous()
     N, C, H, W = x.shape
     y = empty_nhwc(N, 8, H, W, x.device)
-    _check(lib().fvm_input_nhwc8_f32(x.data_ptr(), y.data_ptr(), N, C, H, W, _stream()), "input_nhwc8_f32")
+    fn = lib().fvm_input_nhwc8_f32 if x.dtype == torch.float32 else lib().fvm_input_nhwc8_f16
+    _check(fn(x.data_ptr(), y.data_ptr(), N, C, H, W, _stream()), "input_nhwc8")
     return y
 
 
@@ -377,14 +429,15 @@ def input_nhwc8_split(x: torch.Tensor) -> torch.Tensor:
     """input_nhwc8 into two column-parity planes per image row: returns fp16 [N, H, 2, W/2, 8] with
     out[n, h, w & 1, w >> 1, c] = x[n, c, h, w] (channels zero-padded to 8). Input layout of `stem_conv_s2`."""
     init(x.device)
-    if not x.is_cuda or x.dtype != torch.float32:
-        raise FvmError("input_nhwc8_split: expected an fp32 CUDA tensor")
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.float16):
+        raise FvmError("input_nhwc8_split: expected an fp32 or fp16 CUDA tensor")
     x = x.contiguous()
     N, C, H, W = x.shape
     if W % 2:
         raise FvmError("input_nhwc8_split: the width must be even")
     y = torch.empty((N, H, 2, W // 2, 8), dtype=torch.float16, device=x.device)
-    _check(lib().fvm_input_nhwc8_split_f32(x.data_ptr(), y.data_ptr(), N, C, H, W, _stream()), "input_nhwc8_split_f32")
+    fn = lib().fvm_input_nhwc8_split_f32 if x.dtype == torch.float32 else lib().fvm_input_nhwc8_split_f16
+    _check(fn(x.data_ptr(), y.data_ptr(), N, C, H, W, _stream()), "input_nhwc8_split")
     return y
 
 
@@ -475,6 +528,48 @@ def upsample_bilinear(x, H: int, W: int, sf_h: Optional[float] = None, sf_w: Opt
     _check(lib().fvm_bilinear_f16(x.data_ptr(), _ptr(base), y.data_ptr(), N, h, w, C, H, W, int(align),
                                   float(sf_h or 0.0), float(sf_w or 0.0), int(relu), ldx, ldy, _stream()), "bilinear_f16")
     return y
+
+
+def upsample_like(x, ref, align: bool = False) -> torch.Tensor:
+    """segx::upsample_like(x, ref, align) (segx_ops.cu:160-162): bilinear resize of x to ref's height and width."""
+    return upsample_bilinear(x, int(ref.shape[2]), int(ref.shape[3]), None, None, align)
+
+
+def upsample_bilinear_t(x, size: torch.Tensor, align: bool = False) -> torch.Tensor:
+    """segx::upsample_bilinear_t(x, size, align) (segx_ops.cu:166-169): the target size comes as an integer tensor [2]
+    (the reference builds it from traced sizes so that a TorchScript trace stays shape-generic)."""
+    hw = size.to("cpu", torch.int64).reshape(-1).tolist()
+    if len(hw) != 2:
+        raise FvmError("upsample_bilinear_t: size must hold (H, W)")
+    return upsample_bilinear(x, int(hw[0]), int(hw[1]), None, None, align)
+
+
+def _upsample_add(base, z, sf: float, relu: bool, inplace: bool) -> torch.Tensor:
+    import math
+    N, C, H, W = base.shape
+    h, w = z.shape[2], z.shape[3]
+    if z.shape[1] != C:
+        raise FvmError("upsample_add: base and z must have the same channel count")
+    bv, *_b, ldb = nhwc_view(base, "base")
+    if inplace and (bv is not base or ldb != C):
+        raise FvmError("upsample_add_: base must be a contiguous channels-last tensor")
+    out = base if inplace else None
+    if math.floor(h * sf) == H and math.floor(w * sf) == W:
+        # one pass: the resize by `sf` lands exactly on base's size (segx_ops.cu:205-216: source scale 1 / sf)
+        return upsample_bilinear(z, H, W, sf, sf, False, base=bv, relu=relu, out=out)
+    # composite of the reference (segx_ops.cu:209-214): resize by sf, resize again to base's size, add, ReLU
+    u = upsample_bilinear(z, int(math.floor(h * sf)), int(math.floor(w * sf)), sf, sf, False)
+    return upsample_bilinear(u, H, W, None, None, False, base=bv, relu=relu, out=out)
+
+
+def upsample_add(base, z, sf: float, relu: bool = False) -> torch.Tensor:
+    """segx::upsample_add(base, z, sf, relu) (segx_ops.cu:200-218): relu?(base + half(bilinear(z, scale_factor sf)))."""
+    return _upsample_add(base, z, float(sf), bool(relu), False)
+
+
+def upsample_add_(base, z, sf: float, relu: bool = False) -> torch.Tensor:
+    """segx::upsample_add_(base, z, sf, relu): the same, written into `base`."""
+    return _upsample_add(base, z, float(sf), bool(relu), True)
 
 
 def up_argmax(s, H: int, W: int, align: bool = False, num_classes: Optional[int] = None) -> torch.Tensor:

@@ -16,7 +16,7 @@ import torch
 from torch import nn
 
 from .. import ops
-from ..classification.fast import ResNetTrunk
+from ..classification.fast import ResNetTrunk, as_image
 from ..layers import FusedConv
 from ..runtime import GraphRunner
 
@@ -75,19 +75,19 @@ class FastSeg(nn.Module):
     def __init__(self, net: B200DeepLabV3, graphs: bool = True):
         super().__init__()
         self.net = net
-        self._logits = GraphRunner(lambda x: self.net(x), enabled=graphs)
-        self._classmap = GraphRunner(lambda x: self.net.classmap(x), enabled=graphs)
+        self._logits = GraphRunner(lambda x: self.net(x), enabled=graphs, chainable=True)
+        self._classmap = GraphRunner(lambda x: self.net.classmap(x), enabled=graphs, chainable=True)
         self.info = {"tier": "b200", "fused_upsample_argmax": True}
 
     @torch.no_grad()
     def logits(self, x: torch.Tensor) -> torch.Tensor:
-        return self._logits(x.float().contiguous())
+        return self._logits(as_image(x))
 
     @torch.no_grad()
     def predict(self, x: torch.Tensor, out_size=None) -> torch.Tensor:
         if out_size is not None and tuple(out_size) != tuple(x.shape[2:]):
-            s = self.net.logits_nhwc(x.float().contiguous())
+            s = self.net.logits_nhwc(as_image(x))
             return ops.up_argmax(s, int(out_size[0]), int(out_size[1]), align=False, num_classes=self.net.num_classes)
-        return self._classmap(x.float().contiguous())
+        return self._classmap(as_image(x))
 
     forward = logits

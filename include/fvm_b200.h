@@ -50,12 +50,19 @@ long long fvm_query(int what);
 /* Reads and clears the asynchronous status word of the current device (0 = no fault). Call after synchronising. */
 int fvm_last_status(int* code);
 
+/* Self-test of the fault path -- no counterpart in the reference (its kernels have no device-side waits). Launches one
+ * small kernel whose only thread waits, for at most limit_us microseconds (1..100000), on a barrier that nothing arrives
+ * at; the wait runs out, the kernel writes 0x1ff to the status word and returns. After a synchronise fvm_last_status
+ * reports 0x1ff and the device is as usable as before. */
+int fvm_selftest_wait_expiry(int limit_us, void* stream);
+
 /* Dense convolution / GEMM with fused epilogue -- replaces clf::conv_fused / conv_fused_into
  * (classification/fast/csrc/fused_conv.cu:231-306), segx::conv_fused_d (segmentation/fast/csrc/segx_conv.cu:231-299)
  * and clfr3::pw (classification/fast/csrc/r3.cu:633-765):
  *   y[n,p,q,k] = act( (sum_{r,s,c} x[n, p*sh-ph+r*dh, q*sw-pw+s*dw, c] * w[k,r,s,c] + bias[k]) * scale[k] + res[n,p,q,k] )
  * fp16 operands, fp32 accumulation (TMEM), fp32 epilogue, one rounding to fp16. bias, scale (fp32 [K], a LayerScale
- * that was not folded into w) and res may be NULL. Requires C % 8 == 0 and K % 8 == 0. */
+ * that was not folded into w) and res may be NULL. Requires C % 8 == 0 and K % 8 == 0; x, w, y, res, bias AND scale
+ * must be 16-byte aligned (scale is read as float4): a misaligned pointer returns 1 before anything is launched. */
 int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y,
                    int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                    long long ldx, long long ldy, long long ldr, int act, void* stream);
@@ -129,13 +136,15 @@ int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C
 int fvm_layernorm_cl_f16(const void* x, const void* gamma, const void* beta, void* y, long long rows, int C, float eps,
                          long long ldx, long long ldy, void* stream);
 
-/* fp32 NCHW [N,C,H,W] (C <= 8) -> fp16 NHWC with channels zero-padded to 8 -- replaces clf::input_nhwc8
- * (fused_conv.cu:597-620). */
+/* fp32 or fp16 NCHW [N,C,H,W] (C <= 8) -> fp16 NHWC with channels zero-padded to 8 -- replaces clf::input_nhwc8
+ * (fused_conv.cu:597-620, a template over float and __half inputs: one entry point per input type here). */
 int fvm_input_nhwc8_f32(const float* x, void* y, int N, int C, int H, int W, void* stream);
+int fvm_input_nhwc8_f16(const void* x, void* y, int N, int C, int H, int W, void* stream);
 
 /* The same conversion into two column-parity planes per image row, y[n][h][w & 1][w >> 1][8] (W even): the input
  * layout of fvm_stem_conv_s2_f16. Same bytes as the NHWC8 tensor, columns regrouped. */
 int fvm_input_nhwc8_split_f32(const float* x, void* y, int N, int C, int H, int W, void* stream);
+int fvm_input_nhwc8_split_f16(const void* x, void* y, int N, int C, int H, int W, void* stream);
 
 /* Stride-2 stem convolution on that layout: y[N,P,Q,K] (row stride ldy) = act(conv(x, w) + bias), w [K][R][S][8]
  * (input channels zero-padded to 8), padding (ph, pw) on both sides, stride 2 in both directions, R, S <= 8,

@@ -107,3 +107,86 @@ def test_backbones_registry_features():
         f, u = fast.fn(x), up.fn(x)
         assert f.shape == u.shape
         assert rel_l2(f, u) < TOL
+
+
+# ---------------------------------------------------------------------------------------- benchmark-sized configurations
+def _upstream_in_chunks(model, x, chunk=16):
+    outs = []
+    with torch.inference_mode():
+        for i in range(0, x.shape[0], chunk):
+            outs.append(model(x[i:i + chunk]))
+    return torch.cat(outs)
+
+
+def _argmax_agreement(y, ref):
+    """(raw agreement, agreement when a disagreement between two classes whose reference scores are closer than twice
+    the largest observed score error counts as a tie). y, ref: [items, classes]."""
+    y, ref = y.float(), ref.float()
+    a, b = y.argmax(1), ref.argmax(1)
+    raw = float((a == b).float().mean())
+    err = float((y - ref).abs().max())
+    gap = (ref.gather(1, b[:, None]) - ref.gather(1, a[:, None])).squeeze(1)      # >= 0; 0 where they agree
+    tie = (a != b) & (gap <= 2 * err)
+    return raw, float(((a == b) | tie).float().mean())
+
+
+@pytest.mark.parametrize("name,size,ls", [("efficientnet_b4", 380, None), ("convnext_tiny", 224, 1e-6),
+                                          ("convnext_tiny", 224, "uniform")])
+def test_classifiers_at_benchmark_size_agree_with_upstream_fp32_and_portable(name, size, ls):
+    # batch 64 at the network's native resolution: every depthwise / LayerNorm / squeeze-excite tile shape of the
+    # benchmark configuration is exercised; compared on the device with the upstream fp32 model and the portable tier
+    x = seeded_input((64, 3, size, size), seed=0).cuda()
+    fast = zoo.load(name, "b200", device="cuda", seed=1, layer_scale=ls).model(x)
+    from fast_vision_models_b200 import ops
+    assert ops.last_status() == 0
+    up = zoo.load(name, "upstream", device="cuda", seed=1, layer_scale=ls).model
+    y32 = _upstream_in_chunks(up, x)
+    del up
+    port_m = zoo.load(name, "portable", device="cuda", seed=1, layer_scale=ls).model
+    port = torch.cat([port_m(x[i:i + 16]) for i in range(0, 64, 16)])
+    del port_m
+    torch.cuda.empty_cache()
+    assert torch.isfinite(fast).all()
+    e32, eport = rel_l2(fast, y32), rel_l2(fast, port)
+    raw32, tie32 = _argmax_agreement(fast, y32)
+    rawp, tiep = _argmax_agreement(fast, port)
+    print(f"{name}@{size} ls={ls}: rel-L2 vs fp32 {e32:.2e}, vs portable {eport:.2e}; argmax vs fp32 {raw32:.4f} "
+          f"(ties resolved {tie32:.4f}), vs portable {rawp:.4f} ({tiep:.4f})")
+    assert e32 < TOL and eport < TOL
+    assert tie32 >= 0.995 and tiep >= 0.995 and raw32 >= 0.95
+
+
+def test_deeplabv3_at_benchmark_size_pixel_agreement():
+    # batch 8 of 512x1024: low-resolution logits against upstream fp32 and the portable tier, and the int32 class map
+    # of the fused upsample+argmax kernel against argmax(interpolate(fp32 logits)) over all 8*512*1024 pixels
+    from fast_vision_models_b200 import ops
+    from fast_vision_models_b200.segmentation import zoo as segzoo
+    x = seeded_input((8, 3, 512, 1024), seed=0).cuda()
+    w = segzoo.build("deeplabv3-r50", "b200", device="cuda", num_classes=19, seed=1)
+    logits = w.logits(x)
+    cm = w.predict(x)
+    assert ops.last_status() == 0
+    assert logits.shape == (8, 19, 64, 128) and cm.shape == (8, 512, 1024) and cm.dtype == torch.int32
+    up = segzoo.build("deeplabv3-r50", "upstream", device="cuda", num_classes=19, seed=1)
+    y32 = torch.cat([up.logits(x[i:i + 2]) for i in range(0, 8, 2)])
+    port = segzoo.build("deeplabv3-r50", "portable", device="cuda", num_classes=19, seed=1)
+    yp = torch.cat([port.logits(x[i:i + 2]) for i in range(0, 8, 2)])
+    e32, ep = rel_l2(logits, y32), rel_l2(logits, yp)
+    agree = []
+    margins = []
+    for i in range(8):
+        full = torch.nn.functional.interpolate(y32[i:i + 1], size=(512, 1024), mode="bilinear", align_corners=False)[0]
+        want = full.argmax(0)
+        same = cm[i].long() == want
+        agree.append(float(same.float().mean()))
+        top2 = full.topk(2, dim=0).values
+        margins.append((top2[0] - top2[1])[~same].flatten().cpu())
+    margins = torch.cat(margins)
+    pixel = sum(agree) / len(agree)
+    hist = torch.histc(margins, bins=5, min=0.0, max=0.05).int().tolist() if margins.numel() else []
+    scale = float(y32.abs().max())
+    print(f"deeplabv3 b8@512x1024: logits rel-L2 vs fp32 {e32:.2e}, vs portable {ep:.2e}; pixel argmax agreement "
+          f"{pixel:.5f} over {8 * 512 * 1024} pixels; fp32 top-2 margins at the {margins.numel()} disagreeing pixels "
+          f"(5 bins over [0, 0.05], logit scale {scale:.2f}): {hist}, max {float(margins.max()) if margins.numel() else 0:.4f}")
+    assert e32 < TOL and ep < TOL
+    assert pixel >= 0.995

@@ -295,6 +295,42 @@ def test_conv_linearity_at_full_size():
     assert rel_l2(y12, y1.float() + y2.float()) < 2e-3
 
 
+SWEEP_CASES = [(r, c, h) for r in (1, 3) for c in (64, 128, 256, 512) for h in (56, 28, 14, 7)]
+
+
+@pytest.mark.parametrize("r,c,h", SWEEP_CASES)
+def test_conv_sweep_at_batch_64(r, c, h):
+    # The single-op sweep at its real size: N = 64, C_in = C_out = c, H = W = h, 1x1 (pad 0) and 3x3 (pad 1), stride 1,
+    # input N(0,1), weights N(0,0.02), epilogue = folded-BatchNorm bias + residual N(0,1) + ReLU. The kernel flattens
+    # the output pixels of all images into one row dimension, so tiles straddle image boundaries: the CPU oracle
+    # checks the first, a middle and the last image, an fp32 convolution on the device checks the whole tensor.
+    N, pad = 64, r // 2
+    i = SWEEP_CASES.index((r, c, h))
+    g = torch.Generator().manual_seed(10 + i)
+    x = torch.randn((N, c, h, h), generator=g).half()
+    w = (torch.randn((c, c, r, r), generator=g) * 0.02).half()
+    res = torch.randn((N, c, h, h), generator=g).half()
+    # bias of a BatchNorm folded with gamma ~ U(0.5,1.5), beta ~ N(0,0.1), mean ~ N(0,0.1), var ~ U(0.5,1.5)
+    gamma, beta = torch.rand(c, generator=g) + 0.5, torch.randn(c, generator=g) * 0.1
+    mean, var = torch.randn(c, generator=g) * 0.1, torch.rand(c, generator=g) + 0.5
+    b = (beta - mean * gamma / torch.sqrt(var + 1e-5)).half()
+    xd, wd, rd, bd = cl(x), cl(w), cl(res), b.to(DEV)
+    y = ops.conv_fused(xd, wd, bd, rd, (pad, pad), (1, 1), ops.ACT_RELU)
+    assert ops.last_status() == 0
+    for img in (0, 31, 63):
+        ref = R.conv_fused_ref(x[img:img + 1], w, b, res[img:img + 1], (pad, pad), (1, 1), 1)
+        close(y[img:img + 1], ref)
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        full = torch.nn.functional.conv2d(xd.float(), wd.float(), bd.float(), 1, pad) + rd.float()
+    finally:
+        torch.backends.cudnn.allow_tf32 = old
+    full = full.clamp_min(0)
+    assert rel_l2(y, full) < TOL_REL_L2
+    assert float((y.float() - full).abs().max()) <= 4 * TOL_ULP * float(full.abs().max()) + 1e-3
+
+
 def test_conv_rejects_bad_arguments():
     x = cl(gen((1, 12, 4, 4), 1))        # C not a multiple of 8
     w = cl(gen((8, 12, 1, 1), 2))
@@ -338,7 +374,7 @@ def test_pools_match_oracle(shape, k, s, p, ceil):
     y = ops.maxpool(cl(x), k, s, p, ceil)
     assert torch.equal(y.cpu().float(), R.maxpool_ref(x, k, s, p, ceil).float())    # max is exact
     for cip in (True, False):
-        close(ops.avgpool(cl(x), k, s, p, ceil, cip), R.avgpool_ref(x, k, s, p, ceil, cip))
+        close(ops.avgpool(cl(x), k, s, p, cip, ceil=ceil), R.avgpool_ref(x, k, s, p, ceil, cip))
 
 
 @pytest.mark.parametrize("shape", [(64, 2048, 7, 7), (2, 144, 95, 95), (3, 8, 1, 1), (2, 1792, 12, 12), (1, 48, 190, 190)])
