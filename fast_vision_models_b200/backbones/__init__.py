@@ -77,7 +77,7 @@ def build(name: str, tier: str = "cuda-kernels", spec=None, device: str = "cuda"
     else:
         def raw(x):
             return net.features(x).float().contiguous()
-    runner = GraphRunner(raw, enabled=graphs, chainable=True)
+    runner = GraphRunner(raw, enabled=graphs)
 
     def fn(x):
         with torch.no_grad():

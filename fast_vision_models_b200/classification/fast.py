@@ -127,8 +127,8 @@ class MBConvBlock(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self.expand(x) if self.expand is not None else x
-        y = self.dw(y)
-        y = self.se(y)
+        y, partial = self.dw(y, pool=True)      # the squeeze sums come out of the depthwise conv's epilogue
+        y = self.se(y, partial)
         # eval-mode stochastic depth is the identity: the residual add rides in the project conv's epilogue
         return self.project(y, res=x if self.use_res else None)
 
@@ -238,7 +238,7 @@ class Fast(nn.Module):
     def __init__(self, net: nn.Module, graphs: bool = True):
         super().__init__()
         self.net = net
-        self._runner = GraphRunner(self._run, enabled=graphs, chainable=True)
+        self._runner = GraphRunner(self._run, enabled=graphs)
 
     def _run(self, x: torch.Tensor) -> torch.Tensor:
         return self.net(x)

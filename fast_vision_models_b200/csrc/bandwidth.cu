@@ -221,14 +221,19 @@ static int gap_splits(int N, int HW, int C, int sms) {
 __global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __restrict__ w1,
                                const __half* __restrict__ b1, const __half* __restrict__ w2,
                                const __half* __restrict__ b2, __half* __restrict__ s_out, int C, int Cs, int act,
-                               float mean_scale) {
+                               float mean_scale, int slots) {
     extern __shared__ float sm[];
     float* g = sm;          // [C]
     float* h = sm + C;      // [Cs]
     const long long n = blockIdx.x;
     if (mean_scale != 0.f) {
-        const float* gs = static_cast<const float*>(g_in) + n * C;
-        for (int c = threadIdx.x; c < C; c += blockDim.x) g[c] = __half2float(__float2half_rn(gs[c] * mean_scale));
+        // fused squeeze: fp32 partial sums [slots][C] of this image, added in slot order, times 1 / pixels
+        const float* gs = static_cast<const float*>(g_in) + n * slots * C;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float sum = 0.f;
+            for (int k = 0; k < slots; ++k) sum += gs[static_cast<long long>(k) * C + c];
+            g[c] = __half2float(__float2half_rn(sum * mean_scale));
+        }
     } else {
         const __half* gh = static_cast<const __half*>(g_in) + n * C;
         for (int c = threadIdx.x; c < C; c += blockDim.x) g[c] = __half2float(gh[c]);
@@ -640,9 +645,9 @@ extern "C" int fvm_global_avgpool_f16(const void* x, void* y, float* partial, in
     FVM_LAUNCH_CHECK();
 }
 
-extern "C" int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, const void* w2, const void* b2, void* s,
-                               int N, int C, int Cs, int act, float mean_scale, void* stream) {
-    if (!g || !w1 || !w2 || !s || N <= 0 || C <= 0 || Cs <= 0 || (C & 7) || (Cs & 7) || act < 0 || act > 6 ||
+static int se_gate_launch(const void* g, int slots, const void* w1, const void* b1, const void* w2, const void* b2, void* s,
+                          int N, int C, int Cs, int act, float mean_scale, void* stream) {
+    if (!g || !w1 || !w2 || !s || N <= 0 || C <= 0 || Cs <= 0 || (C & 7) || (Cs & 7) || act < 0 || act > 6 || slots < 1 ||
         !aligned16(w1) || !aligned16(w2))
         return FVM_ERR_ARG;
     const size_t smem = static_cast<size_t>(C + Cs) * sizeof(float);
@@ -653,8 +658,20 @@ extern "C" int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, co
     while (split < 4 && N * split * 2 <= 2 * sms && C / (split * 2) >= 256) split *= 2;
     se_gate_kernel<<<dim3(N, split), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         g, static_cast<const __half*>(w1), static_cast<const __half*>(b1), static_cast<const __half*>(w2),
-        static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale);
+        static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale, slots);
     FVM_LAUNCH_CHECK();
+}
+
+extern "C" int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, const void* w2, const void* b2, void* s,
+                               int N, int C, int Cs, int act, float mean_scale, void* stream) {
+    return se_gate_launch(g, 1, w1, b1, w2, b2, s, N, C, Cs, act, mean_scale, stream);
+}
+
+extern "C" int fvm_se_gate_pooled_f16(const float* partial, int slots, const void* w1, const void* b1, const void* w2,
+                                      const void* b2, void* s, int N, int C, int Cs, int act, float mean_scale,
+                                      void* stream) {
+    if (mean_scale == 0.f) return FVM_ERR_ARG;
+    return se_gate_launch(partial, slots, w1, b1, w2, b2, s, N, C, Cs, act, mean_scale, stream);
 }
 
 extern "C" int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C, void* stream) {

@@ -857,6 +857,24 @@ int conv_host_init() {
     return FVM_OK;
 }
 
+int encode_tiled_f16(CUtensorMap* map, const void* ptr, int rank, const unsigned long long* dims,
+                     const unsigned long long* strides_bytes, const unsigned* box, bool swizzle128) {
+    if (!g_encode_tiled || rank < 1 || rank > 5) return FVM_ERR_SETUP;
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        es[i] = 1;
+        if (i + 1 < rank) st[i] = strides_bytes[i];
+    }
+    const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(ptr),
+                                      d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FVM_OK : FVM_ERR_TMAP;
+}
+
 // Shared-memory plan for an output-channel tile of BN: staging buffers for the residual/output tiles first (3 if the
 // main loop still gets enough stages, else 2), then the zero-padded bias copy, the rest goes to the A/B pipeline.
 struct SmemPlan {

@@ -1,5 +1,6 @@
 // Internal declarations shared by the translation units of libfvm_b200 (not part of the C ABI).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "../../include/fvm_b200.h"
@@ -19,6 +20,10 @@ DeviceState* device_state();
 void count_launch();
 
 int conv_host_init();
+// cuTensorMapEncodeTiled for an fp16 tensor of `rank` dimensions (innermost first): sizes, byte strides of dimensions
+// 1.., box; no interleave, 128-byte swizzle or none, zero fill outside the tensor. Returns an FVM_* status.
+int encode_tiled_f16(CUtensorMap* map, const void* ptr, int rank, const unsigned long long* dims,
+                     const unsigned long long* strides_bytes, const unsigned* box, bool swizzle128);
 int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K, int R, int S,
                    int ph, int pw, long long ldy, int act, cudaStream_t stream);
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,

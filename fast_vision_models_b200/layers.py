@@ -15,6 +15,7 @@ from . import fold, ops
 
 AUTOTUNE = os.environ.get("FVM_B200_AUTOTUNE", "1") != "0"
 PAIR_STEMS = os.environ.get("FVM_B200_PAIR_STEMS", "1") != "0"   # run RGB stems over column pairs (16-channel taps)   # kill switch, in the style of the reference's CLF_* variables
+FUSED_SQUEEZE = os.environ.get("FVM_B200_FUSED_SQUEEZE", "1") != "0"   # squeeze sums from the depthwise conv's epilogue
 SPLIT_STEMS = os.environ.get("FVM_B200_SPLIT_STEMS", "1") != "0"   # stride-2 RGB stems on column-parity planes
 
 _ACT_CODES = {
@@ -218,9 +219,9 @@ class DepthwiseConv(nn.Module):
         self.register_buffer("b", b.half().contiguous())
         self.stride, self.padding, self.dilation, self.act = conv.stride, conv.padding, conv.dilation, int(act)
 
-    def forward(self, x: torch.Tensor, pool_sums: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return ops.dwconv(x, self.w, self.b, self.stride, self.padding, self.act, dilation=self.dilation,
-                          pool_sums=pool_sums)
+    def forward(self, x: torch.Tensor, pool: bool = False):
+        """pool=True: returns (y, partial sums per tile) for a squeeze-excite block that follows (fused squeeze)."""
+        return ops.dwconv(x, self.w, self.b, self.stride, self.padding, self.act, dilation=self.dilation, pool=pool)
 
 
 class SqueezeExcite(nn.Module):
@@ -250,9 +251,14 @@ class SqueezeExcite(nn.Module):
         self.register_buffer("b2", b2.half().contiguous())
         self.act = int(act)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        g = ops.global_avgpool(x)
-        s = ops.se_gate(g, self.w1, self.b1, self.w2, self.b2, self.act)
+    def forward(self, x: torch.Tensor, partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`partial`: the per-tile sums the producing depthwise conv emitted (`DepthwiseConv.forward(pool=True)`); the
+        squeeze then costs no pass over x (the reference's fused form: gconv2_pool + sums_to_mean_k, r3.cu:181-203,
+        283-299). Without it the squeeze is a global average pool of x."""
+        if partial is not None and FUSED_SQUEEZE:
+            s = ops.se_gate_pooled(partial, x.shape[2] * x.shape[3], self.w1, self.b1, self.w2, self.b2, self.act)
+        else:
+            s = ops.se_gate(ops.global_avgpool(x), self.w1, self.b1, self.w2, self.b2, self.act)
         return ops.se_scale(x, s)
 
 

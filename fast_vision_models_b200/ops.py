@@ -247,9 +247,11 @@ def linear(x2d: torch.Tensor, w: torch.Tensor, bias=None, res2d=None, act: int =
 
 # ------------------------------------------------------------------------------------------------ depthwise
 def dwconv(x, w_rsc, bias=None, stride=(1, 1), padding=(0, 0), act: int = 0, dilation=(1, 1),
-           pool_sums: Optional[torch.Tensor] = None) -> torch.Tensor:
+           pool: bool = False):
     """clf::dwconv(x, w_rsc, bias?, stride, padding, act) (fused_conv.cu:480-502) / clfr3::dwconv2 (r3.cu:423-454) /
-    segx::dwconv with dilation (segx_ops.cu:45-57). w_rsc is [R,S,C] contiguous."""
+    segx::dwconv with dilation (segx_ops.cu:45-57). w_rsc is [R,S,C] contiguous.
+    With `pool=True` returns (y, partial): `partial` is fp32 [N, slots, C], per-tile sums of the rounded outputs (the
+    fused squeeze of a squeeze-excite block, cf. clfr3::gconv2_pool r3.cu:181-203); `se_gate_pooled` consumes it."""
     init(x.device)
     x, N, C, H, W, ldx = nhwc_view(x, "x")
     _require_cuda_half(w_rsc, "w_rsc")
@@ -265,11 +267,15 @@ def dwconv(x, w_rsc, bias=None, stride=(1, 1), padding=(0, 0), act: int = 0, dil
     y = empty_nhwc(N, C, P, Q, x.device)
     if bias is not None:
         bias = bias.contiguous()
-    if pool_sums is not None and (pool_sums.dtype != torch.float32 or pool_sums.numel() != N * C):
-        raise FvmError("dwconv: pool_sums must be fp32 [N,C]")
-    _check(lib().fvm_dwconv_f16(x.data_ptr(), w_rsc.data_ptr(), _ptr(bias), y.data_ptr(), _ptr(pool_sums), N, H, W, C,
+    partial = None
+    if pool:
+        slots = int(lib().fvm_dwconv_pool_slots(H, W, C, R, S, ph, pw_, sh, sw, dh, dw))
+        if slots <= 0:
+            raise FvmError("dwconv: unsupported geometry")
+        partial = torch.empty((N, slots, C), dtype=torch.float32, device=x.device)
+    _check(lib().fvm_dwconv_f16(x.data_ptr(), w_rsc.data_ptr(), _ptr(bias), y.data_ptr(), _ptr(partial), N, H, W, C,
                                 R, S, ph, pw_, sh, sw, dh, dw, ldx, C, int(act), _stream()), "dwconv_f16")
-    return y
+    return (y, partial) if pool else y
 
 
 dwconv2 = dwconv      # clfr3::dwconv2(x, w_rsc, bias?, stride, padding, act): same schema (r3.cu:803)
@@ -373,6 +379,25 @@ def se_gate(g, w1, b1, w2, b2, act: int = ACT_SILU, mean_scale: float = 0.0) -> 
     s = torch.empty((N, C), dtype=torch.float16, device=g.device)
     _check(lib().fvm_se_gate_f16(g.data_ptr(), w1.data_ptr(), _ptr(b1), w2.data_ptr(), _ptr(b2), s.data_ptr(), N, C, Cs,
                                  int(act), float(mean_scale), _stream()), "se_gate_f16")
+    return s.view(N, C, 1, 1)
+
+
+def se_gate_pooled(partial, pixels: int, w1, b1, w2, b2, act: int = ACT_SILU) -> torch.Tensor:
+    """The gate fed by the fused squeeze of `dwconv(..., pool=True)`: partial fp32 [N, slots, C] -> s [N,C,1,1] fp16
+    with g = half(sum over slots / pixels) (deterministic: the slots are added in order)."""
+    init(partial.device)
+    if partial.dtype != torch.float32 or partial.dim() != 3 or not partial.is_cuda:
+        raise FvmError("se_gate_pooled: partial must be an fp32 CUDA tensor [N, slots, C]")
+    partial = partial.contiguous()
+    N, slots, C = partial.shape
+    w1 = w1.reshape(w1.shape[0], -1).contiguous()
+    w2 = w2.reshape(w2.shape[0], -1).contiguous()
+    Cs = w1.shape[0]
+    if w1.shape[1] != C or tuple(w2.shape) != (C, Cs):
+        raise FvmError("se_gate_pooled: weight shapes do not match")
+    s = torch.empty((N, C), dtype=torch.float16, device=partial.device)
+    _check(lib().fvm_se_gate_pooled_f16(partial.data_ptr(), slots, w1.data_ptr(), _ptr(b1), w2.data_ptr(), _ptr(b2),
+                                        s.data_ptr(), N, C, Cs, int(act), 1.0 / float(pixels), _stream()), "se_gate_pooled_f16")
     return s.view(N, C, 1, 1)
 
 

@@ -6,18 +6,15 @@ launch on the current stream, so the forward is captured once per (shape, dtype,
 launches of a network cost one graph launch. Activation memory comes from the graph's private pool of torch's caching
 allocator and is reused between layers.
 
-Image chains. Inference has no cross-image op, so a batch may be cut into `chains` equal groups of images that run
-the same network as independent kernel sequences on separate streams inside the one graph. A convolution over a
-14x14 or 7x7 map has fewer output tiles than the GPU has SMs, and every kernel boundary drains the machine; with
-several chains in flight the tiles of one chain's layer fill the SMs another chain leaves idle. The number of chains
-per shape is chosen once by timing the captured graphs (FVM_B200_CHAINS forces it).
+Faults: a kernel whose bounded device-side wait ran out writes a code to the device's status word and returns; the
+runner polls that word (no synchronisation) before every replay and raises, and `check()` synchronises and raises.
 """
 from __future__ import annotations
 
 import os
 import time
 from collections import OrderedDict
-from typing import Callable, Optional
+from typing import Callable
 
 import torch
 
@@ -25,53 +22,27 @@ from . import ops
 
 GRAPHS = os.environ.get("FVM_B200_GRAPHS", "1") != "0"   # kill switch in the style of the reference's CLF_* variables
 MAX_GRAPHS = int(os.environ.get("FVM_B200_MAX_GRAPHS", "8"))
-CHAINS = int(os.environ.get("FVM_B200_CHAINS", "0"))      # 0 = choose by timing
-CHAIN_CANDIDATES = (1, 2, 4)
 
 
 class _Entry:
-    __slots__ = ("graph", "static_in", "static_out", "chains", "capture_s", "timings")
+    __slots__ = ("graph", "static_in", "static_out", "capture_s")
 
-    def __init__(self, graph, static_in, static_out, chains, capture_s, timings):
-        self.graph, self.static_in, self.static_out = graph, static_in, static_out
-        self.chains, self.capture_s, self.timings = chains, capture_s, timings
+    def __init__(self, graph, static_in, static_out, capture_s):
+        self.graph, self.static_in, self.static_out, self.capture_s = graph, static_in, static_out, capture_s
 
 
 class GraphRunner:
-    """Calls fn(x) through a per-shape CUDA graph. `fn` must be a pure function of x made of stream-ordered launches.
-    With `chainable=True`, fn must also treat the images of a batch independently and return a tensor whose first
-    dimension is the batch: the runner may then run groups of images as concurrent chains."""
+    """Calls fn(x) through a per-shape CUDA graph. `fn` must be a pure function of x made of stream-ordered launches."""
 
-    def __init__(self, fn: Callable[[torch.Tensor], torch.Tensor], enabled: bool = True, chainable: bool = False,
-                 chains: Optional[int] = None):
+    def __init__(self, fn: Callable[[torch.Tensor], torch.Tensor], enabled: bool = True):
         self.fn = fn
         self.enabled = enabled and GRAPHS
-        self.chainable = chainable
-        self.chains = CHAINS if chains is None else int(chains)
         self.cache: "OrderedDict[tuple, _Entry]" = OrderedDict()
-        self.last_capture_s = 0.0      # seconds the most recent first call at a new shape spent on warm-up + capture
+        self.last_capture_s = 0.0      # seconds the most recent first call at a new shape spent on tuning + capture
 
-    # ------------------------------------------------------------------------------------------------ capture
-    def _run_chained(self, x: torch.Tensor, chains: int) -> torch.Tensor:
-        """fn over `chains` groups of images, group i > 0 on its own stream, joined on the current stream."""
-        if chains <= 1:
-            return self.fn(x)
-        cur = torch.cuda.current_stream()
-        fork = torch.cuda.Event()
-        fork.record(cur)
-        parts = x.chunk(chains, dim=0)
-        outs = [None] * len(parts)
-        side = [torch.cuda.Stream(device=x.device) for _ in parts[1:]]
-        for i, (part, s) in enumerate(zip(parts[1:], side), start=1):
-            s.wait_event(fork)
-            with torch.cuda.stream(s):
-                outs[i] = self.fn(part)
-        outs[0] = self.fn(parts[0])
-        for s in side:
-            cur.wait_stream(s)
-        return torch.cat(outs, dim=0)
-
-    def _capture(self, x: torch.Tensor, chains: int):
+    def _build(self, x: torch.Tensor) -> _Entry:
+        ops.init(x.device)
+        t0 = time.perf_counter()
         static_in = torch.empty_strided(tuple(x.shape), tuple(x.stride()), dtype=x.dtype, device=x.device)
         static_in.copy_(x)
         cur = torch.cuda.current_stream()
@@ -79,53 +50,17 @@ class GraphRunner:
         side.wait_stream(cur)
         with torch.cuda.stream(side):
             for _ in range(2):
-                self._run_chained(static_in, chains)   # warm-up outside capture (first-call set-up and tuning of every op)
+                self.fn(static_in)       # outside capture: first-call set-up and per-layer tile tuning of every op
         cur.wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            static_out = self._run_chained(static_in, chains)
-        return graph, static_in, static_out
-
-    @staticmethod
-    def _time_graph(graph, reps: int = 8) -> float:
-        for _ in range(3):
-            graph.replay()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            graph.replay()
-        e1.record()
-        e1.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    def _build(self, x: torch.Tensor) -> _Entry:
-        ops.init(x.device)
-        t0 = time.perf_counter()
-        cands = [1]
-        n = x.shape[0]
-        if self.chainable and x.dim() >= 1:
-            if self.chains > 0:
-                cands = [self.chains if n % self.chains == 0 else 1]
-            else:
-                cands = [c for c in CHAIN_CANDIDATES if n % c == 0 and n // c >= 8] or [1]
-        best, timings = None, {}
-        for c in cands:
-            ent = self._capture(x, c)
-            if len(cands) == 1:
-                best = (c, ent)
-                break
-            ms = self._time_graph(ent[0])
-            timings[c] = ms
-            if best is None or ms < timings[best[0]] * 0.98:     # more chains must be clearly faster
-                best = (c, ent)
-        torch.cuda.synchronize()
+            static_out = self.fn(static_in)
         code = ops.last_status()
         if code:
             raise ops.FvmError(f"device status {code:#x} after capturing the forward (a bounded wait ran out)")
         self.last_capture_s = time.perf_counter() - t0
-        c, (graph, static_in, static_out) = best
-        return _Entry(graph, static_in, static_out, c, self.last_capture_s, timings)
+        return _Entry(graph, static_in, static_out, self.last_capture_s)
 
     def _entry(self, x: torch.Tensor) -> _Entry:
         key = (tuple(x.shape), x.dtype, x.device.index, tuple(x.stride()))
@@ -139,7 +74,6 @@ class GraphRunner:
             self.cache.move_to_end(key)
         return ent
 
-    # ------------------------------------------------------------------------------------------------ calls
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if not self.enabled or not x.is_cuda:
             return self.fn(x)
@@ -157,11 +91,6 @@ class GraphRunner:
         static buffer itself (e.g. straight from pinned host memory) and replay without the extra device copy."""
         ent = self._entry(x)
         return ent.graph, ent.static_in, ent.static_out
-
-    def info(self, x: torch.Tensor) -> dict:
-        """What was decided for x's shape: chains in use, the candidates' replay times (ms), seconds spent capturing."""
-        ent = self._entry(x)
-        return {"chains": ent.chains, "chain_ms": dict(ent.timings), "capture_s": round(ent.capture_s, 3)}
 
     def check(self) -> None:
         """Synchronises and raises if a kernel of this device reported a fault (a bounded device-side wait ran out);

@@ -75,8 +75,8 @@ class FastSeg(nn.Module):
     def __init__(self, net: B200DeepLabV3, graphs: bool = True):
         super().__init__()
         self.net = net
-        self._logits = GraphRunner(lambda x: self.net(x), enabled=graphs, chainable=True)
-        self._classmap = GraphRunner(lambda x: self.net.classmap(x), enabled=graphs, chainable=True)
+        self._logits = GraphRunner(lambda x: self.net(x), enabled=graphs)
+        self._classmap = GraphRunner(lambda x: self.net.classmap(x), enabled=graphs)
         self.info = {"tier": "b200", "fused_upsample_argmax": True}
 
     @torch.no_grad()

@@ -86,11 +86,16 @@ int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias, const voi
                        void* stream);
 
 /* Depthwise RxS convolution -- replaces clf::dwconv (fused_conv.cu:418-502), clfr3::dwconv2 (r3.cu:335-454) and
- * segx::dwconv (segmentation/fast/csrc/seg_kernels.cu:124-158):
- *   y[n,p,q,c] = act( bias[c] + sum_{r,s} x[n, p*sh-ph+r*dh, q*sw-pw+s*dw, c] * w[r,s,c] ), fp32 accumulation.
- * If pool_sums != NULL (fp32 [N,C], zeroed by the caller) the per-(image,channel) sums of the fp16-rounded outputs
- * are accumulated into it (the squeeze of a squeeze-excite block; cf. gconv2_pool, r3.cu:181-203). */
-int fvm_dwconv_f16(const void* x, const void* w_rsc, const void* bias, void* y, float* pool_sums, int N, int H, int W,
+ * segx::dwconv (segmentation/fast/seg_kernels.cu:124-158):
+ *   y[n,p,q,c] = act( bias[c] + sum_{r,s} x[n, p*sh-ph+r*dh, q*sw-pw+s*dw, c] * w[r,s,c] )
+ * Square 3/5/7-tap filters with stride 1 or 2 and no dilation use the arithmetic of dwconv2 (fp16x2 FMAs within a
+ * kernel row, fp32 across rows); every other shape accumulates in fp32 throughout.
+ * Fused squeeze (cf. gconv2_pool, r3.cu:181-203): if pool_partial != NULL it receives fp32 partial sums of the
+ * fp16-rounded outputs, laid out [N][slots][C] with slots = fvm_dwconv_pool_slots(...) for the same geometry; every
+ * element is written (no zeroing needed) and the sums do not depend on scheduling (no atomics). The mean over the
+ * pixels is sum over slots / (P*Q): fvm_se_gate_pooled_f16 takes the partial sums as they are. */
+int fvm_dwconv_pool_slots(int H, int W, int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw);
+int fvm_dwconv_f16(const void* x, const void* w_rsc, const void* bias, void* y, float* pool_partial, int N, int H, int W,
                    int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw, long long ldx, long long ldy,
                    int act, void* stream);
 
@@ -126,6 +131,12 @@ int fvm_global_avgpool_f16_noalloc(const void* x, void* y, int N, int HW, int C,
  * (pre-sigmoid). If mean_scale != 0, g is read as fp32 sums [N,C] and multiplied by mean_scale first (fused squeeze). */
 int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, const void* w2, const void* b2, void* s, int N,
                     int C, int Cs, int act, float mean_scale, void* stream);
+
+/* The same gate fed by the fused squeeze of fvm_dwconv_f16: `partial` is fp32 [N][slots][C]; g[n,c] =
+ * half(mean_scale * sum over slots), slots added in order (deterministic). Replaces the pair gconv2_pool +
+ * sums_to_mean_k of the reference (r3.cu:181-203, :283-299), which accumulates with atomics. */
+int fvm_se_gate_pooled_f16(const float* partial, int slots, const void* w1, const void* b1, const void* w2,
+                           const void* b2, void* s, int N, int C, int Cs, int act, float mean_scale, void* stream);
 
 /* y = x * sigmoid(s[n,c]) -- replaces clfr3::se_scale (r3.cu:302-329): sigmoid in fp32, rounded to fp16, fp16 multiply. */
 int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C, void* stream);

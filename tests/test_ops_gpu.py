@@ -357,14 +357,48 @@ def test_dwconv_matches_oracle(case):
     close(y, ref)
 
 
-def test_dwconv_fused_pool_sums():
-    x, w, b = gen((3, 144, 19, 19), 1), gen((3, 3, 144), 2, 0.2), gen((144,), 3, 0.1)
-    ref = R.dwconv_ref(x, w, b, (1, 1), (1, 1), 3)
-    sums = torch.zeros((3, 144), dtype=torch.float32, device=DEV)
-    y = ops.dwconv(cl(x), w.to(DEV), b.to(DEV), (1, 1), (1, 1), 3, pool_sums=sums)
+DW_ANY_CASES = [
+    # N, H, W, C, R, S, stride, pad, dil, act: every shape the tiled 3/5/7 kernel does not take
+    (2, 20, 24, 64, 3, 3, 1, 2, 2, 5), (1, 40, 40, 32, 3, 3, 1, 12, 12, 0), (2, 9, 9, 24, 1, 5, 1, 2, 1, 1),
+    (2, 16, 16, 48, 2, 2, 2, 0, 1, 0), (2, 3, 3, 72, 3, 3, 1, 1, 1, 3), (2, 30, 30, 16, 9, 9, 1, 4, 1, 0),
+    (2, 21, 17, 40, 3, 3, 3, 1, 1, 4), (1, 2, 2, 8, 7, 7, 1, 3, 1, 0),
+]
+
+
+@pytest.mark.parametrize("case", DW_ANY_CASES)
+def test_dwconv_any_shape_matches_oracle(case):
+    N, H, W, C, Rr, S, stride, pad, dil, act = case
+    pw_ = pad if Rr == S else (S // 2) * dil
+    ph_ = pad if Rr == S else (Rr // 2) * dil
+    x, w, b = gen((N, C, H, W), 1), gen((Rr, S, C), 2, 0.2), gen((C,), 3, 0.1)
+    ref = R.dwconv_ref(x, w, b, (stride, stride), (ph_, pw_), act, (dil, dil))
+    y = ops.dwconv(cl(x), w.to(DEV), b.to(DEV), (stride, stride), (ph_, pw_), act, dilation=(dil, dil))
+    assert ops.last_status() == 0
     close(y, ref)
-    want = ref.float().sum(dim=(2, 3))
-    assert (sums.cpu() - want).abs().max() <= 1e-3 * want.abs().max() + 1e-2
+
+
+@pytest.mark.parametrize("case", [(3, 144, 19, 19, 3, 1, 3), (2, 96, 30, 30, 7, 1, 0), (2, 336, 17, 23, 5, 2, 3),
+                                  (2, 48, 40, 40, 3, 1, 3), (2, 64, 12, 12, 3, 1, 1)])
+def test_dwconv_fused_squeeze_is_exact_and_deterministic(case):
+    N, C, H, W, k, stride, act = case
+    x, w, b = gen((N, C, H, W), 1), gen((k, k, C), 2, 0.2), gen((C,), 3, 0.1)
+    ref = R.dwconv_ref(x, w, b, (stride, stride), (k // 2, k // 2), act)
+    y, partial = ops.dwconv(cl(x), w.to(DEV), b.to(DEV), (stride, stride), (k // 2, k // 2), act, pool=True)
+    assert ops.last_status() == 0
+    close(y, ref)
+    assert partial.dtype == torch.float32 and partial.shape[0] == N and partial.shape[2] == C
+    # the partial sums are sums of the kernel's own fp16 outputs: compare with those, not with the oracle's
+    want = y.float().sum(dim=(2, 3))
+    got = partial.sum(dim=1)
+    assert (got - want).abs().max() <= 2e-4 * want.abs().max() + 1e-3
+    y2, partial2 = ops.dwconv(cl(x), w.to(DEV), b.to(DEV), (stride, stride), (k // 2, k // 2), act, pool=True)
+    assert torch.equal(partial, partial2) and torch.equal(y, y2)            # no atomics: same bits every time
+    # the gate fed by the partial sums equals the gate fed by the global average pool of y
+    Cs = 16
+    w1, b1, w2, b2 = gen((Cs, C), 4, 0.1).to(DEV), gen((Cs,), 5, 0.1).to(DEV), gen((C, Cs), 6, 0.1).to(DEV), gen((C,), 7, 0.1).to(DEV)
+    s_fused = ops.se_gate_pooled(partial, y.shape[2] * y.shape[3], w1, b1, w2, b2, 3)
+    s_plain = ops.se_gate(ops.global_avgpool(y), w1, b1, w2, b2, 3)
+    close(s_fused, s_plain, 2e-3)
 
 
 @pytest.mark.parametrize("shape,k,s,p,ceil", [((2, 64, 112, 112), 3, 2, 1, False), ((2, 16, 9, 9), 2, 2, 0, True),
