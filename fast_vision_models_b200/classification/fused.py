@@ -20,6 +20,7 @@ tensors, as in the reference. `classification/fast.py` keeps hand-built compiler
 """
 from __future__ import annotations
 
+import copy
 import operator
 from typing import Dict, Optional
 
@@ -93,7 +94,8 @@ def _single_user(node: fx.Node) -> Optional[fx.Node]:
 class Rewriter:
     def __init__(self, model: nn.Module):
         torch_ops.register()
-        self.gm = fx.GraphModule(model, _Tracer().trace(model.eval()))
+        model = copy.deepcopy(model).eval()          # the caller's fp32 model stays as it is
+        self.gm = fx.GraphModule(model, _Tracer().trace(model))
         self.mods = dict(self.gm.named_modules())
         self.g = self.gm.graph
         self.stats = {"conv_fused": 0, "dwconv": 0, "affine_act": 0, "pool": 0, "se_scale": 0, "gemm": 0, "stem_pad": 0,

@@ -71,6 +71,20 @@ extern "C" int fvm_init(void) {
         return FVM_ERR_SETUP;
     const int rc = conv_host_init();
     if (rc != FVM_OK) return rc;
+    // stream-K scratch: one [128][256] fp32 slot and one counter per SM (19 MB on a 148-SM part). Without it the
+    // convolution simply never chooses its stream-K variant.
+    {
+        const size_t floats = static_cast<size_t>(st->sms) * 128 * 256;
+        if (cudaMalloc(reinterpret_cast<void**>(&st->sk_part), floats * sizeof(float)) == cudaSuccess &&
+            cudaMalloc(reinterpret_cast<void**>(&st->sk_flags), static_cast<size_t>(st->sms) * sizeof(int)) == cudaSuccess &&
+            cudaMemset(st->sk_flags, 0, static_cast<size_t>(st->sms) * sizeof(int)) == cudaSuccess) {
+            st->sk_floats = floats;
+        } else {
+            (void)cudaGetLastError();
+            st->sk_part = nullptr;
+            st->sk_floats = 0;
+        }
+    }
     st->ready = true;
     return FVM_OK;
 }
@@ -91,6 +105,8 @@ extern "C" int fvm_last_status(int* code) {
     if (!st || !code) return FVM_ERR_SETUP;
     *code = *static_cast<volatile int*>(st->status_host);
     *static_cast<volatile int*>(st->status_host) = 0;
+    // a kernel that gave up may have left stream-K counters raised: clear them so that later launches start clean
+    if (*code != 0 && st->sk_flags) cudaMemset(st->sk_flags, 0, static_cast<size_t>(st->sms) * sizeof(int));
     return FVM_OK;
 }
 

@@ -160,8 +160,10 @@ __global__ void avgpool_kernel(const __half* __restrict__ x, __half* __restrict_
 // Stage 2 sums the splits in order and scales. Summation order is therefore fixed: results are deterministic.
 static constexpr int GAP_VX = 32, GAP_RY = 8;
 
+// With a single split (maps of up to 64 pixels) stage 2 has nothing to add: `y_direct` != nullptr makes stage 1 write
+// the fp16 means itself (same sums, same order, same rounding as the two-stage path) and stage 2 is not launched.
 __global__ void gap_partial_kernel(const __half* __restrict__ x, float* __restrict__ partial, int HW, int C,
-                                   long long ldx, int splits, int chunk) {
+                                   long long ldx, int splits, int chunk, __half* __restrict__ y_direct, float inv_hw) {
     __shared__ float red[GAP_RY][GAP_VX][8];
     const int cv = C >> 3;
     const int v = blockIdx.x * GAP_VX + threadIdx.x;
@@ -187,7 +189,8 @@ __global__ void gap_partial_kernel(const __half* __restrict__ x, float* __restri
         for (int j = 0; j < 8; ++j) {
             float s = red[0][threadIdx.x][j];
             for (int r = 1; r < GAP_RY; ++r) s += red[r][threadIdx.x][j];
-            partial[(n * splits + split) * C + v * 8 + j] = s;
+            if (y_direct) y_direct[n * C + v * 8 + j] = __float2half_rn(s * inv_hw);
+            else partial[(n * splits + split) * C + v * 8 + j] = s;
         }
     }
 }
@@ -300,66 +303,81 @@ __global__ void se_scale_kernel(const __half* __restrict__ x, const __half* __re
 }
 
 // ------------------------------------------------------------------------------------------- channels-last LayerNorm
-// G lanes cooperate on one row (G = 8, 16 or 32), each lane holds up to VPL 16-byte vectors of the row in registers;
-// two-pass fp32 statistics (mean, then sum of squared deviations), fp32 affine, one rounding.
-template <int G, int VPL>
-__global__ void layernorm_cl_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma,
-                                    const __half* __restrict__ beta, __half* __restrict__ y, long long rows, int C,
-                                    float eps, long long ldx, long long ldy) {
-    constexpr int ROWS_PER_WARP = 32 / G;
+// G lanes cooperate on one row (G = 4, 8, 16 or 32) and each lane holds VPL 16-byte vectors of it, G * VPL being the
+// smallest cover of the row's C / 8 vectors (C = 96: 4 lanes x 3 vectors, every lane busy). A lane group normalises
+// RPG rows at a time: the loads of all of them are issued before the first reduction, which is what keeps enough bytes
+// in flight per SM for an HBM-bound kernel. Two-pass fp32 statistics (mean, then sum of squared deviations), fp32
+// affine, one rounding; gamma / beta are loaded once per thread.
+template <int G, int VPL, int RPG>
+__global__ void __launch_bounds__(256)
+layernorm_cl_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma, const __half* __restrict__ beta,
+                    __half* __restrict__ y, long long rows, int C, float eps, long long ldx, long long ldy) {
+    constexpr int GROUPS = 32 / G;
     const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane / G, gl = lane % G;
-    const long long row = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp_in_block) * ROWS_PER_WARP + sub;
+    const long long group = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp_in_block) * GROUPS + sub;
+    const long long row0 = group * RPG;
     const int cv = C >> 3;
-    const bool row_ok = row < rows;
-    float f[VPL][8];
-    float sum = 0.f;
+    float f[RPG][VPL][8];
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) {
-        const int v = gl + k * G;
-        if (row_ok && v < cv) {
-            to_f8(ldg16(x + row * ldx + v * 8), f[k]);
+    for (int r = 0; r < RPG; ++r)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sum += f[k][j];
-        } else {
+        for (int k = 0; k < VPL; ++k) {
+            const int v = gl + k * G;
+            if (row0 + r < rows && v < cv) {
+                to_f8(ldg16(x + (row0 + r) * ldx + v * 8), f[r][k]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[k][j] = 0.f;
-        }
-    }
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float mean = sum / static_cast<float>(C);
-    float sq = 0.f;
-#pragma unroll
-    for (int k = 0; k < VPL; ++k) {
-        const int v = gl + k * G;
-        if (v < cv) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float d = f[k][j] - mean;
-                sq += d * d;
+                for (int j = 0; j < 8; ++j) f[r][k][j] = 0.f;
             }
         }
-    }
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    const float rstd = rsqrtf(sq / static_cast<float>(C) + eps);
-    if (!row_ok) return;
+    float gm[VPL][8], bt[VPL][8];
 #pragma unroll
     for (int k = 0; k < VPL; ++k) {
         const int v = gl + k * G;
-        if (v < cv) {
-            float gm[8], bt[8], o[8];
-            if (gamma) to_f8(ldg16(gamma + v * 8), gm);
-            if (beta) to_f8(ldg16(beta + v * 8), bt);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float t = (f[k][j] - mean) * rstd;
-                if (gamma) t *= gm[j];
-                if (beta) t += bt[j];
-                o[j] = t;
+        for (int j = 0; j < 8; ++j) { gm[k][j] = 1.f; bt[k][j] = 0.f; }
+        if (v < cv) {
+            if (gamma) to_f8(ldg16(gamma + v * 8), gm[k]);
+            if (beta) to_f8(ldg16(beta + v * 8), bt[k]);
+        }
+    }
+    const float inv_c = 1.f / static_cast<float>(C);
+#pragma unroll
+    for (int r = 0; r < RPG; ++r) {
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPL; ++k)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += f[r][k][j];
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum * inv_c;
+        float sq = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+            if (gl + k * G < cv) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float d = f[r][k][j] - mean;
+                    sq += d * d;
+                }
             }
-            stg16(y + row * ldy + v * 8, from_f8(o));
+        }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float rstd = rsqrtf(sq * inv_c + eps);
+        if (row0 + r < rows) {
+#pragma unroll
+            for (int k = 0; k < VPL; ++k) {
+                const int v = gl + k * G;
+                if (v < cv) {
+                    float o[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = (f[r][k][j] - mean) * rstd * gm[k][j] + bt[k][j];
+                    stg16(y + (row0 + r) * ldy + v * 8, from_f8(o));
+                }
+            }
         }
     }
 }
@@ -626,6 +644,25 @@ extern "C" long long fvm_gap_scratch_floats(int N, int HW, int C) {
     return static_cast<long long>(N) * gap_splits(N, HW, C, sms) * C;
 }
 
+// Both global-average-pool entry points launch through here; `partial` is the fp32 scratch of stage 1.
+static int gap_launch(const void* x, void* y, float* partial, int N, int HW, int C, long long ldx, int splits,
+                      void* stream) {
+    const int chunk = (HW + splits - 1) / splits;
+    const float inv_hw = 1.f / static_cast<float>(HW);
+    dim3 grid(((C >> 3) + GAP_VX - 1) / GAP_VX, splits, N), block(GAP_VX, GAP_RY);
+    gap_partial_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), partial, HW, C, ldx, splits, chunk, splits == 1 ? static_cast<__half*>(y) : nullptr,
+        inv_hw);
+    count_launch();
+    if (splits > 1) {
+        const long long total = static_cast<long long>(N) * C;
+        gap_final_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            partial, static_cast<__half*>(y), C, splits, inv_hw, total);
+        count_launch();
+    }
+    return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
+}
+
 extern "C" int fvm_global_avgpool_f16(const void* x, void* y, float* partial, int N, int HW, int C, long long ldx,
                                       void* stream) {
     DeviceState* st = device_state();
@@ -633,16 +670,7 @@ extern "C" int fvm_global_avgpool_f16(const void* x, void* y, float* partial, in
     if (!x || !y || !partial || N <= 0 || HW <= 0 || C <= 0 || (C & 7) || (ldx & 7) || ldx < C || !aligned16(x))
         return FVM_ERR_ARG;
     if (N > 65535) return FVM_ERR_ARG;
-    const int splits = gap_splits(N, HW, C, st->sms);
-    const int chunk = (HW + splits - 1) / splits;
-    dim3 grid(((C >> 3) + GAP_VX - 1) / GAP_VX, splits, N), block(GAP_VX, GAP_RY);
-    gap_partial_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(x), partial,
-                                                                              HW, C, ldx, splits, chunk);
-    count_launch();
-    const long long total = static_cast<long long>(N) * C;
-    gap_final_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        partial, static_cast<__half*>(y), C, splits, 1.f / static_cast<float>(HW), total);
-    FVM_LAUNCH_CHECK();
+    return gap_launch(x, y, partial, N, HW, C, ldx, gap_splits(N, HW, C, st->sms), stream);
 }
 
 static int se_gate_launch(const void* g, int slots, const void* w1, const void* b1, const void* w2, const void* b2, void* s,
@@ -686,11 +714,25 @@ extern "C" int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, in
 template <int G, int VPL>
 static void launch_ln(const void* x, const void* gamma, const void* beta, void* y, long long rows, int C, float eps,
                       long long ldx, long long ldy, cudaStream_t stream) {
-    constexpr int WARPS = 8;
-    const long long rows_per_block = static_cast<long long>(WARPS) * (32 / G);
-    layernorm_cl_kernel<G, VPL><<<blocks_for(rows, static_cast<int>(rows_per_block)), WARPS * 32, 0, stream>>>(
+    constexpr int RPG = VPL >= 3 ? 2 : 4;           // rows in flight per lane group (registers: RPG * VPL * 8 floats)
+    constexpr int WARPS = 4;
+    const long long rows_per_block = static_cast<long long>(WARPS) * (32 / G) * RPG;
+    layernorm_cl_kernel<G, VPL, RPG><<<blocks_for(rows, static_cast<int>(rows_per_block)), WARPS * 32, 0, stream>>>(
         static_cast<const __half*>(x), static_cast<const __half*>(gamma), static_cast<const __half*>(beta),
         static_cast<__half*>(y), rows, C, eps, ldx, ldy);
+    count_launch();
+}
+
+template <int G>
+static bool launch_ln_g(int vpl, const void* x, const void* gamma, const void* beta, void* y, long long rows, int C,
+                        float eps, long long ldx, long long ldy, cudaStream_t st) {
+    switch (vpl) {
+        case 1: launch_ln<G, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st); return true;
+        case 2: launch_ln<G, 2>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st); return true;
+        case 3: launch_ln<G, 3>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st); return true;
+        case 4: launch_ln<G, 4>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st); return true;
+    }
+    return false;
 }
 
 extern "C" int fvm_layernorm_cl_f16(const void* x, const void* gamma, const void* beta, void* y, long long rows, int C,
@@ -700,14 +742,16 @@ extern "C" int fvm_layernorm_cl_f16(const void* x, const void* gamma, const void
         return FVM_ERR_ARG;
     const int cv = C >> 3;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cv <= 8) launch_ln<8, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
-    else if (cv <= 16) launch_ln<16, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
-    else if (cv <= 32) launch_ln<32, 1>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
-    else if (cv <= 64) launch_ln<32, 2>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
-    else if (cv <= 128) launch_ln<32, 4>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
-    else if (cv <= 256) launch_ln<32, 8>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
-    else return FVM_ERR_ARG;
-    FVM_LAUNCH_CHECK();
+    // smallest lane group whose lanes hold at most 4 vectors each; rows wider than 128 vectors: 32 lanes x 6 or 8
+    bool ok = false;
+    if (cv <= 16) ok = launch_ln_g<4>((cv + 3) / 4, x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 32) ok = launch_ln_g<8>((cv + 7) / 8, x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 64) ok = launch_ln_g<16>((cv + 15) / 16, x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 128) ok = launch_ln_g<32>((cv + 31) / 32, x, gamma, beta, y, rows, C, eps, ldx, ldy, st);
+    else if (cv <= 192) { launch_ln<32, 6>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st); ok = true; }
+    else if (cv <= 256) { launch_ln<32, 8>(x, gamma, beta, y, rows, C, eps, ldx, ldy, st); ok = true; }
+    if (!ok) return FVM_ERR_ARG;
+    return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
 }
 
 extern "C" int fvm_bias_act_f16(void* y, const void* bias, const void* res, long long pixels, int C, int relu,
@@ -816,14 +860,6 @@ extern "C" int fvm_global_avgpool_f16_noalloc(const void* x, void* y, int N, int
     }
     const int splits = gap_splits(N, HW, C, st.sms);
     if (static_cast<long long>(N) * splits * C > FVM_GAP_NOALLOC_MAX_FLOATS) return FVM_ERR_ARG;   // beyond the fixed scratch
-    const int chunk = (HW + splits - 1) / splits;
-    dim3 grid(((C >> 3) + GAP_VX - 1) / GAP_VX, splits, N), block(GAP_VX, GAP_RY);
     // stage 1 overwrites every partial sum stage 2 reads: nothing in the shared array has to start at zero
-    gap_partial_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(x), st.scratch,
-                                                                              HW, C, ldx, splits, chunk);
-    count_launch();
-    const long long total = static_cast<long long>(N) * C;
-    gap_final_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        st.scratch, static_cast<__half*>(y), C, splits, 1.f / static_cast<float>(HW), total);
-    FVM_LAUNCH_CHECK();
+    return gap_launch(x, y, st.scratch, N, HW, C, ldx, splits, stream);
 }

@@ -91,6 +91,15 @@ struct ConvParams {
     const __half* bias;
     const float* scale;
     int* status;
+    // stream-K (conv_streamk_kernel): the k-blocks of all tiles form one sequence of sk_units = tiles * kblocks units
+    // that is cut into gridDim.x equal runs; a tile whose k-blocks fall into several runs is finished by the CTA that
+    // holds its first k-block, the others hand their fp32 partial tile over through sk_part (one [128][BN] slot per
+    // CTA) and sk_flags (one counter per slot, back at zero when the kernel ends).
+    int sk;
+    uint32_t sk_units;
+    FastDiv div_kb;
+    float* sk_part;
+    int* sk_flags;
 };
 
 // status codes written by the device when a bounded wait ran out: 0x100 + role
@@ -111,9 +120,12 @@ __device__ __forceinline__ float2 unpack_h2(uint32_t u) {
 // activation -> fp16, combined in place with the staged residual chunk. `stage_row` points at this row inside the
 // 64-channel staging sub-tile (128-byte swizzle: 16-byte chunk index XOR (row & 7)); `bias_s` at the chunk's bias.
 // ACT: 0 none, 1 relu, 3 silu, 5 gelu (erf), 2 = read p.act at run time. All loads are issued before the arithmetic.
+// `part` / `nparts` / `part_stride` (stream-K only): fp32 partial sums of this row and these columns from `nparts` other
+// CTAs, `part_stride` floats apart, added to the accumulator in that order before the epilogue arithmetic.
 template <int ACT, bool RES, int W>
 __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t taddr, uint32_t stage_row, uint32_t ch0,
-                                               uint32_t row_xor, uint32_t bias_s, int n, int left) {
+                                               uint32_t row_xor, uint32_t bias_s, int n, int left,
+                                               const float* part = nullptr, int nparts = 0, size_t part_stride = 0) {
     static_assert(W == 32 || W == 16, "chunks of 32 or 16 columns");
     uint32_t v[W];
     __syncwarp();
@@ -126,6 +138,17 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
         for (int j = 0; j < W / 8; ++j) rw[j] = lds128(stage_row + (((ch0 + j) ^ row_xor) << 4));
     }
     tmem_ld_wait();
+    for (int q = 0; q < nparts; ++q) {
+        const float4* src = reinterpret_cast<const float4*>(part + static_cast<size_t>(q) * part_stride);
+#pragma unroll
+        for (int i = 0; i < W / 4; ++i) {
+            const float4 t = __ldcg(src + i);       // written by another SM during this launch: read past L1
+            v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + t.x);
+            v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + t.y);
+            v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + t.z);
+            v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + t.w);
+        }
+    }
 #pragma unroll
     for (int j = 0; j < W / 8; ++j) {
         if (8 * j < left) {
@@ -818,6 +841,399 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
 }
 
+// ------------------------------------------------------------------------------------------------ stream-K variant
+// For layers with fewer tiles than SMs, or a ragged last wave (every 14x14 / 7x7 layer of a ResNet at batch 64, the
+// classifier GEMM): the k-blocks of all tiles are laid end to end and every CTA takes an equal run of them, so all SMs
+// pull the same share of the operands through their L2 ports whatever the tile count. A run covers the tail of one
+// tile, whole tiles, and the head of another. A CTA that holds a tile's k-block 0 finishes the tile (bias, residual,
+// activation, store); the CTAs holding its later k-blocks write their fp32 partial tile to their slot of p.sk_part and
+// raise their counter in p.sk_flags. Because runs are contiguous, a partial tile is always the FIRST thing its CTA
+// computes and the tile it is added to is the LAST thing the finishing CTA computes: no CTA waits for work that has not
+// been started, and the wait (bounded like every other) is short. Counters return to zero by themselves: producers
+// add EPI_WARPS, the finishing CTA's warps add EPI_WARPS more once they have read the slot, the last one resets it.
+// Plain mode only: A by tiled or im2col TMA, B streamed per k-block, one 128-pixel sub-tile. Same roles and
+// shared-memory map as conv_tcgen05_kernel.
+static constexpr int STATUS_WAIT_STREAMK = 0x106;
+
+struct SkSeg {
+    int m_tile, n_tile;
+    int kb0, kb1;      // k-blocks [kb0, kb1) of the tile
+    int kind;          // 0 whole tile; 1 partial tile handed over through this CTA's slot; 2 head of a tile: finishes it
+    int nparts;        // kind 2: the next `nparts` CTAs hold the rest of the tile
+};
+
+__device__ __forceinline__ uint32_t sk_run_begin(const ConvParams& p, uint32_t cta) {
+    return static_cast<uint32_t>((static_cast<unsigned long long>(cta) * p.sk_units) / gridDim.x);
+}
+
+// Next segment of this CTA's run [u, u1); advances u.
+__device__ __forceinline__ bool sk_next(const ConvParams& p, uint32_t& u, uint32_t u1, SkSeg& s) {
+    if (u >= u1) return false;
+    const uint32_t tile = fastdiv(u, p.div_kb);
+    const int kb0 = static_cast<int>(u - tile * static_cast<uint32_t>(p.kblocks));
+    const int kb1 = min(p.kblocks, kb0 + static_cast<int>(u1 - u));
+    s.m_tile = static_cast<int>(fastdiv(tile, p.div_ntiles));
+    s.n_tile = static_cast<int>(tile) - s.m_tile * p.n_tiles;
+    s.kb0 = kb0;
+    s.kb1 = kb1;
+    s.nparts = 0;
+    if (kb0 > 0) {
+        s.kind = 1;
+    } else if (kb1 == p.kblocks) {
+        s.kind = 0;
+    } else {
+        s.kind = 2;
+        const uint32_t tile_end = (tile + 1u) * static_cast<uint32_t>(p.kblocks);
+        for (uint32_t j = blockIdx.x + 1; j < gridDim.x && sk_run_begin(p, j) < tile_end; ++j) ++s.nparts;
+    }
+    u += static_cast<uint32_t>(kb1 - kb0);
+    return true;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_y,
+                    const ConvParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t b_kb_bytes = static_cast<uint32_t>(p.BN) * BK * 2;
+    const uint32_t stage_bytes = A_STAGE_BYTES + b_kb_bytes;
+    const uint32_t epi_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+    const uint32_t epi_bytes = static_cast<uint32_t>(p.nsub) * SUB_BYTES;
+    const uint32_t bar_base = epi_base + static_cast<uint32_t>(p.nepi) * epi_bytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + MAX_ACC + a); };
+    auto res_full_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + e); };
+    auto epi_done_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + MAX_EPI + e); };
+    auto epi_free_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 2 * MAX_EPI + e); };
+    const uint32_t misc_off = (bar_base - smem_u32(smem_raw)) + 8u * NUM_BARRIERS;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + misc_off + 4);
+    const uint32_t bias_off = misc_off + MISC_BYTES;
+    const uint32_t bias_base = smem_u32(smem_raw) + bias_off;
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < p.nacc; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), EPI_WARPS);
+        }
+        for (int e = 0; e < p.nepi; ++e) {
+            mbar_init(res_full_bar(e), 1);
+            mbar_init(epi_done_bar(e), EPI_WARPS);
+            mbar_init(epi_free_bar(e), 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_y);
+        if (p.has_res) tma_prefetch_desc(&tmap_r);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), static_cast<uint32_t>(p.tmem_cols));
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t run_begin = sk_run_begin(p, blockIdx.x), run_end = sk_run_begin(p, blockIdx.x + 1);
+    const size_t slot_floats = static_cast<size_t>(BM) * p.BN;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int e = 0;
+            uint32_t e_phase = 0;
+            bool ok = true;
+            const int PQ = p.P * p.Q;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            uint32_t u = run_begin;
+            SkSeg sg;
+            while (ok && sk_next(p, u, run_end, sg)) {
+                const int m0 = sg.m_tile * BM;
+                const int n0 = sg.n_tile * p.BN;
+                if (p.has_res && sg.kind != 1) {
+                    if (!mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag)) {
+                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    e_phase ^= 1u << e;
+                    const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
+                    mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(nsub) * SUB_BYTES);
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0);
+                    if (++e == p.nepi) e = 0;
+                }
+                int img = 0, h0 = 0, w0 = 0;
+                if (p.im2col) {
+                    img = static_cast<int>(fastdiv(static_cast<uint32_t>(m0), p.div_pq));
+                    const int rem = m0 - img * PQ;
+                    const int pp = static_cast<int>(fastdiv(static_cast<uint32_t>(rem), p.div_q));
+                    const int qq = rem - pp * p.Q;
+                    h0 = pp * p.sh - p.ph;
+                    w0 = qq * p.sw - p.pw;
+                }
+                int tap = sg.kb0 / p.cchunks;
+                int cc = sg.kb0 - tap * p.cchunks;
+                int r = tap / p.S;
+                int s = tap - r * p.S;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
+                    mbar_expect_tx(full_bar(stage), stage_bytes);
+                    tma_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    if (p.im2col)
+                        tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
+                                           static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                    else
+                        tma_load_2d(a_dst, &tmap_a, full_bar(stage), cc * BK, m0);
+                    if (++cc == p.cchunks) {
+                        cc = 0;
+                        ++tap;
+                        if (++s == p.S) { s = 0; ++r; }
+                    }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (ok) {       // no bulk load of this CTA may be in flight when it exits
+                for (int i = 0; i < p.stages; ++i) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            const uint32_t idesc = umma_idesc_f16_f32(BM, p.BN);
+            const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
+            auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
+            const uint32_t stage_step = stage_bytes >> 4;
+            const uint32_t a_lo0 = lo_of(smem_base);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t st_lo = a_lo0;
+            uint32_t acc_phase = 0;
+            int acc = -1;
+            bool failed = false;
+            uint32_t u = run_begin;
+            SkSeg sg;
+            while (sk_next(p, u, run_end, sg)) {
+                if (++acc == p.nacc) acc = 0;
+                failed |= !mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag);
+                acc_phase ^= 1u << acc;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+                    failed |= !mbar_wait(full_bar(stage), phase, abort_flag);
+                    tc_fence_after();
+                    umma_f16_kblock(d_tmem, st_lo, hi128, st_lo + (A_STAGE_BYTES >> 4), hi128, idesc,
+                                    static_cast<uint32_t>(kb != sg.kb0));
+                    umma_commit(empty_bar(stage));
+                    st_lo += stage_step;
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }
+                }
+                umma_commit(tfull_bar(acc));
+            }
+            if (failed) atomicExch(p.status, STATUS_WAIT_MMA);
+        }
+        __syncwarp();
+    } else if (warp < STORE_WARP) {
+        // ------------------------------------------------------------------ epilogue
+        const int lane_group = warp & 3;
+        const int group = (warp - 2) >> 2;
+        const int row = lane_group * 32 + lane;
+        const uint32_t row_xor = static_cast<uint32_t>(row & 7);
+        const uint32_t bias_s = bias_base;
+        const uint32_t stage0 = epi_base + static_cast<uint32_t>(row) * 128u;
+        {
+            float* bias_f = reinterpret_cast<float*>(smem_raw + bias_off);
+            for (int i = threadIdx.x - 64; i < p.bias_elems; i += EPI_WARPS * 32)
+                bias_f[i] = (p.bias != nullptr && i < p.K) ? __half2float(p.bias[i]) : 0.f;
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        }
+        uint32_t acc_phase = 0, e_phase = 0;
+        int e = 0, acc = -1;
+        bool ok = true;
+        uint32_t u = run_begin;
+        SkSeg sg;
+        const int act_t = (p.act == 0 || p.act == 1 || p.act == 3 || p.act == 5) ? p.act : 2;
+        const int variant = act_t * 2 + (p.has_res ? 1 : 0);
+        while (ok && sk_next(p, u, run_end, sg)) {
+            if (++acc == p.nacc) acc = 0;
+            const int n0 = sg.n_tile * p.BN;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                                   static_cast<uint32_t>(acc * p.acc_stride);
+            if (sg.kind == 1) {
+                // partial tile: fp32 accumulator rows to this CTA's slot, then the counter
+                if (!mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag)) {
+                    if (lane == 0) atomicExch(p.status, STATUS_WAIT_EPILOGUE);
+                    ok = false;
+                    break;
+                }
+                acc_phase ^= 1u << acc;
+                tc_fence_after();
+                float* dst_row = p.sk_part + static_cast<size_t>(blockIdx.x) * slot_floats + static_cast<size_t>(row) * p.BN;
+                for (int c0 = 32 * group; c0 < p.BN; c0 += 32 * EPI_GROUPS) {
+                    uint32_t v[32];
+                    __syncwarp();
+                    tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c0), v);
+                    tmem_ld_wait();
+                    float4* dst = reinterpret_cast<float4*>(dst_row + c0);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        __stcg(dst + i, make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                    __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+                }
+                __threadfence();                 // this thread's partial sums are visible device-wide before the counter moves
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(tempty_bar(acc));
+                    atomicAdd(p.sk_flags + blockIdx.x, 1);
+                }
+                continue;
+            }
+            const bool got_buf = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(e), (e_phase >> e) & 1u, abort_flag)
+                                           : mbar_wait<EPI_BACKOFF_NS>(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag);
+            if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag)) {
+                if (lane == 0) atomicExch(p.status, STATUS_WAIT_EPILOGUE);
+                ok = false;
+                break;
+            }
+            e_phase ^= 1u << e;
+            acc_phase ^= 1u << acc;
+            tc_fence_after();
+            if (sg.kind == 2) {
+                // the rest of this tile: wait (bounded) until every epilogue warp of each contributing CTA has written
+                bool seen = true;
+                if (lane == 0) {
+                    for (int q = 0; q < sg.nparts && seen; ++q) {
+                        const int* flag = p.sk_flags + blockIdx.x + 1 + q;
+                        unsigned long long t0 = 0;
+                        uint32_t spins = 0;
+                        while (ld_acquire_gpu(flag) < EPI_WARPS) {
+                            __nanosleep(64);
+                            if ((++spins & 0x3f) == 0) {
+                                const unsigned long long now = globaltimer_ns();
+                                if (t0 == 0) t0 = now;
+                                else if (*abort_flag || now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; seen = false; break; }
+                            }
+                        }
+                    }
+                }
+                seen = __shfl_sync(0xffffffffu, seen ? 1 : 0, 0) != 0;
+                if (!seen) {
+                    if (lane == 0) atomicExch(p.status, STATUS_WAIT_STREAMK);
+                    ok = false;
+                    break;
+                }
+            }
+            const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
+            const int ncols = min(p.BN, p.K - n0);
+            const float* part_row = p.sk_part + static_cast<size_t>(blockIdx.x + 1) * slot_floats + static_cast<size_t>(row) * p.BN;
+            for (int c0 = 32 * group; c0 < ncols; c0 += 32 * EPI_GROUPS) {
+                const uint32_t sub = stage_row0 + static_cast<uint32_t>(c0 >> 6) * SUB_BYTES;
+                const uint32_t ch0 = static_cast<uint32_t>((c0 & 63) >> 3);
+                const uint32_t bs = bias_s + 4u * static_cast<uint32_t>(n0 + c0);
+                const uint32_t ta = t_row + static_cast<uint32_t>(c0);
+#define SK_CHUNK(A, R) epilogue_chunk<A, R, 32>(p, ta, sub, ch0, row_xor, bs, n0 + c0, ncols - c0, part_row + c0, sg.nparts, slot_floats)
+                switch (variant) {
+                    case 0: SK_CHUNK(0, false); break;
+                    case 1: SK_CHUNK(0, true); break;
+                    case 2: SK_CHUNK(1, false); break;
+                    case 3: SK_CHUNK(1, true); break;
+                    case 4: SK_CHUNK(2, false); break;
+                    case 5: SK_CHUNK(2, true); break;
+                    case 6: SK_CHUNK(3, false); break;
+                    case 7: SK_CHUNK(3, true); break;
+                    case 10: SK_CHUNK(5, false); break;
+                    default: SK_CHUNK(5, true); break;
+                }
+#undef SK_CHUNK
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(tempty_bar(acc));
+                mbar_arrive(epi_done_bar(e));
+                // this warp has read the contributors' slots: EPI_WARPS more arrivals per counter, the last one clears it
+                for (int q = 0; q < sg.nparts; ++q) {
+                    int* flag = p.sk_flags + blockIdx.x + 1 + q;
+                    if (atomicAdd(flag, 1) == 2 * EPI_WARPS - 1) atomicExch(flag, 0);
+                }
+            }
+            if (++e == p.nepi) e = 0;
+        }
+    } else {
+        // ------------------------------------------------------------------ store warp
+        if (elect_one()) {
+            uint32_t e_phase = 0;
+            int e = 0;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            bool ok = true;
+            uint32_t u = run_begin;
+            SkSeg sg;
+            while (ok && sk_next(p, u, run_end, sg)) {
+                if (sg.kind == 1) continue;
+                const int m0 = sg.m_tile * BM;
+                const int n0 = sg.n_tile * p.BN;
+                if (!mbar_wait<EPI_BACKOFF_NS>(epi_done_bar(e), (e_phase >> e) & 1u, abort_flag)) {
+                    atomicExch(p.status, STATUS_WAIT_STORE);
+                    ok = false;
+                    break;
+                }
+                e_phase ^= 1u << e;
+                const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
+                for (int sub = 0; sub < nsub; ++sub)
+                    tma_store_2d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                 n0 + sub * 64, m0);
+                tma_store_commit();
+                tma_store_wait_read();
+                mbar_arrive(epi_free_bar(e));
+                if (++e == p.nepi) e = 0;
+            }
+            tma_store_wait_read();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- host side
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -852,7 +1268,9 @@ int conv_host_init() {
         cudaDriverGetVersion(&g_driver_version);
     }
     if (cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
-        cudaSuccess)
+            cudaSuccess ||
+        cudaFuncSetAttribute(conv_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+            cudaSuccess)
         return FVM_ERR_SETUP;
     return FVM_OK;
 }
@@ -1082,7 +1500,9 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (!st) return FVM_ERR_SETUP;
     if (!x || !w || !y) return FVM_ERR_ARG;
     // force_bn: low 16 bits = output-channel tile (0 = choose), bits 16..23 = sub-tiles per tile (0 = choose),
-    // bits 24..25 = weight-resident mode (0 = choose, 1 = on, 2 = off), bits 26..27 = halo mode (same coding)
+    // bits 24..25 = weight-resident mode (0 = choose, 1 = on, 2 = off), bits 26..27 = halo mode, bits 28..29 = stream-K
+    // (same coding)
+    const int force_sk = force_bn > 0 ? ((force_bn >> 28) & 3) : 0;
     const int force_halo = force_bn > 0 ? ((force_bn >> 26) & 3) : 0;
     const int force_bres = force_bn > 0 ? ((force_bn >> 24) & 3) : 0;
     const int force_mt = force_bn > 0 ? ((force_bn >> 16) & 0xff) : 0;
@@ -1172,9 +1592,25 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // carry activations only, so more tiles' worth of loads are in flight and the weights are not re-read from L2 for
     // every tile. Used when the tile fits in 96 KB, every CTA gets at least two tiles, and the grid can be made a
     // multiple of the n-tile count.
+    // Stream-K: on request, or by default when there are fewer tiles than SMs (see conv_streamk_kernel).
+    {
+        const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+        const long long units = tiles * p.kblocks;
+        const bool can = !p.tapk && !p.halo && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
+                         units >= st->sms && units < 0x7fffffffll &&
+                         static_cast<size_t>(st->sms) * BM * p.BN <= st->sk_floats;
+        if (force_sk == 1 && !can) return FVM_ERR_ARG;
+        p.sk = can && (force_sk == 1 || (force_sk == 0 && tiles * 10 < static_cast<long long>(st->sms) * 9)) ? 1 : 0;
+        if (p.sk) {
+            p.sk_units = static_cast<uint32_t>(units);
+            p.div_kb = fastdiv_init(static_cast<uint32_t>(p.kblocks));
+            p.sk_part = st->sk_part;
+            p.sk_flags = st->sk_flags;
+        }
+    }
     SmemPlan sp;
     p.bres = 0;
-    if (!p.tapk && force_bres != 2 && p.n_tiles <= st->sms) {
+    if (!p.sk && !p.tapk && force_bres != 2 && p.n_tiles <= st->sms) {
         const long long wbytes = static_cast<long long>(p.kblocks) * p.BN * BK * 2;
         const int cta_per_n = st->sms / p.n_tiles;
         const bool worth = p.m_tiles >= 2 * cta_per_n;
@@ -1310,6 +1746,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         if (cta_per_n > p.m_tiles) cta_per_n = p.m_tiles;
         grid = cta_per_n * p.n_tiles;
     }
+    if (p.sk) grid = st->sms;       // units >= SMs: every CTA gets at least one k-block
     return launch_conv_kernel(tmap_a, tmap_b, tmap_r, tmap_y, p, grid, smem, stream);
 }
 
@@ -1330,14 +1767,17 @@ static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap
         attr.val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, conv_tcgen05_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p) == cudaSuccess) {
+        const cudaError_t err = p.sk ? cudaLaunchKernelEx(&cfg, conv_streamk_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p)
+                                     : cudaLaunchKernelEx(&cfg, conv_tcgen05_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p);
+        if (err == cudaSuccess) {
             count_launch();
             return FVM_OK;
         }
         (void)cudaGetLastError();   // not accepted here (e.g. by an older driver during capture): plain launches from now on
         use_pdl = 0;
     }
-    conv_tcgen05_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
+    if (p.sk) conv_streamk_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
+    else conv_tcgen05_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
 }

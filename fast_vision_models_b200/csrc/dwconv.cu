@@ -134,7 +134,8 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
         }
         constexpr int L = (DW_TW - 1) * SW + S;      // staged columns one kernel row of this thread's strip reads
         const uint32_t pix = static_cast<uint32_t>(p.cbv) * 16u;
-        for (int r = 0; r < p.R; ++r) {
+#pragma unroll
+        for (int r = 0; r < S; ++r) {          // square filter: R == S; unrolled so that the next row's loads issue early
             const __half* wrow = w + static_cast<long long>(r) * S * p.C + v * 8;
             uint4 wr[S];
 #pragma unroll
@@ -301,28 +302,38 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
     p.ldy = ldy;
     const int cv = C >> 3;
     out->tile_kernel = R == S && (S == 3 || S == 5 || S == 7) && dh == 1 && dw == 1 && sh == sw && (sw == 1 || sw == 2);
+    // Candidates: channel blocks from the widest acceptable one down, cell grids px x py with px a power of two. The
+    // best product of (useful lanes) x (useful cells: tiles overhang the map) wins; ties go to the patch with the least
+    // staged bytes per output pixel (less border).
+    const int unit = out->tile_kernel ? DW_TW : 1;
+    double best_score = -1.0, best_cost = 0.0;
+    bool found = false;
     for (int cbv = pick_cbv(cv); cbv >= 1; cbv >>= 1) {
         const int cells = DW_THREADS / cbv;
-        // cell grid: as square a tile of output pixels as the map allows (less border per output), then shrink rows
-        // until the staged patch fits the shared-memory limit
-        const int unit = out->tile_kernel ? DW_TW : 1;
-        int px = 1;
-        while (px * 2 <= cells && px * unit * 2 <= p.Q + unit - 1 && px * unit < cells / px) px *= 2;
-        for (; px >= 1; px >>= 1) {
+        const int vblocks = (cv + cbv - 1) / cbv;
+        const double lane_eff = static_cast<double>(cv) / (vblocks * cbv);
+        for (int px = 1; px <= cells; px <<= 1) {
             const int py = cells / px;
             const int tile_w = (px * unit - 1) * sw + (S - 1) * dw + 1;
             const int tile_h = (py - 1) * sh + (R - 1) * dh + 1;
             const size_t bytes = static_cast<size_t>(tile_h) * tile_w * cbv * 16;
             if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 > static_cast<size_t>(DW_SMEM_LIMIT)) continue;
-            p.cbv = cbv; p.px = px; p.py = py; p.tile_w = tile_w; p.tile_h = tile_h;
-            p.tiles_x = (p.Q + px * unit - 1) / (px * unit);
-            p.tiles_y = (p.P + py - 1) / py;
-            p.vblocks = (cv + cbv - 1) / cbv;
-            out->smem = 128 + bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
-            return true;
+            const int tiles_x = (p.Q + px * unit - 1) / (px * unit), tiles_y = (p.P + py - 1) / py;
+            const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * py * tiles_x * px * unit);
+            const double score = lane_eff * tile_eff;
+            const double cost = static_cast<double>(tile_h) * tile_w / (py * px * unit);
+            if (score > best_score * 1.02 || (score > best_score * 0.98 && cost < best_cost)) {
+                best_score = score > best_score ? score : best_score;
+                best_cost = cost;
+                found = true;
+                p.cbv = cbv; p.px = px; p.py = py; p.tile_w = tile_w; p.tile_h = tile_h;
+                p.tiles_x = tiles_x; p.tiles_y = tiles_y; p.vblocks = vblocks;
+                out->smem = 128 + bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
+            }
         }
+        if (found && best_score > 0.97) break;       // narrower channel blocks only when the wide ones waste lanes
     }
-    return false;
+    return found;
 }
 
 }  // namespace fvm

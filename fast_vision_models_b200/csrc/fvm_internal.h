@@ -12,6 +12,11 @@ struct DeviceState {
     int max_smem = 0;
     int* status_dev = nullptr;    // device-visible address of the status word (mapped pinned host memory)
     int* status_host = nullptr;   // host address of the same word
+    // stream-K scratch of the convolution kernel: fp32 partial tiles (one slot per CTA) and one counter per slot. Shared
+    // by every stream of the device: stream-K launches on different streams must not overlap in time.
+    float* sk_part = nullptr;
+    int* sk_flags = nullptr;
+    size_t sk_floats = 0;
     bool ready = false;
 };
 

@@ -117,6 +117,10 @@ class FusedConv(nn.Module):
             # weight tile resident in shared memory (bits 24..25 = 1) or streamed per k-block (= 2), per tile width
             base = list(widths)
             cands += [c | (1 << 24) for c in base] + [c | (2 << 24) for c in base]
+        if rows <= 148 * 128 * 3 and self.w.shape[1] > 16:
+            # few tiles per SM: stream-K (bits 28..29 = 1) spreads the k-blocks of all tiles evenly over the SMs; offered
+            # per tile width against the plain schedule (= 2)
+            cands += [c | (1 << 28) for c in widths] + [c | (2 << 28) for c in widths]
         best = 0
         if len(cands) > 1:
             # Candidates are timed in rounds (every candidate once per round, best burst kept), so that a drift of the

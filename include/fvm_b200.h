@@ -72,7 +72,10 @@ int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* r
  * most 256; 0 = choose), bits 16..23 = 128-pixel sub-tiles per tile (1, 2, 4; 0 = choose), bits 24..25 = keep the
  * weight tile resident in shared memory (0 = choose, 1 = on, 2 = off), bits 26..27 = halo mode, same coding: a 3x3
  * stride-1 convolution (dilation 1..4) walks 16 x 8 patches of output pixels and reads each patch's input (with its
- * border) once per 64 channels instead of once per filter tap. Shapes that do not fit return 1. */
+ * border) once per 64 channels instead of once per filter tap; bits 28..29 = stream-K, same coding: the k-blocks of all
+ * tiles are cut into one equal run per SM (for layers with fewer tiles than SMs); tiles whose k-blocks fall into
+ * several runs are summed in fp32 through a per-device scratch buffer that all streams share, so two stream-K launches
+ * on different streams of one device must not overlap in time. Shapes that do not fit return 1. */
 int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y,
                         int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                         long long ldx, long long ldy, long long ldr, int act, int tile_n, void* stream);

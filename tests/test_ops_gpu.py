@@ -127,6 +127,53 @@ def test_conv_weight_resident_mode_matches_streaming_mode(case):
     assert torch.equal(y_on, y_off)
 
 
+STREAMK_CASES = [
+    # N, H, W, C, K, R, pad, stride, res, tile width (0 = library's choice)
+    (64, 14, 14, 1024, 256, 1, 0, 1, False, 256),    # 98 tiles on 148 SMs: every tile shared by two or three CTAs
+    (64, 14, 14, 256, 256, 3, 1, 1, False, 256),     # im2col loads, 36 k-blocks per tile
+    (64, 14, 14, 256, 1024, 1, 0, 1, True, 256),     # residual, 392 tiles of 4 k-blocks
+    (64, 7, 7, 2048, 512, 1, 0, 1, False, 128),
+    (64, 7, 7, 512, 2048, 1, 0, 1, True, 0),
+    (64, 7, 7, 512, 512, 3, 1, 1, False, 128),
+    (64, 1, 1, 2048, 1000, 1, 0, 1, False, 128),     # classifier GEMM: one row tile, ragged last column tile
+    (64, 14, 14, 1024, 512, 1, 0, 2, False, 0),      # stride-2 downsample (im2col map)
+    (5, 9, 11, 128, 192, 1, 0, 1, True, 64),         # ragged rows, two k-blocks
+    (3, 10, 10, 96, 40, 3, 1, 1, False, 0),          # ragged channels on both sides
+]
+
+
+@pytest.mark.parametrize("case", STREAMK_CASES)
+def test_conv_stream_k_matches_oracle_and_plain_schedule(case):
+    # the k-blocks of all tiles cut into one run per SM; tiles that straddle runs are summed in fp32 through the
+    # library's scratch buffer. Against the oracle (first and last image) and against the plain schedule (all of it);
+    # twice in a row: the hand-over counters must be back at zero after every launch.
+    N, H, W, C, K, Rr, pad, stride, res, bn = case
+    x, w, b = gen((N, C, H, W), 21), gen((K, C, Rr, Rr), 22, 0.02), gen((K,), 23, 0.1)
+    P = (H + 2 * pad - Rr) // stride + 1
+    r = gen((N, K, P, P if H == W else (W + 2 * pad - Rr) // stride + 1), 24) if res else None
+    args = (cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (stride, stride), 1)
+    y_sk = ops.conv_fused(*args, tile_n=(1 << 28) | bn)
+    assert ops.last_status() == 0
+    y_plain = ops.conv_fused(*args, tile_n=(2 << 28) | bn)
+    assert ops.last_status() == 0
+    for img in (0, N - 1):
+        ref = R.conv_fused_ref(x[img:img + 1], w, b, None if r is None else r[img:img + 1], (pad, pad), (stride, stride), 1)
+        close(y_sk[img:img + 1], ref)
+    close(y_sk, y_plain)
+    y_again = ops.conv_fused(*args, tile_n=(1 << 28) | bn)
+    assert ops.last_status() == 0
+    assert torch.equal(y_again, y_sk)           # fixed order of the partial sums: same bits every time
+
+
+def test_conv_stream_k_is_refused_where_it_does_not_apply():
+    x, w = cl(gen((1, 64, 4, 4), 1)), cl(gen((64, 64, 1, 1), 2, 0.05))
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x, w, None, None, (0, 0), (1, 1), 0, tile_n=1 << 28)          # fewer k-blocks than SMs
+    x8, w8 = cl(gen((2, 8, 32, 32), 1)), cl(gen((64, 8, 7, 7), 2, 0.05))
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x8, w8, None, None, (3, 3), (2, 2), 0, tile_n=1 << 28)        # tap-packed stem
+
+
 HALO_CASES = [
     # N, H, W, C, K, dil, res, tile, weight-resident (0 choose / 1 on / 2 off)
     (2, 16, 8, 64, 64, 1, False, 0, 2),        # exactly one patch per image
