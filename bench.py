@@ -277,6 +277,14 @@ def main():
     NBUF = 4      # rotating inputs: 4 x 38.5 MB > the 126 MB L2, on top of ~3.8 GB of activation traffic per step
     xs = [seeded_input((BATCH, 3, size, size), seed=100 * rank + i).to(dev) for i in range(NBUF)]
 
+    # ---------------------------------------------------------------- start-up: first call at the benchmark shape (tile tuning of every layer
+    # unless an earlier process left its choices in the per-user cache, then graph capture)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    y = m.model(xs[0])
+    torch.cuda.synchronize()
+    first_call_s = time.perf_counter() - t0
+
     # launches per forward: count the library's launches over one un-captured forward (after tuning)
     eager = zoo.load(MODEL, "b200", device=dev, seed=1, graphs=False)
     eager.model(xs[0])            # first call: per-layer tile tuning launches extra kernels
@@ -291,13 +299,6 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-
-    # ---------------------------------------------------------------- start-up: first call at the benchmark shape
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    y = m.model(xs[0])
-    torch.cuda.synchronize()
-    first_call_s = time.perf_counter() - t0
 
     # ---------------------------------------------------------------- value: inputs resident in HBM
     for i in range(warmup):

@@ -95,6 +95,7 @@ struct ConvParams {
     // that is cut into gridDim.x equal runs; a tile whose k-blocks fall into several runs is finished by the CTA that
     // holds its first k-block, the others hand their fp32 partial tile over through sk_part (one [128][BN] slot per
     // CTA) and sk_flags (one counter per slot, back at zero when the kernel ends).
+    int w_keep;    // 1: weight loads carry an L2 evict-last hint (the weights of a network are re-read by every forward)
     int sk;
     uint32_t sk_units;
     FastDiv div_kb;
@@ -121,7 +122,8 @@ __device__ __forceinline__ float2 unpack_h2(uint32_t u) {
 // 64-channel staging sub-tile (128-byte swizzle: 16-byte chunk index XOR (row & 7)); `bias_s` at the chunk's bias.
 // ACT: 0 none, 1 relu, 3 silu, 5 gelu (erf), 2 = read p.act at run time. All loads are issued before the arithmetic.
 // `part` / `nparts` / `part_stride` (stream-K only): fp32 partial sums of this row and these columns from `nparts` other
-// CTAs, `part_stride` floats apart, added to the accumulator in that order before the epilogue arithmetic.
+// CTAs (`part` points at this row's float4 of the chunk's first four columns in the first slot, slots are `part_stride`
+// floats apart), added to the accumulator in that order before the epilogue arithmetic.
 template <int ACT, bool RES, int W>
 __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t taddr, uint32_t stage_row, uint32_t ch0,
                                                uint32_t row_xor, uint32_t bias_s, int n, int left,
@@ -139,10 +141,11 @@ __device__ __forceinline__ void epilogue_chunk(const ConvParams& p, uint32_t tad
     }
     tmem_ld_wait();
     for (int q = 0; q < nparts; ++q) {
+        // slot layout: [column / 4][row] float4, so that the 32 rows of a warp read (and wrote) 512 contiguous bytes
         const float4* src = reinterpret_cast<const float4*>(part + static_cast<size_t>(q) * part_stride);
 #pragma unroll
         for (int i = 0; i < W / 4; ++i) {
-            const float4 t = __ldcg(src + i);       // written by another SM during this launch: read past L1
+            const float4 t = __ldcg(src + i * BM);  // written by another SM during this launch: read past L1
             v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + t.x);
             v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + t.y);
             v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + t.z);
@@ -363,24 +366,29 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             bool ok = true;
             const int PQ = p.P * p.Q;
+            const unsigned long long w_policy = l2_policy_evict_last();
+            auto load_w = [&](uint32_t dst, uint32_t bar, int c0, int c1, int c2) {
+                if (p.w_keep) tma_load_3d_hint(dst, &tmap_b, bar, c0, c1, c2, w_policy);
+                else tma_load_3d(dst, &tmap_b, bar, c0, c1, c2);
+            };
             if (p.tapk) {
                 // weights of every tap (taps past R*S are out of bounds of the weight tensor: zero-filled)
                 mbar_expect_tx(bres_full_bar, bres_bytes);
                 for (int t = 0; t < p.kblocks * tpk; ++t)
-                    tma_load_3d(bres_base + static_cast<uint32_t>(t) * tap_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
+                    load_w(bres_base + static_cast<uint32_t>(t) * tap_b_bytes, bres_full_bar, 0, t, 0);
             }
             int m_tile, n_tile;
             if (p.halo == 2) {
                 // stem mode: every tap's [BN][8] block (taps past R*S are out of bounds of the weight tensor: zeros)
                 mbar_expect_tx(bres_full_bar, bres_bytes);
                 for (int t = 0; t < p.stem_taps; ++t)
-                    tma_load_3d(bres_base + static_cast<uint32_t>(t) * stem_b_bytes, &tmap_b, bres_full_bar, 0, t, 0);
+                    load_w(bres_base + static_cast<uint32_t>(t) * stem_b_bytes, bres_full_bar, 0, t, 0);
             } else if (p.bres && tile_at(p, 0, m_tile, n_tile)) {
                 // this CTA's weight tile, all k-blocks, once: k-block kb = (tap kb / cchunks, channels (kb % cchunks)*64)
                 mbar_expect_tx(bres_full_bar, bres_bytes);
                 int tp = 0, cc = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
-                    tma_load_3d(bres_base + static_cast<uint32_t>(kb) * b_kb_bytes, &tmap_b, bres_full_bar, cc * BK, tp,
+                    load_w(bres_base + static_cast<uint32_t>(kb) * b_kb_bytes, bres_full_bar, cc * BK, tp,
                                 n_tile * p.BN);
                     if (++cc == p.cchunks) { cc = 0; ++tp; }
                 }
@@ -393,8 +401,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     int tap = 0, cc = 0;
                     for (int kb = 0; kb < p.kblocks && pre < p.stages; ++kb, ++pre) {
                         mbar_expect_tx(full_bar(pre), stage_bytes);
-                        tma_load_3d(smem_base + static_cast<uint32_t>(pre) * stage_bytes + a_stage_bytes, &tmap_b,
-                                    full_bar(pre), cc * BK, tap, n_tile * p.BN);
+                        load_w(smem_base + static_cast<uint32_t>(pre) * stage_bytes + a_stage_bytes, full_bar(pre), cc * BK, tap, n_tile * p.BN);
                         if (++cc == p.cchunks) { cc = 0; ++tap; }
                     }
                 }
@@ -459,7 +466,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                 break;
                             }
                             mbar_expect_tx(full_bar(stage), stage_bytes);
-                            tma_load_3d(smem_base + static_cast<uint32_t>(stage) * stage_bytes, &tmap_b, full_bar(stage),
+                            load_w(smem_base + static_cast<uint32_t>(stage) * stage_bytes, full_bar(stage),
                                         hc * BK, tp, n0);
                             if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         }
@@ -500,7 +507,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
-                    if (!p.bres && !armed) tma_load_3d(b_dst, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    if (!p.bres && !armed) load_w(b_dst, full_bar(stage), cc * BK, tap, n0);
                     if (p.im2col) {
                         tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
                                            static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
@@ -966,6 +973,7 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t e_phase = 0;
             bool ok = true;
             const int PQ = p.P * p.Q;
+            const unsigned long long w_policy = l2_policy_evict_last();
             asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t u = run_begin;
             SkSeg sg;
@@ -1007,7 +1015,8 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     mbar_expect_tx(full_bar(stage), stage_bytes);
-                    tma_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    if (p.w_keep) tma_load_3d_hint(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0, w_policy);
+                    else tma_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0);
                     if (p.im2col)
                         tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
                                            static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
@@ -1100,16 +1109,16 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 acc_phase ^= 1u << acc;
                 tc_fence_after();
-                float* dst_row = p.sk_part + static_cast<size_t>(blockIdx.x) * slot_floats + static_cast<size_t>(row) * p.BN;
+                float4* slot = reinterpret_cast<float4*>(p.sk_part + static_cast<size_t>(blockIdx.x) * slot_floats);
                 for (int c0 = 32 * group; c0 < p.BN; c0 += 32 * EPI_GROUPS) {
                     uint32_t v[32];
                     __syncwarp();
                     tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c0), v);
                     tmem_ld_wait();
-                    float4* dst = reinterpret_cast<float4*>(dst_row + c0);
+                    float4* dst = slot + static_cast<size_t>(c0 >> 2) * BM + row;      // [column / 4][row]
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        __stcg(dst + i, make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                        __stcg(dst + i * BM, make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
                                                     __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
                 }
                 __threadfence();                 // this thread's partial sums are visible device-wide before the counter moves
@@ -1158,13 +1167,13 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
             const int ncols = min(p.BN, p.K - n0);
-            const float* part_row = p.sk_part + static_cast<size_t>(blockIdx.x + 1) * slot_floats + static_cast<size_t>(row) * p.BN;
+            const float* part_row = p.sk_part + static_cast<size_t>(blockIdx.x + 1) * slot_floats + static_cast<size_t>(row) * 4;
             for (int c0 = 32 * group; c0 < ncols; c0 += 32 * EPI_GROUPS) {
                 const uint32_t sub = stage_row0 + static_cast<uint32_t>(c0 >> 6) * SUB_BYTES;
                 const uint32_t ch0 = static_cast<uint32_t>((c0 & 63) >> 3);
                 const uint32_t bs = bias_s + 4u * static_cast<uint32_t>(n0 + c0);
                 const uint32_t ta = t_row + static_cast<uint32_t>(c0);
-#define SK_CHUNK(A, R) epilogue_chunk<A, R, 32>(p, ta, sub, ch0, row_xor, bs, n0 + c0, ncols - c0, part_row + c0, sg.nparts, slot_floats)
+#define SK_CHUNK(A, R) epilogue_chunk<A, R, 32>(p, ta, sub, ch0, row_xor, bs, n0 + c0, ncols - c0, part_row + static_cast<size_t>(c0) * BM, sg.nparts, slot_floats)
                 switch (variant) {
                     case 0: SK_CHUNK(0, false); break;
                     case 1: SK_CHUNK(0, true); break;
@@ -1373,6 +1382,12 @@ static int pick_bn(int m_tiles, int K, int kblocks, bool tapk, int sms) {
 static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_r,
                               const CUtensorMap& tmap_y, const ConvParams& p, int grid, size_t smem, cudaStream_t stream);
 
+// FVM_B200_WEIGHTS_L2=0 drops the evict-last hint on weight loads (a switch in the style of the reference's CLF_* variables).
+static int weights_keep_hint() {
+    static int v = [] { const char* e = getenv("FVM_B200_WEIGHTS_L2"); return (e && e[0] == '0') ? 0 : 1; }();
+    return v;
+}
+
 // Stride-2 stem over an 8-channel input held as two column-parity planes per image row (x: [N][H][2][W/2][8], the
 // layout fvm_input_nhwc8_split_f32 writes): y = act(conv(x, w) + bias), w [K][R][S][8], symmetric padding, no residual.
 int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K, int R, int S,
@@ -1426,6 +1441,7 @@ int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int 
     p.nh = 3;
     p.act = act;
     p.has_res = 0;
+    p.w_keep = weights_keep_hint();
     p.bias = static_cast<const __half*>(bias);
     p.scale = nullptr;
     p.status = st->status_dev;
@@ -1574,6 +1590,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && ph_hi == 0 && pw_hi == 0);
     p.act = act;
     p.has_res = res != nullptr;
+    p.w_keep = weights_keep_hint();
     p.bias = static_cast<const __half*>(bias);
     p.scale = scale;
     p.status = st->status_dev;
@@ -1592,7 +1609,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // carry activations only, so more tiles' worth of loads are in flight and the weights are not re-read from L2 for
     // every tile. Used when the tile fits in 96 KB, every CTA gets at least two tiles, and the grid can be made a
     // multiple of the n-tile count.
-    // Stream-K: on request, or by default when there are fewer tiles than SMs (see conv_streamk_kernel).
+    // Stream-K (see conv_streamk_kernel): on request only.
     {
         const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
         const long long units = tiles * p.kblocks;
@@ -1600,7 +1617,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
                          units >= st->sms && units < 0x7fffffffll &&
                          static_cast<size_t>(st->sms) * BM * p.BN <= st->sk_floats;
         if (force_sk == 1 && !can) return FVM_ERR_ARG;
-        p.sk = can && (force_sk == 1 || (force_sk == 0 && tiles * 10 < static_cast<long long>(st->sms) * 9)) ? 1 : 0;
+        p.sk = (can && force_sk == 1) ? 1 : 0;     // only on request: the host's per-layer timing decides
         if (p.sk) {
             p.sk_units = static_cast<uint32_t>(units);
             p.div_kb = fastdiv_init(static_cast<uint32_t>(p.kblocks));

@@ -33,7 +33,8 @@
 namespace fvm {
 
 static constexpr int DW_THREADS = 128;
-static constexpr int DW_TW = 8;                 // output columns per thread in the tile kernel
+// output columns per thread in the tile kernel: 8, or 4 for 7-tap filters (fewer registers, more warps per SM)
+__host__ __device__ constexpr int dw_tw(int S) { return S >= 7 ? 4 : 8; }
 static constexpr int DW_SMEM_LIMIT = 96 * 1024; // per CTA: at least two CTAs per SM
 static constexpr int STATUS_WAIT_DW = 0x105;
 
@@ -97,6 +98,7 @@ template <int S, int SW, int ACT>
 __global__ void __launch_bounds__(DW_THREADS)
 dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restrict__ w, const __half* __restrict__ bias,
                __half* __restrict__ y, float* __restrict__ pool_partial, const DwParams p) {
+    constexpr int TW = dw_tw(S);
     extern __shared__ __align__(128) uint8_t dw_smem[];
     const uint32_t smem0 = (smem_u32(dw_smem) + 127u) & ~127u;
     const uint32_t tile_bytes = static_cast<uint32_t>(p.tile_h * p.tile_w * p.cbv) * 16u;
@@ -108,7 +110,7 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
     int tx, ty, vb;
     dw_decode_block(p, tx, ty, vb);
     const long long n = blockIdx.y;
-    const int TWB = p.px * DW_TW, TH = p.py;
+    const int TWB = p.px * TW, TH = p.py;
     const int p0 = ty * TH, q0 = tx * TWB;
     if (!dw_stage(&tmap_x, p, smem0, bar, vb, q0 * SW - p.pw, p0 * p.sh - p.ph, static_cast<int>(n), abort_flag)) return;
 
@@ -116,11 +118,11 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
     const int cell = threadIdx.x / p.cbv;
     const int sx = cell % p.px, sy = cell / p.px;
     const int v = vb * p.cbv + vv;
-    const int pr = p0 + sy, qs = q0 + sx * DW_TW;
+    const int pr = p0 + sy, qs = q0 + sx * TW;
     const bool active = v < (p.C >> 3) && pr < p.P && qs < p.Q;
     float psum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (active) {
-        unsigned long long acc[DW_TW][4];      // fp32 accumulators as packed pairs
+        unsigned long long acc[TW][4];      // fp32 accumulators as packed pairs
         {
             unsigned long long b2[4] = {0ull, 0ull, 0ull, 0ull};
             if (bias) {
@@ -128,32 +130,32 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
                 b2[0] = h2_to_f2(bv.x); b2[1] = h2_to_f2(bv.y); b2[2] = h2_to_f2(bv.z); b2[3] = h2_to_f2(bv.w);
             }
 #pragma unroll
-            for (int j = 0; j < DW_TW; ++j)
+            for (int j = 0; j < TW; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) acc[j][k] = b2[k];
         }
-        constexpr int L = (DW_TW - 1) * SW + S;      // staged columns one kernel row of this thread's strip reads
+        constexpr int L = (TW - 1) * SW + S;      // staged columns one kernel row of this thread's strip reads
         const uint32_t pix = static_cast<uint32_t>(p.cbv) * 16u;
-#pragma unroll
-        for (int r = 0; r < S; ++r) {          // square filter: R == S; unrolled so that the next row's loads issue early
+#pragma unroll(S == 3 ? 3 : 1)
+        for (int r = 0; r < S; ++r) {          // square filter: R == S; short filters unrolled (next row's loads issue early)
             const __half* wrow = w + static_cast<long long>(r) * S * p.C + v * 8;
             uint4 wr[S];
 #pragma unroll
             for (int s2 = 0; s2 < S; ++s2)
                 wr[s2] = __ldg(reinterpret_cast<const uint4*>(wrow + static_cast<long long>(s2) * p.C));
-            __half2 racc[DW_TW][4];
+            __half2 racc[TW][4];
 #pragma unroll
-            for (int j = 0; j < DW_TW; ++j)
+            for (int j = 0; j < TW; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) racc[j][k] = __float2half2_rn(0.f);
-            const uint32_t row_addr = smem0 + static_cast<uint32_t>((sy * p.sh + r) * p.tile_w + sx * DW_TW * SW) * pix +
+            const uint32_t row_addr = smem0 + static_cast<uint32_t>((sy * p.sh + r) * p.tile_w + sx * TW * SW) * pix +
                                       static_cast<uint32_t>(vv) * 16u;
 #pragma unroll
             for (int l = 0; l < L; ++l) {
                 const uint4 xv = lds128(row_addr + static_cast<uint32_t>(l) * pix);
                 const __half2* hx = reinterpret_cast<const __half2*>(&xv);
 #pragma unroll
-                for (int j = 0; j < DW_TW; ++j) {
+                for (int j = 0; j < TW; ++j) {
                     const int s2 = l - j * SW;          // compile-time after unrolling
                     if (s2 >= 0 && s2 < S) {
                         const __half2* hw = reinterpret_cast<const __half2*>(&wr[s2]);
@@ -163,13 +165,13 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
                 }
             }
 #pragma unroll
-            for (int j = 0; j < DW_TW; ++j)
+            for (int j = 0; j < TW; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     acc[j][k] = f2_add(acc[j][k], h2_to_f2(*reinterpret_cast<const uint32_t*>(&racc[j][k])));
         }
 #pragma unroll
-        for (int j = 0; j < DW_TW; ++j) {
+        for (int j = 0; j < TW; ++j) {
             const int q = qs + j;
             if (q < p.Q) {
                 __align__(16) __half2 o[4];
@@ -302,10 +304,10 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
     p.ldy = ldy;
     const int cv = C >> 3;
     out->tile_kernel = R == S && (S == 3 || S == 5 || S == 7) && dh == 1 && dw == 1 && sh == sw && (sw == 1 || sw == 2);
-    // Candidates: channel blocks from the widest acceptable one down, cell grids px x py with px a power of two. The
-    // best product of (useful lanes) x (useful cells: tiles overhang the map) wins; ties go to the patch with the least
-    // staged bytes per output pixel (less border).
-    const int unit = out->tile_kernel ? DW_TW : 1;
+    // Candidates: channel blocks from the widest acceptable one down, cell grids px x py with px a power of two. A
+    // clearly better product of (useful lanes) x (useful cells: tiles overhang the map) wins; among candidates within a
+    // tenth of each other the patch with the least staged bytes per output pixel (least border) is kept.
+    const int unit = out->tile_kernel ? dw_tw(S) : 1;
     double best_score = -1.0, best_cost = 0.0;
     bool found = false;
     for (int cbv = pick_cbv(cv); cbv >= 1; cbv >>= 1) {
@@ -322,7 +324,7 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
             const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * py * tiles_x * px * unit);
             const double score = lane_eff * tile_eff;
             const double cost = static_cast<double>(tile_h) * tile_w / (py * px * unit);
-            if (score > best_score * 1.02 || (score > best_score * 0.98 && cost < best_cost)) {
+            if (score > best_score * 1.10 || (score > best_score * 0.90 && cost < best_cost)) {
                 best_score = score > best_score ? score : best_score;
                 best_cost = cost;
                 found = true;

@@ -39,11 +39,79 @@ _FLUSH = {}
 
 
 def _l2_flush_buffer(device) -> torch.Tensor:
-    """A scratch buffer larger than the 126 MB L2 (one per device, allocated at the first tuning)."""
+    """A scratch buffer larger than the 126 MB L2 (one per device, allocated at the first tuning, released by
+    `release_tuning_buffers`, which the graph runner calls once a forward has been tuned and captured)."""
     key = torch.device(device).index
     if key not in _FLUSH:
         _FLUSH[key] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     return _FLUSH[key]
+
+
+def release_tuning_buffers() -> None:
+    _FLUSH.clear()
+
+
+class TileCache:
+    """Tile codes chosen by timing, kept across processes: one JSON file per (library source hash, SM count) under
+    $FVM_CACHE/fvm_b200 or ~/.cache/fvm_b200. A layer whose key is in the file skips its tuning launches, so the first
+    call at a known shape costs the graph capture only. Written with an atomic replace; FVM_B200_TILE_CACHE=0 turns it
+    off (every process then tunes for itself)."""
+
+    enabled = os.environ.get("FVM_B200_TILE_CACHE", "1") != "0"
+    _data = {}          # device index -> {key: code}
+    _dirty = set()
+
+    @staticmethod
+    def _path(device_index: int) -> str:
+        from . import _lib
+        base = os.environ.get("FVM_CACHE") or os.path.join(os.path.expanduser("~"), ".cache")
+        sms = torch.cuda.get_device_properties(device_index).multi_processor_count
+        return os.path.join(base, "fvm_b200", f"tiles-{_lib.source_hash()[:16]}-sm{sms}.json")
+
+    @classmethod
+    def table(cls, device_index: int) -> dict:
+        if device_index not in cls._data:
+            data = {}
+            if cls.enabled:
+                try:
+                    import json
+                    with open(cls._path(device_index)) as f:
+                        data = {str(k): int(v) for k, v in json.load(f).items()}
+                except (OSError, ValueError):
+                    data = {}
+            cls._data[device_index] = data
+        return cls._data[device_index]
+
+    @classmethod
+    def put(cls, device_index: int, key: str, code: int) -> None:
+        cls.table(device_index)[key] = int(code)
+        cls._dirty.add(device_index)
+
+    @classmethod
+    def flush(cls) -> None:
+        """Writes what was tuned since the last flush (called by the graph runner after a capture)."""
+        if not cls.enabled:
+            cls._dirty.clear()
+            return
+        import json
+        for idx in list(cls._dirty):
+            path = cls._path(idx)
+            try:
+                os.makedirs(os.path.dirname(path), exist_ok=True)
+                merged = {}
+                try:
+                    with open(path) as f:
+                        merged = json.load(f)
+                except (OSError, ValueError):
+                    pass
+                merged.update(cls._data[idx])
+                tmp = f"{path}.tmp{os.getpid()}"
+                with open(tmp, "w") as f:
+                    json.dump(merged, f)
+                os.replace(tmp, path)
+            except OSError:
+                pass                      # a read-only home: the choices live for this process only
+        cls._dirty.clear()
 
 
 class FusedConv(nn.Module):
@@ -96,7 +164,17 @@ class FusedConv(nn.Module):
         t = self._tiles.get(key)
         if t is not None:
             return t
-        if not AUTOTUNE or torch.cuda.is_current_stream_capturing():
+        if not AUTOTUNE:
+            return 0
+        K_, C_, R_k, S_k = self.w.shape
+        ckey = (f"{tuple(x.shape)}|ld{x.stride(3) if x.shape[3] > 1 else 0}|K{K_}R{R_k}S{S_k}|s{self.stride}p{self.padding}"
+                f"d{self.dilation}|act{act}|res{int(res is not None)}|scale{int(self.scale is not None)}")
+        dev_idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        cached = TileCache.table(dev_idx).get(ckey)
+        if cached is not None:
+            self._tiles[key] = cached
+            return cached
+        if torch.cuda.is_current_stream_capturing():
             return 0
         K = self.w.shape[0]
         # tile code: low 16 bits = output-channel tile (0 = library's choice), bits 16.. = 128-pixel sub-tiles per tile
@@ -155,6 +233,7 @@ class FusedConv(nn.Module):
                 if ms < best_ms * 0.97:      # a different tile must be clearly faster than the incumbent
                     best, best_ms = c, ms
         self._tiles[key] = best
+        TileCache.put(dev_idx, ckey, best)
         return best
 
     def forward_image(self, x: torch.Tensor) -> torch.Tensor:

@@ -53,6 +53,9 @@ class GraphRunner:
                 self.fn(static_in)       # outside capture: first-call set-up and per-layer tile tuning of every op
         cur.wait_stream(side)
         torch.cuda.synchronize()
+        from . import layers
+        layers.release_tuning_buffers()      # the L2-flush buffer of the tile tuning is not needed once every layer is tuned
+        layers.TileCache.flush()             # tile codes measured just now are kept for later processes
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             static_out = self.fn(static_in)

@@ -131,14 +131,14 @@ STREAMK_CASES = [
     # N, H, W, C, K, R, pad, stride, res, tile width (0 = library's choice)
     (64, 14, 14, 1024, 256, 1, 0, 1, False, 256),    # 98 tiles on 148 SMs: every tile shared by two or three CTAs
     (64, 14, 14, 256, 256, 3, 1, 1, False, 256),     # im2col loads, 36 k-blocks per tile
-    (64, 14, 14, 256, 1024, 1, 0, 1, True, 256),     # residual, 392 tiles of 4 k-blocks
+    (64, 14, 14, 256, 1024, 1, 0, 1, True, 128),     # residual, 784 tiles of 4 k-blocks
     (64, 7, 7, 2048, 512, 1, 0, 1, False, 128),
     (64, 7, 7, 512, 2048, 1, 0, 1, True, 0),
     (64, 7, 7, 512, 512, 3, 1, 1, False, 128),
     (64, 1, 1, 2048, 1000, 1, 0, 1, False, 128),     # classifier GEMM: one row tile, ragged last column tile
     (64, 14, 14, 1024, 512, 1, 0, 2, False, 0),      # stride-2 downsample (im2col map)
-    (5, 9, 11, 128, 192, 1, 0, 1, True, 64),         # ragged rows, two k-blocks
-    (3, 10, 10, 96, 40, 3, 1, 1, False, 0),          # ragged channels on both sides
+    (37, 9, 11, 128, 192, 1, 0, 1, True, 64),        # ragged rows, two k-blocks
+    (12, 10, 10, 96, 40, 3, 1, 1, False, 0),         # ragged channels on both sides
 ]
 
 
