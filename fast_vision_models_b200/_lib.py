@@ -164,7 +164,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "fvm_conv2d_f16_tile": ([_P] * 6 + [_I] * 13 + [_L] * 3 + [_I, _I, _P], _I),
         "fvm_conv2d_f16_pad": ([_P] * 6 + [_I] * 13 + [_L] * 3 + [_I, _I, _I, _I, _P], _I),
         "fvm_dwconv_f16": ([_P] * 5 + [_I] * 12 + [_L] * 2 + [_I, _P], _I),
-        "fvm_dwconv_pool_slots": ([_I] * 11, _I),
+        "fvm_dwconv_pool_slots": ([_I] * 12, _I),
         "fvm_se_gate_pooled_f16": ([_P, _I] + [_P] * 5 + [_I] * 4 + [_F, _P], _I),
         "fvm_maxpool_f16": ([_P] * 2 + [_I] * 12 + [_P], _I),
         "fvm_avgpool_f16": ([_P] * 2 + [_I] * 13 + [_P], _I),

@@ -95,7 +95,6 @@ struct ConvParams {
     // that is cut into gridDim.x equal runs; a tile whose k-blocks fall into several runs is finished by the CTA that
     // holds its first k-block, the others hand their fp32 partial tile over through sk_part (one [128][BN] slot per
     // CTA) and sk_flags (one counter per slot, back at zero when the kernel ends).
-    int w_keep;    // 1: weight loads carry an L2 evict-last hint (the weights of a network are re-read by every forward)
     int sk;
     uint32_t sk_units;
     FastDiv div_kb;
@@ -366,10 +365,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             bool ok = true;
             const int PQ = p.P * p.Q;
-            const unsigned long long w_policy = l2_policy_evict_last();
             auto load_w = [&](uint32_t dst, uint32_t bar, int c0, int c1, int c2) {
-                if (p.w_keep) tma_load_3d_hint(dst, &tmap_b, bar, c0, c1, c2, w_policy);
-                else tma_load_3d(dst, &tmap_b, bar, c0, c1, c2);
+                tma_load_3d(dst, &tmap_b, bar, c0, c1, c2);
             };
             if (p.tapk) {
                 // weights of every tap (taps past R*S are out of bounds of the weight tensor: zero-filled)
@@ -973,7 +970,6 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t e_phase = 0;
             bool ok = true;
             const int PQ = p.P * p.Q;
-            const unsigned long long w_policy = l2_policy_evict_last();
             asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t u = run_begin;
             SkSeg sg;
@@ -1015,8 +1011,7 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     mbar_expect_tx(full_bar(stage), stage_bytes);
-                    if (p.w_keep) tma_load_3d_hint(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0, w_policy);
-                    else tma_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0);
+                    tma_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, full_bar(stage), cc * BK, tap, n0);
                     if (p.im2col)
                         tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
                                            static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
@@ -1382,12 +1377,6 @@ static int pick_bn(int m_tiles, int K, int kblocks, bool tapk, int sms) {
 static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_r,
                               const CUtensorMap& tmap_y, const ConvParams& p, int grid, size_t smem, cudaStream_t stream);
 
-// FVM_B200_WEIGHTS_L2=0 drops the evict-last hint on weight loads (a switch in the style of the reference's CLF_* variables).
-static int weights_keep_hint() {
-    static int v = [] { const char* e = getenv("FVM_B200_WEIGHTS_L2"); return (e && e[0] == '0') ? 0 : 1; }();
-    return v;
-}
-
 // Stride-2 stem over an 8-channel input held as two column-parity planes per image row (x: [N][H][2][W/2][8], the
 // layout fvm_input_nhwc8_split_f32 writes): y = act(conv(x, w) + bias), w [K][R][S][8], symmetric padding, no residual.
 int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K, int R, int S,
@@ -1441,7 +1430,6 @@ int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int 
     p.nh = 3;
     p.act = act;
     p.has_res = 0;
-    p.w_keep = weights_keep_hint();
     p.bias = static_cast<const __half*>(bias);
     p.scale = nullptr;
     p.status = st->status_dev;
@@ -1590,7 +1578,6 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && ph_hi == 0 && pw_hi == 0);
     p.act = act;
     p.has_res = res != nullptr;
-    p.w_keep = weights_keep_hint();
     p.bias = static_cast<const __half*>(bias);
     p.scale = scale;
     p.status = st->status_dev;

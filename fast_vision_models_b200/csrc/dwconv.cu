@@ -43,6 +43,7 @@ struct DwParams {
     int sh, sw, ph, pw, dh, dw;
     int cbv;                 // channel vectors (8 channels each) per block: 8, 4, 2 or 1
     int px, py;              // thread grid over the tile: px x py "cells" per channel vector (px * py * cbv = 128)
+    int rpt;                 // tile kernel: consecutive output rows per thread (a taller tile has less border per output)
     int tiles_x, tiles_y, vblocks;
     int tile_h, tile_w;      // staged input patch in pixels
     int act;
@@ -110,7 +111,7 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
     int tx, ty, vb;
     dw_decode_block(p, tx, ty, vb);
     const long long n = blockIdx.y;
-    const int TWB = p.px * TW, TH = p.py;
+    const int TWB = p.px * TW, TH = p.py * p.rpt;
     const int p0 = ty * TH, q0 = tx * TWB;
     if (!dw_stage(&tmap_x, p, smem0, bar, vb, q0 * SW - p.pw, p0 * p.sh - p.ph, static_cast<int>(n), abort_flag)) return;
 
@@ -118,10 +119,13 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
     const int cell = threadIdx.x / p.cbv;
     const int sx = cell % p.px, sy = cell / p.px;
     const int v = vb * p.cbv + vv;
-    const int pr = p0 + sy, qs = q0 + sx * TW;
-    const bool active = v < (p.C >> 3) && pr < p.P && qs < p.Q;
+    const int qs = q0 + sx * TW;
+    const bool active = v < (p.C >> 3) && qs < p.Q;
     float psum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (active) {
+    for (int rr = 0; active && rr < p.rpt; ++rr) {
+        const int ly = sy * p.rpt + rr;          // output row inside the tile
+        const int pr = p0 + ly;
+        if (pr >= p.P) break;
         unsigned long long acc[TW][4];      // fp32 accumulators as packed pairs
         {
             unsigned long long b2[4] = {0ull, 0ull, 0ull, 0ull};
@@ -148,7 +152,7 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
             for (int j = 0; j < TW; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) racc[j][k] = __float2half2_rn(0.f);
-            const uint32_t row_addr = smem0 + static_cast<uint32_t>((sy * p.sh + r) * p.tile_w + sx * TW * SW) * pix +
+            const uint32_t row_addr = smem0 + static_cast<uint32_t>((ly * p.sh + r) * p.tile_w + sx * TW * SW) * pix +
                                       static_cast<uint32_t>(vv) * 16u;
 #pragma unroll
             for (int l = 0; l < L; ++l) {
@@ -316,21 +320,26 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
         const double lane_eff = static_cast<double>(cv) / (vblocks * cbv);
         for (int px = 1; px <= cells; px <<= 1) {
             const int py = cells / px;
-            const int tile_w = (px * unit - 1) * sw + (S - 1) * dw + 1;
-            const int tile_h = (py - 1) * sh + (R - 1) * dh + 1;
-            const size_t bytes = static_cast<size_t>(tile_h) * tile_w * cbv * 16;
-            if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 > static_cast<size_t>(DW_SMEM_LIMIT)) continue;
-            const int tiles_x = (p.Q + px * unit - 1) / (px * unit), tiles_y = (p.P + py - 1) / py;
-            const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * py * tiles_x * px * unit);
-            const double score = lane_eff * tile_eff;
-            const double cost = static_cast<double>(tile_h) * tile_w / (py * px * unit);
-            if (score > best_score * 1.10 || (score > best_score * 0.90 && cost < best_cost)) {
-                best_score = score > best_score ? score : best_score;
-                best_cost = cost;
-                found = true;
-                p.cbv = cbv; p.px = px; p.py = py; p.tile_w = tile_w; p.tile_h = tile_h;
-                p.tiles_x = tiles_x; p.tiles_y = tiles_y; p.vblocks = vblocks;
-                out->smem = 128 + bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
+            for (int rpt = 1; rpt <= (out->tile_kernel ? 8 : 1); ++rpt) {
+                const int rows = py * rpt;
+                const int tile_w = (px * unit - 1) * sw + (S - 1) * dw + 1;
+                const int tile_h = (rows - 1) * sh + (R - 1) * dh + 1;
+                const size_t bytes = static_cast<size_t>(tile_h) * tile_w * cbv * 16;
+                if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 > static_cast<size_t>(DW_SMEM_LIMIT)) break;
+                const int tiles_x = (p.Q + px * unit - 1) / (px * unit), tiles_y = (p.P + rows - 1) / rows;
+                // enough CTAs to fill the machine a few times over, or the layer is too small to care
+                if (rpt > 1 && static_cast<long long>(tiles_x) * tiles_y * vblocks * N < 4ll * 148 * 4) break;
+                const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * rows * tiles_x * px * unit);
+                const double score = lane_eff * tile_eff;
+                const double cost = static_cast<double>(tile_h) * tile_w / (rows * px * unit);
+                if (score > best_score * 1.10 || (score > best_score * 0.90 && cost < best_cost)) {
+                    best_score = score > best_score ? score : best_score;
+                    best_cost = cost;
+                    found = true;
+                    p.cbv = cbv; p.px = px; p.py = py; p.rpt = rpt; p.tile_w = tile_w; p.tile_h = tile_h;
+                    p.tiles_x = tiles_x; p.tiles_y = tiles_y; p.vblocks = vblocks;
+                    out->smem = 128 + bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
+                }
             }
         }
         if (found && best_score > 0.97) break;       // narrower channel blocks only when the wide ones waste lanes
@@ -342,11 +351,12 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
 
 using namespace fvm;
 
-extern "C" int fvm_dwconv_pool_slots(int H, int W, int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw) {
+extern "C" int fvm_dwconv_pool_slots(int N, int H, int W, int C, int R, int S, int ph, int pw, int sh, int sw, int dh,
+                                     int dw) {
     DwPlan plan;
-    if (H <= 0 || W <= 0 || C <= 0 || (C & 7) || R <= 0 || S <= 0 || sh <= 0 || sw <= 0 || dh <= 0 || dw <= 0 || ph < 0 || pw < 0)
+    if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || (C & 7) || R <= 0 || S <= 0 || sh <= 0 || sw <= 0 || dh <= 0 || dw <= 0 || ph < 0 || pw < 0)
         return -1;
-    if (!dw_plan(1, H, W, C, R, S, ph, pw, sh, sw, dh, dw, C, 0, &plan)) return -1;
+    if (!dw_plan(N, H, W, C, R, S, ph, pw, sh, sw, dh, dw, C, 0, &plan)) return -1;
     return plan.p.tiles_x * plan.p.tiles_y;
 }
 

@@ -124,21 +124,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* desc, uint
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
-// L2 eviction policy for loads of data that is re-read by every later launch (weights): kept in L2 in preference to
-// streaming data. The 3-D load with such a policy as cache hint.
-__device__ __forceinline__ unsigned long long l2_policy_evict_last() {
-    unsigned long long pol;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2,
-                                                 unsigned long long policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
-        : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2, int c3) {
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"

@@ -269,7 +269,7 @@ def dwconv(x, w_rsc, bias=None, stride=(1, 1), padding=(0, 0), act: int = 0, dil
         bias = bias.contiguous()
     partial = None
     if pool:
-        slots = int(lib().fvm_dwconv_pool_slots(H, W, C, R, S, ph, pw_, sh, sw, dh, dw))
+        slots = int(lib().fvm_dwconv_pool_slots(N, H, W, C, R, S, ph, pw_, sh, sw, dh, dw))
         if slots <= 0:
             raise FvmError("dwconv: unsupported geometry")
         partial = torch.empty((N, slots, C), dtype=torch.float32, device=x.device)

@@ -97,7 +97,7 @@ int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias, const voi
  * fp16-rounded outputs, laid out [N][slots][C] with slots = fvm_dwconv_pool_slots(...) for the same geometry; every
  * element is written (no zeroing needed) and the sums do not depend on scheduling (no atomics). The mean over the
  * pixels is sum over slots / (P*Q): fvm_se_gate_pooled_f16 takes the partial sums as they are. */
-int fvm_dwconv_pool_slots(int H, int W, int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw);
+int fvm_dwconv_pool_slots(int N, int H, int W, int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw);
 int fvm_dwconv_f16(const void* x, const void* w_rsc, const void* bias, void* y, float* pool_partial, int N, int H, int W,
                    int C, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw, long long ldx, long long ldy,
                    int act, void* stream);

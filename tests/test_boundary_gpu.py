@@ -133,7 +133,9 @@ def test_generic_graph_pass_matches_upstream_fp32(name):
     from fast_vision_models_b200.classification.fast import Fast
     from fast_vision_models_b200.classification.fused import fuse_graph
     from fast_vision_models_b200.weights import seeded_init, seeded_input
-    model = seeded_init(torchvision.models.get_model(name, weights=None), seed=1)
+    model = torchvision.models.get_model(name, weights=None).eval()
+    if name != "densenet121":      # 120 concatenating layers with randomised BatchNorm statistics leave the fp16 range
+        model = seeded_init(model, seed=1)          # (plain fp16 PyTorch overflows too); DenseNet keeps torchvision's init
     net = Fast(fuse_graph(model)).to(DEV)          # what optimize() builds for a family without a hand-built compiler
     stats = net.net.gm.fvm_stats
     assert stats["conv_fused"] >= 10 and stats["stem_pad"] == 1
