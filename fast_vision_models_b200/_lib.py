@@ -174,6 +174,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "fvm_global_avgpool_f16_noalloc_max_floats": ([], _L),
         "fvm_se_gate_f16": ([_P] * 6 + [_I] * 4 + [_F, _P], _I),
         "fvm_se_scale_f16": ([_P] * 3 + [_I] * 3 + [_P], _I),
+        "fvm_gate_weights_f16": ([_P] * 3 + [_I] * 3 + [_P], _I),
+        "fvm_conv1x1_wbatch_f16": ([_P] * 5 + [_I] * 5 + [_L] * 3 + [_I, _P], _I),
         "fvm_layernorm_cl_f16": ([_P] * 4 + [_L, _I, _F, _L, _L, _P], _I),
         "fvm_input_nhwc8_f32": ([_P] * 2 + [_I] * 4 + [_P], _I),
         "fvm_input_nhwc8_split_f32": ([_P] * 2 + [_I] * 4 + [_P], _I),
@@ -202,7 +204,7 @@ OPTIONAL_SIGNATURES: dict = {}
 EXPORTED = ["fvm_init", "fvm_query", "fvm_last_status", "fvm_selftest_wait_expiry", "fvm_conv2d_f16", "fvm_conv2d_f16_tile", "fvm_conv2d_f16_pad", "fvm_dwconv_f16", "fvm_dwconv_pool_slots", "fvm_se_gate_pooled_f16", "fvm_maxpool_f16",
             "fvm_avgpool_f16", "fvm_gap_scratch_floats", "fvm_global_avgpool_f16", "fvm_global_avgpool_f16_noalloc",
             "fvm_global_avgpool_f16_noalloc_max_floats", "fvm_se_gate_f16",
-            "fvm_se_scale_f16", "fvm_layernorm_cl_f16", "fvm_input_nhwc8_f32", "fvm_input_nhwc8_split_f32",
+            "fvm_se_scale_f16", "fvm_gate_weights_f16", "fvm_conv1x1_wbatch_f16", "fvm_layernorm_cl_f16", "fvm_input_nhwc8_f32", "fvm_input_nhwc8_split_f32",
             "fvm_input_nhwc8_f16", "fvm_input_nhwc8_split_f16",
             "fvm_stem_conv_s2_f16", "fvm_bias_act_f16",
             "fvm_affine_act_f16", "fvm_add_act_f16", "fvm_bilinear_f16", "fvm_up_argmax_f16"]

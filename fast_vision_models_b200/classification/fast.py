@@ -28,7 +28,7 @@ import torch
 from torch import nn
 
 from .. import fold, ops
-from ..layers import DepthwiseConv, FusedConv, LayerNormCL, SqueezeExcite, act_code
+from ..layers import GATE_IN_WEIGHTS, DepthwiseConv, FusedConv, LayerNormCL, SqueezeExcite, act_code
 from ..runtime import GraphRunner
 
 
@@ -128,9 +128,13 @@ class MBConvBlock(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self.expand(x) if self.expand is not None else x
         y, partial = self.dw(y, pool=True)      # the squeeze sums come out of the depthwise conv's epilogue
-        y = self.se(y, partial)
-        # eval-mode stochastic depth is the identity: the residual add rides in the project conv's epilogue
-        return self.project(y, res=x if self.use_res else None)
+        res = x if self.use_res else None      # eval-mode stochastic depth is the identity: the add rides in the epilogue
+        pj = self.project
+        if GATE_IN_WEIGHTS and pj.scale is None and pj.w.shape[2] == 1 and pj.w.shape[3] == 1 and pj.stride == (1, 1):
+            # the gate multiplies the project conv's weights (per image) instead of the activations: no pass over y
+            w_n = ops.gate_weights(pj.w, self.se.gate(y, partial))
+            return ops.conv1x1_wbatch(y, w_n, pj.b, res, pj.act)
+        return pj(self.se(y, partial), res=res)
 
 
 class B200EfficientNet(nn.Module):

@@ -138,6 +138,15 @@ extern "C" int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias
                          tile_n, ph_hi, pw_hi, static_cast<cudaStream_t>(stream));
 }
 
+// 1x1 stride-1 convolution whose weights differ per image: w_n is [N][K][C]. Used for the project conv of a
+// squeeze-excite block with the gate folded into the weights (see fvm_gate_weights_f16).
+extern "C" int fvm_conv1x1_wbatch_f16(const void* x, const void* w_n, const void* bias, const void* res, void* y, int N,
+                                      int H, int W, int C, int K, long long ldx, long long ldy, long long ldr, int act,
+                                      void* stream) {
+    return conv2d_launch(x, w_n, bias, res, nullptr, y, N, H, W, C, K, 1, 1, 0, 0, 1, 1, 1, 1, ldx, ldy, ldr, act, 0, -1, -1,
+                         static_cast<cudaStream_t>(stream), 1);
+}
+
 // Stride-2 stem on the column-parity-split 8-channel input (see stem_s2_launch).
 extern "C" int fvm_stem_conv_s2_f16(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int K,
                                     int R, int S, int ph, int pw, long long ldy, int act, void* stream) {

@@ -302,6 +302,30 @@ __global__ void se_scale_kernel(const __half* __restrict__ x, const __half* __re
     stg16(y + i * 8, o.u);
 }
 
+// Squeeze-excite gate folded into the weights of the 1x1 conv that follows: out[n][k][c] = half(w[k][c] * half(sigmoid(s[n][c])))
+// -- the same rounded gate as se_scale_kernel multiplies the activations with (reference: r3.cu:312-315), applied to
+// the other operand of the products instead, so that the scaled activation tensor is never written or re-read.
+__global__ void gate_weights_kernel(const __half* __restrict__ w, const __half* __restrict__ s, __half* __restrict__ out,
+                                    int K, int C, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;     // one 8-channel vector
+    if (i >= total) return;
+    const int cv = C >> 3;
+    const int v = static_cast<int>(i % cv);
+    const long long t = i / cv;
+    const int k = static_cast<int>(t % K);
+    const long long n = t / K;
+    V8 a, g, o;
+    a.u = ldg16(w + (static_cast<long long>(k) * C + v * 8));
+    g.u = ldg16(s + n * C + v * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(g.h2[j]);
+        const __half2 sg = __floats2half2_rn(__fdividef(1.f, 1.f + __expf(-f.x)), __fdividef(1.f, 1.f + __expf(-f.y)));
+        o.h2[j] = __hmul2(a.h2[j], sg);
+    }
+    stg16(out + i * 8, o.u);
+}
+
 // ------------------------------------------------------------------------------------------- channels-last LayerNorm
 // G lanes cooperate on one row (G = 4, 8, 16 or 32) and each lane holds VPL 16-byte vectors of it, G * VPL being the
 // smallest cover of the row's C / 8 vectors (C = 96: 4 lanes x 3 vectors, every lane busy). A lane group normalises
@@ -700,6 +724,15 @@ extern "C" int fvm_se_gate_pooled_f16(const float* partial, int slots, const voi
                                       void* stream) {
     if (mean_scale == 0.f) return FVM_ERR_ARG;
     return se_gate_launch(partial, slots, w1, b1, w2, b2, s, N, C, Cs, act, mean_scale, stream);
+}
+
+extern "C" int fvm_gate_weights_f16(const void* w, const void* s, void* out, int N, int K, int C, void* stream) {
+    if (!w || !s || !out || N <= 0 || K <= 0 || C <= 0 || (C & 7) || !aligned16(w) || !aligned16(s) || !aligned16(out))
+        return FVM_ERR_ARG;
+    const long long total = static_cast<long long>(N) * K * (C >> 3);
+    gate_weights_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(w), static_cast<const __half*>(s), static_cast<__half*>(out), K, C, total);
+    FVM_LAUNCH_CHECK();
 }
 
 extern "C" int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C, void* stream) {

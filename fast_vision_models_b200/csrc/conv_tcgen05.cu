@@ -95,6 +95,10 @@ struct ConvParams {
     // that is cut into gridDim.x equal runs; a tile whose k-blocks fall into several runs is finished by the CTA that
     // holds its first k-block, the others hand their fp32 partial tile over through sk_part (one [128][BN] slot per
     // CTA) and sk_flags (one counter per slot, back at zero when the kernel ends).
+    // per-image weights (1x1 stride-1 only): w is [N][K][C], image n uses its own [K][C] block; an m-tile is 128 pixels
+    // of ONE image (wb_tpi tiles per image), activations / residual / output are addressed as (channel, pixel, image)
+    int wb, wb_tpi;
+    FastDiv div_tpi;
     int sk;
     uint32_t sk_units;
     FastDiv div_kb;
@@ -393,7 +397,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // Streamed weights: the B tiles of the first k-blocks (one per pipeline stage) are requested before the wait
             // as well; their barriers are armed for the whole stage, the A tiles follow after the wait.
             int pre = 0;
-            if (!p.tapk && !p.bres && !p.halo) {
+            if (!p.tapk && !p.bres && !p.halo && !p.wb) {
                 for (int pit = 0; pre < p.stages && tile_at(p, pit, m_tile, n_tile); ++pit) {
                     int tap = 0, cc = 0;
                     for (int kb = 0; kb < p.kblocks && pre < p.stages; ++kb, ++pre) {
@@ -410,6 +414,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int pit = 0; ok && tile_at(p, pit, m_tile, n_tile); ++pit) {
                 const int m0 = m_tile * BM * p.mt;
                 const int n0 = n_tile * p.BN;
+                int wb_img = 0, wb_row0 = 0;      // per-image weights: m_tile = (image, 128-pixel tile of that image)
+                if (p.wb) {
+                    wb_img = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_tpi));
+                    wb_row0 = (m_tile - wb_img * p.wb_tpi) * BM;
+                }
                 // halo mode: m_tile = (image, patch row, patch column)
                 int himg = 0, hy0 = 0, hx0 = 0;
                 if (p.halo) {
@@ -434,6 +443,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             const uint32_t dst = epi_base + static_cast<uint32_t>(e) * epi_bytes +
                                                  static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES;
                             if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg);
+                            else if (p.wb) tma_load_3d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, wb_row0, wb_img);
                             else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
                         }
                     if (++e == p.nepi) e = 0;
@@ -504,10 +514,12 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
-                    if (!p.bres && !armed) load_w(b_dst, full_bar(stage), cc * BK, tap, n0);
+                    if (!p.bres && !armed) load_w(b_dst, full_bar(stage), cc * BK, tap, n0 + wb_img * p.K);
                     if (p.im2col) {
                         tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
                                            static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                    } else if (p.wb) {
+                        tma_load_3d(a_dst, &tmap_a, full_bar(stage), cc * BK, wb_row0, wb_img);
                     } else {
                         for (int l = 0; l < p.a_loads; ++l)
                             tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage), cc * BK,
@@ -819,7 +831,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         tma_store_4d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
                                      n0 + sub * 64, (rem - ty * p.tiles_x) * HALO_TW, ty * HALO_TH, himg);
                 }
-                for (int mt = 0; !p.halo && mt < p.mt && m0 + mt * BM < p.M; ++mt)     // sub-tiles past the last row: nothing to store
+                if (p.wb) {       // per-image weights: (channel, pixel of the image, image), clipped at the image's last pixel
+                    const int wb_img = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_tpi));
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_store_3d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                     n0 + sub * 64, (m_tile - wb_img * p.wb_tpi) * BM, wb_img);
+                }
+                for (int mt = 0; !p.halo && !p.wb && mt < p.mt && m0 + mt * BM < p.M; ++mt)     // sub-tiles past the last row: nothing to store
                     for (int sub = 0; sub < nsub; ++sub)
                         tma_store_2d(&tmap_y,
                                      epi_base + static_cast<uint32_t>(e) * epi_bytes +
@@ -1496,7 +1514,7 @@ int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int 
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int w_per_image) {
     // ph / pw pad the top / left; ph_hi / pw_hi the bottom / right (negative: same as top / left)
     if (ph_hi < 0) ph_hi = ph;
     if (pw_hi < 0) pw_hi = pw;
@@ -1535,6 +1553,16 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.kblocks = R * S * p.cchunks;
     p.m_tiles = (p.M + BM - 1) / BM;
     p.taps = R * S;
+    if (w_per_image) {
+        // w is [N][K][C]: 1x1 stride-1 only, tiles never straddle images
+        if (R != 1 || S != 1 || sh != 1 || sw != 1 || ph || pw || ph_hi || pw_hi || force_mt > 1 || force_halo == 1 ||
+            force_bres == 1 || force_sk == 1)
+            return FVM_ERR_ARG;
+        p.wb = 1;
+        p.wb_tpi = (P * Q + BM - 1) / BM;
+        p.div_tpi = fastdiv_init(static_cast<uint32_t>(p.wb_tpi));
+        p.m_tiles = N * p.wb_tpi;
+    }
     // Tap-packed mode for 8-channel inputs (zero-padded RGB stems): 8 taps per k-block instead of one tap with 56 of
     // its 64 channels empty. Needs all output channels in one tile (the weights stay resident in shared memory).
     {
@@ -1588,7 +1616,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // overlap between the roles), so the default stays at one sub-tile; the host's per-layer tuning may force more.
     p.mt = force_mt > 0 ? force_mt : 1;
     if (p.mt != 1 && p.mt != 2 && p.mt != 4) return FVM_ERR_ARG;
-    if (!p.halo) p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
+    if (!p.halo && !p.wb) p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
     p.a_rows = BM * p.mt < 256 ? BM * p.mt : 256;
     p.a_loads = BM * p.mt / p.a_rows;
 
@@ -1600,7 +1628,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     {
         const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
         const long long units = tiles * p.kblocks;
-        const bool can = !p.tapk && !p.halo && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
+        const bool can = !p.tapk && !p.halo && !p.wb && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
                          units >= st->sms && units < 0x7fffffffll &&
                          static_cast<size_t>(st->sms) * BM * p.BN <= st->sk_floats;
         if (force_sk == 1 && !can) return FVM_ERR_ARG;
@@ -1614,7 +1642,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     }
     SmemPlan sp;
     p.bres = 0;
-    if (!p.sk && !p.tapk && force_bres != 2 && p.n_tiles <= st->sms) {
+    if (!p.sk && !p.wb && !p.tapk && force_bres != 2 && p.n_tiles <= st->sms) {
         const long long wbytes = static_cast<long long>(p.kblocks) * p.BN * BK * 2;
         const int cta_per_n = st->sms / p.n_tiles;
         const bool worth = p.m_tiles >= 2 * cta_per_n;
@@ -1661,6 +1689,19 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         } else {
             tmap_r = tmap_y;
         }
+    } else if (p.wb) {
+        // output / residual as (K, pixel of the image, image): 64-channel x 128-pixel boxes, clipped per image
+        const unsigned long long dims[3] = {static_cast<unsigned long long>(K), static_cast<unsigned long long>(P) * Q,
+                                            static_cast<unsigned long long>(N)};
+        const unsigned box[3] = {64, BM, 1};
+        const unsigned long long ystr[2] = {static_cast<unsigned long long>(ldy) * 2, static_cast<unsigned long long>(P) * Q * ldy * 2};
+        if (encode_tiled_f16(&tmap_y, y, 3, dims, ystr, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        if (res) {
+            const unsigned long long rstr[2] = {static_cast<unsigned long long>(ldr) * 2, static_cast<unsigned long long>(P) * Q * ldr * 2};
+            if (encode_tiled_f16(&tmap_r, res, 3, dims, rstr, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        } else {
+            tmap_r = tmap_y;
+        }
     } else {
         // output [M, K] (row stride ldy) and residual [M, K] (row stride ldr): 64-channel x 128-row boxes
         cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(p.M)};
@@ -1682,8 +1723,9 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         }
     }
     {
-        // weights [K][R*S][C]
-        cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(R * S), static_cast<cuuint64_t>(K)};
+        // weights [K][R*S][C] (per-image weights: [N * K][1][C], image n's rows start at n * K)
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(R * S),
+                              static_cast<cuuint64_t>(K) * (p.wb ? N : 1)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 2, static_cast<cuuint64_t>(R) * S * C * 2};
         cuuint32_t box[3] = {static_cast<cuuint32_t>(p.tapk ? p.tapk : BK), 1, static_cast<cuuint32_t>(p.BN)};
         cuuint32_t estr[3] = {1, 1, 1};
@@ -1706,6 +1748,12 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
                                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
+    } else if (p.wb) {
+        const unsigned long long dims[3] = {static_cast<unsigned long long>(C), static_cast<unsigned long long>(P) * Q,
+                                            static_cast<unsigned long long>(N)};
+        const unsigned long long strides[2] = {static_cast<unsigned long long>(ldx) * 2, static_cast<unsigned long long>(P) * Q * ldx * 2};
+        const unsigned box[3] = {BK, BM, 1};
+        if (encode_tiled_f16(&tmap_a, x, 3, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
     } else if (!p.im2col) {
         cuuint64_t dims[2] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(p.M)};
         cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldx) * 2};

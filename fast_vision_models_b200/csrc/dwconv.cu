@@ -33,8 +33,8 @@
 namespace fvm {
 
 static constexpr int DW_THREADS = 128;
-// output columns per thread in the tile kernel: 8, or 4 for 7-tap filters (fewer registers, more warps per SM)
-__host__ __device__ constexpr int dw_tw(int S) { return S >= 7 ? 4 : 8; }
+// output columns per thread in the tile kernel
+__host__ __device__ constexpr int dw_tw(int) { return 8; }
 static constexpr int DW_SMEM_LIMIT = 96 * 1024; // per CTA: at least two CTAs per SM
 static constexpr int STATUS_WAIT_DW = 0x105;
 
@@ -308,43 +308,45 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
     p.ldy = ldy;
     const int cv = C >> 3;
     out->tile_kernel = R == S && (S == 3 || S == 5 || S == 7) && dh == 1 && dw == 1 && sh == sw && (sw == 1 || sw == 2);
-    // Candidates: channel blocks from the widest acceptable one down, cell grids px x py with px a power of two. A
-    // clearly better product of (useful lanes) x (useful cells: tiles overhang the map) wins; among candidates within a
-    // tenth of each other the patch with the least staged bytes per output pixel (least border) is kept.
+    // Candidates: channel blocks from the widest acceptable one down, cell grids px x py with px a power of two. Among
+    // the candidates whose product of (useful lanes) x (useful cells: tiles overhang the map) is within 15 % of the best,
+    // the one with the least staged bytes per output pixel (least border) is taken. Measured on B200: small CTAs win
+    // over taller tiles with several output rows per thread (more CTAs per SM overlap one CTA's copy with the others'
+    // arithmetic), so a thread keeps to one output row.
     const int unit = out->tile_kernel ? dw_tw(S) : 1;
-    double best_score = -1.0, best_cost = 0.0;
-    bool found = false;
-    for (int cbv = pick_cbv(cv); cbv >= 1; cbv >>= 1) {
+    struct Cand { int cbv, px, py, tile_w, tile_h, tiles_x, tiles_y, vblocks; double score, cost; size_t bytes; };
+    Cand cands[40];
+    int nc = 0;
+    double best_score = 0.0;
+    for (int cbv = pick_cbv(cv); cbv >= 1 && nc < 32; cbv >>= 1) {
         const int cells = DW_THREADS / cbv;
         const int vblocks = (cv + cbv - 1) / cbv;
         const double lane_eff = static_cast<double>(cv) / (vblocks * cbv);
-        for (int px = 1; px <= cells; px <<= 1) {
+        for (int px = 1; px <= cells && nc < 40; px <<= 1) {
             const int py = cells / px;
-            for (int rpt = 1; rpt <= (out->tile_kernel ? 8 : 1); ++rpt) {
-                const int rows = py * rpt;
-                const int tile_w = (px * unit - 1) * sw + (S - 1) * dw + 1;
-                const int tile_h = (rows - 1) * sh + (R - 1) * dh + 1;
-                const size_t bytes = static_cast<size_t>(tile_h) * tile_w * cbv * 16;
-                if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 > static_cast<size_t>(DW_SMEM_LIMIT)) break;
-                const int tiles_x = (p.Q + px * unit - 1) / (px * unit), tiles_y = (p.P + rows - 1) / rows;
-                // enough CTAs to fill the machine a few times over, or the layer is too small to care
-                if (rpt > 1 && static_cast<long long>(tiles_x) * tiles_y * vblocks * N < 4ll * 148 * 4) break;
-                const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * rows * tiles_x * px * unit);
-                const double score = lane_eff * tile_eff;
-                const double cost = static_cast<double>(tile_h) * tile_w / (rows * px * unit);
-                if (score > best_score * 1.10 || (score > best_score * 0.90 && cost < best_cost)) {
-                    best_score = score > best_score ? score : best_score;
-                    best_cost = cost;
-                    found = true;
-                    p.cbv = cbv; p.px = px; p.py = py; p.rpt = rpt; p.tile_w = tile_w; p.tile_h = tile_h;
-                    p.tiles_x = tiles_x; p.tiles_y = tiles_y; p.vblocks = vblocks;
-                    out->smem = 128 + bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
-                }
-            }
+            const int tile_w = (px * unit - 1) * sw + (S - 1) * dw + 1;
+            const int tile_h = (py - 1) * sh + (R - 1) * dh + 1;
+            const size_t bytes = static_cast<size_t>(tile_h) * tile_w * cbv * 16;
+            if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 > static_cast<size_t>(DW_SMEM_LIMIT)) continue;
+            const int tiles_x = (p.Q + px * unit - 1) / (px * unit), tiles_y = (p.P + py - 1) / py;
+            const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * py * tiles_x * px * unit);
+            Cand c = {cbv, px, py, tile_w, tile_h, tiles_x, tiles_y, vblocks, lane_eff * tile_eff,
+                      static_cast<double>(tile_h) * tile_w / (py * px * unit), bytes};
+            cands[nc++] = c;
+            if (c.score > best_score) best_score = c.score;
         }
-        if (found && best_score > 0.97) break;       // narrower channel blocks only when the wide ones waste lanes
+        if (best_score > 0.97) break;       // narrower channel blocks only when the wide ones waste lanes
     }
-    return found;
+    int pick = -1;
+    for (int i = 0; i < nc; ++i)
+        if (cands[i].score >= 0.85 * best_score && (pick < 0 || cands[i].cost < cands[pick].cost)) pick = i;
+    if (pick < 0) return false;
+    const Cand& c = cands[pick];
+    p.cbv = c.cbv; p.px = c.px; p.py = c.py; p.rpt = 1; p.tile_w = c.tile_w; p.tile_h = c.tile_h;
+    p.tiles_x = c.tiles_x; p.tiles_y = c.tiles_y; p.vblocks = c.vblocks;
+    out->smem = 128 + c.bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
+    (void)N;
+    return true;
 }
 
 }  // namespace fvm

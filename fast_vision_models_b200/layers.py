@@ -15,6 +15,7 @@ from . import fold, ops
 
 AUTOTUNE = os.environ.get("FVM_B200_AUTOTUNE", "1") != "0"
 PAIR_STEMS = os.environ.get("FVM_B200_PAIR_STEMS", "1") != "0"   # run RGB stems over column pairs (16-channel taps)   # kill switch, in the style of the reference's CLF_* variables
+GATE_IN_WEIGHTS = os.environ.get("FVM_B200_GATE_IN_WEIGHTS", "1") != "0"   # squeeze-excite scale folded into the project conv's weights
 FUSED_SQUEEZE = os.environ.get("FVM_B200_FUSED_SQUEEZE", "1") != "0"   # squeeze sums from the depthwise conv's epilogue
 SPLIT_STEMS = os.environ.get("FVM_B200_SPLIT_STEMS", "1") != "0"   # stride-2 RGB stems on column-parity planes
 
@@ -338,11 +339,13 @@ class SqueezeExcite(nn.Module):
         """`partial`: the per-tile sums the producing depthwise conv emitted (`DepthwiseConv.forward(pool=True)`); the
         squeeze then costs no pass over x (the reference's fused form: gconv2_pool + sums_to_mean_k, r3.cu:181-203,
         283-299). Without it the squeeze is a global average pool of x."""
+        return ops.se_scale(x, self.gate(x, partial))
+
+    def gate(self, x: torch.Tensor, partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The pre-sigmoid gate s [N, C, 1, 1] of x."""
         if partial is not None and FUSED_SQUEEZE:
-            s = ops.se_gate_pooled(partial, x.shape[2] * x.shape[3], self.w1, self.b1, self.w2, self.b2, self.act)
-        else:
-            s = ops.se_gate(ops.global_avgpool(x), self.w1, self.b1, self.w2, self.b2, self.act)
-        return ops.se_scale(x, s)
+            return ops.se_gate_pooled(partial, x.shape[2] * x.shape[3], self.w1, self.b1, self.w2, self.b2, self.act)
+        return ops.se_gate(ops.global_avgpool(x), self.w1, self.b1, self.w2, self.b2, self.act)
 
 
 class LayerNormCL(nn.Module):

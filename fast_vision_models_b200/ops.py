@@ -401,6 +401,48 @@ def se_gate_pooled(partial, pixels: int, w1, b1, w2, b2, act: int = ACT_SILU) ->
     return s.view(N, C, 1, 1)
 
 
+def gate_weights(w, s) -> torch.Tensor:
+    """Folds a squeeze-excite gate into the 1x1 weights of the conv that follows, per image:
+    out[n, k, c] = half(w[k, c] * half(sigmoid(s[n, c]))); w [K, C(,1,1)] fp16, s [N, C(,1,1)] fp16 (pre-sigmoid)."""
+    init(w.device)
+    _require_cuda_half(w, "w")
+    _require_cuda_half(s, "s")
+    K = w.shape[0]
+    w2 = w.reshape(K, -1).contiguous()
+    C = w2.shape[1]
+    N = s.shape[0]
+    s2 = s.reshape(N, -1).contiguous()
+    if s2.shape[1] != C:
+        raise FvmError("gate_weights: the gate has another channel count than the weights")
+    out = torch.empty((N, K, C), dtype=torch.float16, device=w.device)
+    _check(lib().fvm_gate_weights_f16(w2.data_ptr(), s2.data_ptr(), out.data_ptr(), N, K, C, _stream()), "gate_weights_f16")
+    return out
+
+
+def conv1x1_wbatch(x, w_n, bias=None, res=None, act: int = 0) -> torch.Tensor:
+    """1x1 stride-1 convolution with per-image weights w_n [N, K, C] (from `gate_weights`): together they are
+    se_scale + project conv without the pass that writes and re-reads the scaled tensor."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    _require_cuda_half(w_n, "w_n")
+    if w_n.dim() != 3 or w_n.shape[0] != N or w_n.shape[2] != C:
+        raise FvmError(f"conv1x1_wbatch: w_n must be [N, K, C] = [{N}, K, {C}], got {tuple(w_n.shape)}")
+    w_n = w_n.contiguous()
+    K = w_n.shape[1]
+    y = empty_nhwc(N, K, H, W, x.device)
+    ldr = 0
+    if res is not None:
+        res, Nr, Kr, Hr, Wr, ldr = nhwc_view(res, "res")
+        if (Nr, Kr, Hr, Wr) != (N, K, H, W):
+            raise FvmError("conv1x1_wbatch: residual shape does not match the output")
+    if bias is not None:
+        _require_cuda_half(bias, "bias")
+        bias = bias.contiguous()
+    _check(lib().fvm_conv1x1_wbatch_f16(x.data_ptr(), w_n.data_ptr(), _ptr(bias), _ptr(res), y.data_ptr(), N, H, W, C, K,
+                                        ldx, K, ldr, int(act), _stream()), "conv1x1_wbatch_f16")
+    return y
+
+
 def se_scale(x, s) -> torch.Tensor:
     """clfr3::se_scale(x, s) (classification/fast/csrc/r3.cu:319-329): y = x * sigmoid(s)."""
     init(x.device)

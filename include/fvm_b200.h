@@ -141,6 +141,17 @@ int fvm_se_gate_f16(const void* g, const void* w1, const void* b1, const void* w
 int fvm_se_gate_pooled_f16(const float* partial, int slots, const void* w1, const void* b1, const void* w2,
                            const void* b2, void* s, int N, int C, int Cs, int act, float mean_scale, void* stream);
 
+/* The squeeze-excite scale without its pass over the tensor -- no counterpart in the reference, which always runs
+ * clfr3::se_scale (r3.cu:302-329) and then the project conv. fvm_gate_weights_f16 folds the rounded gate into the 1x1
+ * weights of the conv that follows, per image: out[n][k][c] = half(w[k][c] * half(sigmoid(s[n][c]))), w fp16 [K][C],
+ * s fp16 [N][C] (pre-sigmoid), out fp16 [N][K][C]. fvm_conv1x1_wbatch_f16 is the 1x1 stride-1 convolution with such
+ * per-image weights: y[n,p,k] = act(sum_c x[n,p,c] * w_n[n][k][c] + bias[k] + res[n,p,k]); an output tile never
+ * straddles two images. Same products as scale-then-convolve, the one fp16 rounding of each product's gate factor
+ * falls on the weight instead of the activation. */
+int fvm_gate_weights_f16(const void* w, const void* s, void* out, int N, int K, int C, void* stream);
+int fvm_conv1x1_wbatch_f16(const void* x, const void* w_n, const void* bias, const void* res, void* y, int N, int H, int W,
+                           int C, int K, long long ldx, long long ldy, long long ldr, int act, void* stream);
+
 /* y = x * sigmoid(s[n,c]) -- replaces clfr3::se_scale (r3.cu:302-329): sigmoid in fp32, rounded to fp16, fp16 multiply. */
 int fvm_se_scale_f16(const void* x, const void* s, void* y, int N, int HW, int C, void* stream);
 

@@ -478,6 +478,29 @@ def test_se_gate_and_scale_match_oracle(N, C, Cs, act):
     close(ops.se_scale(cl(x), ref_s.to(DEV)), R.se_scale_ref(x, ref_s))
 
 
+@pytest.mark.parametrize("case", [(3, 144, 19, 19, 24, False), (4, 672, 24, 24, 112, True), (2, 48, 7, 5, 40, True),
+                                  (64, 960, 12, 12, 272, False), (5, 96, 1, 1, 32, False)])
+def test_gate_folded_into_project_weights_matches_scale_then_conv(case):
+    # squeeze-excite scale + project conv without the scaled tensor: the rounded gate multiplies the 1x1 weights (per
+    # image) instead of the activations; same products, the gate's fp16 rounding falls on the other operand
+    N, C, H, W, K, res = case
+    x, s = gen((N, C, H, W), 31), gen((N, C, 1, 1), 32)
+    w, b = gen((K, C, 1, 1), 33, 0.05), gen((K,), 34, 0.1)
+    r = gen((N, K, H, W), 35) if res else None
+    ref = R.conv_fused_ref(R.se_scale_ref(x, s), w, b, r, act=0)
+    w_n = ops.gate_weights(cl(w), s.to(DEV))
+    assert w_n.shape == (N, K, C)
+    want_w = (w.float().view(1, K, C) * torch.sigmoid(s.float()).half().float().view(N, 1, C)).half()
+    assert rel_l2(w_n, want_w) < 1e-3
+    y = ops.conv1x1_wbatch(cl(x), w_n, b.to(DEV), None if r is None else cl(r), 0)
+    assert ops.last_status() == 0
+    close(y, ref, 2e-3)
+    # and it is exactly the plain convolution of each image with that image's weights
+    for n in (0, N - 1):
+        one = ops.conv_fused(cl(x[n:n + 1]), cl(w_n[n].view(K, C, 1, 1)), b.to(DEV), None if r is None else cl(r[n:n + 1]))
+        assert torch.equal(one, y[n:n + 1])
+
+
 @pytest.mark.parametrize("shape", [(2, 96, 14, 14), (2, 192, 9, 7), (1, 384, 5, 5), (3, 768, 7, 7), (2, 8, 3, 3),
                                    (2, 1536, 2, 2), (5, 768, 1, 1)])
 def test_layernorm_matches_oracle(shape):
