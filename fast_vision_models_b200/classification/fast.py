@@ -130,8 +130,11 @@ class MBConvBlock(nn.Module):
         y, partial = self.dw(y, pool=True)      # the squeeze sums come out of the depthwise conv's epilogue
         res = x if self.use_res else None      # eval-mode stochastic depth is the identity: the add rides in the epilogue
         pj = self.project
-        if GATE_IN_WEIGHTS and pj.scale is None and pj.w.shape[2] == 1 and pj.w.shape[3] == 1 and pj.stride == (1, 1):
-            # the gate multiplies the project conv's weights (per image) instead of the activations: no pass over y
+        if (GATE_IN_WEIGHTS and pj.scale is None and pj.w.shape[2] == 1 and pj.w.shape[3] == 1 and pj.stride == (1, 1)
+                and 2 * pj.w.shape[0] <= y.shape[2] * y.shape[3]):
+            # the gate multiplies the project conv's weights (per image) instead of the activations: no pass over y.
+            # Only where an image has at least twice as many pixels as the conv has output channels: the per-image
+            # weights [K][C] are then less than half the size of the tensor [pixels][C] they save a pass over.
             w_n = ops.gate_weights(pj.w, self.se.gate(y, partial))
             return ops.conv1x1_wbatch(y, w_n, pj.b, res, pj.act)
         return pj(self.se(y, partial), res=res)

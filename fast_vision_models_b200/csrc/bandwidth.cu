@@ -224,17 +224,30 @@ static int gap_splits(int N, int HW, int C, int sms) {
 __global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __restrict__ w1,
                                const __half* __restrict__ b1, const __half* __restrict__ w2,
                                const __half* __restrict__ b2, __half* __restrict__ s_out, int C, int Cs, int act,
-                               float mean_scale, int slots) {
+                               float mean_scale, int slots, int sgroups) {
     extern __shared__ float sm[];
     float* g = sm;          // [C]
     float* h = sm + C;      // [Cs]
     const long long n = blockIdx.x;
     if (mean_scale != 0.f) {
-        // fused squeeze: fp32 partial sums [slots][C] of this image, added in slot order, times 1 / pixels
+        // fused squeeze: fp32 partial sums [slots][C] of this image times 1 / pixels. The slots are cut into `sgroups`
+        // contiguous runs that are summed in parallel (every thread busy, several loads in flight), then the runs are
+        // added in order: a fixed summation order, whatever the scheduling.
         const float* gs = static_cast<const float*>(g_in) + n * slots * C;
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float* part = sm + C + Cs;                 // [sgroups][C]
+        const int run = (slots + sgroups - 1) / sgroups;
+        for (int idx = threadIdx.x; idx < C * sgroups; idx += blockDim.x) {
+            const int sg = idx / C, c = idx - sg * C;
+            const int k1 = min(slots, (sg + 1) * run);
             float sum = 0.f;
-            for (int k = 0; k < slots; ++k) sum += gs[static_cast<long long>(k) * C + c];
+#pragma unroll 8
+            for (int k = sg * run; k < k1; ++k) sum += gs[static_cast<long long>(k) * C + c];
+            part[idx] = sum;
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float sum = part[c];
+            for (int sg = 1; sg < sgroups; ++sg) sum += part[sg * C + c];
             g[c] = __half2float(__float2half_rn(sum * mean_scale));
         }
     } else {
@@ -702,7 +715,12 @@ static int se_gate_launch(const void* g, int slots, const void* w1, const void* 
     if (!g || !w1 || !w2 || !s || N <= 0 || C <= 0 || Cs <= 0 || (C & 7) || (Cs & 7) || act < 0 || act > 6 || slots < 1 ||
         !aligned16(w1) || !aligned16(w2))
         return FVM_ERR_ARG;
-    const size_t smem = static_cast<size_t>(C + Cs) * sizeof(float);
+    // runs of slots summed in parallel: enough to keep all threads busy, within the static shared-memory limit
+    int sgroups = mean_scale != 0.f ? slots / 16 : 0;
+    if (mean_scale != 0.f && sgroups < 1) sgroups = 1;
+    if (sgroups > 8) sgroups = 8;
+    while (sgroups > 1 && static_cast<size_t>(C) * (1 + sgroups) + Cs > 12 * 1024 - 64) --sgroups;
+    const size_t smem = (static_cast<size_t>(C) * (1 + sgroups) + Cs) * sizeof(float);
     if (smem > 48 * 1024) return FVM_ERR_ARG;
     DeviceState* st = device_state();
     const int sms = st ? st->sms : 148;
@@ -710,7 +728,7 @@ static int se_gate_launch(const void* g, int slots, const void* w1, const void* 
     while (split < 4 && N * split * 2 <= 2 * sms && C / (split * 2) >= 256) split *= 2;
     se_gate_kernel<<<dim3(N, split), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         g, static_cast<const __half*>(w1), static_cast<const __half*>(b1), static_cast<const __half*>(w2),
-        static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale, slots);
+        static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale, slots, sgroups);
     FVM_LAUNCH_CHECK();
 }
 

@@ -43,7 +43,6 @@ struct DwParams {
     int sh, sw, ph, pw, dh, dw;
     int cbv;                 // channel vectors (8 channels each) per block: 8, 4, 2 or 1
     int px, py;              // thread grid over the tile: px x py "cells" per channel vector (px * py * cbv = 128)
-    int rpt;                 // tile kernel: consecutive output rows per thread (a taller tile has less border per output)
     int tiles_x, tiles_y, vblocks;
     int tile_h, tile_w;      // staged input patch in pixels
     int act;
@@ -60,9 +59,10 @@ __device__ __forceinline__ void dw_decode_block(const DwParams& p, int& tx, int&
 }
 
 // Brings the input patch of this CTA's tile into shared memory: (channels vb*cbv*8 .., columns w0 .., rows h0 .., image
-// n); coordinates outside the tensor are filled with zeros by the copy. Returns false if the bounded wait ran out.
-__device__ __forceinline__ bool dw_stage(const CUtensorMap* tmap, const DwParams& p, uint32_t smem0, uint32_t bar, int vb,
-                                         int w0, int h0, int n, volatile int* abort_flag) {
+// n); coordinates outside the tensor are filled with zeros by the copy. dw_stage_issue starts the copy (one thread),
+// dw_stage_wait joins the CTA and waits for it; returns false if the bounded wait ran out.
+__device__ __forceinline__ void dw_stage_issue(const CUtensorMap* tmap, const DwParams& p, uint32_t smem0, uint32_t bar,
+                                               int vb, int w0, int h0, int n, volatile int* abort_flag) {
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar, 1);
@@ -70,6 +70,8 @@ __device__ __forceinline__ bool dw_stage(const CUtensorMap* tmap, const DwParams
         mbar_expect_tx(bar, static_cast<uint32_t>(p.tile_h * p.tile_w * p.cbv) * 16u);
         tma_load_4d(smem0, tmap, bar, vb * p.cbv * 8, w0, h0, n);
     }
+}
+__device__ __forceinline__ bool dw_stage_wait(const DwParams& p, uint32_t bar, volatile int* abort_flag) {
     __syncthreads();
     if (!mbar_wait<32>(bar, 0u, abort_flag)) {
         if (threadIdx.x == 0) atomicExch(p.status, STATUS_WAIT_DW);
@@ -111,48 +113,56 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
     int tx, ty, vb;
     dw_decode_block(p, tx, ty, vb);
     const long long n = blockIdx.y;
-    const int TWB = p.px * TW, TH = p.py * p.rpt;
+    const int TWB = p.px * TW, TH = p.py;
     const int p0 = ty * TH, q0 = tx * TWB;
-    if (!dw_stage(&tmap_x, p, smem0, bar, vb, q0 * SW - p.pw, p0 * p.sh - p.ph, static_cast<int>(n), abort_flag)) return;
+    dw_stage_issue(&tmap_x, p, smem0, bar, vb, q0 * SW - p.pw, p0 * p.sh - p.ph, static_cast<int>(n), abort_flag);
+    // the block's S x S x (cbv * 8) weights: [tap][channel vector], copied while the input patch is in flight
+    const uint32_t w_s = smem_u32(pool_s) + DW_THREADS * 8 * 4;
+    {
+        uint4* w_dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pool_s) + DW_THREADS * 8 * 4);
+        const int cvb = p.C >> 3;
+        for (int i = threadIdx.x; i < S * S * p.cbv; i += DW_THREADS) {
+            const int tap = i / p.cbv, wv = vb * p.cbv + i % p.cbv;
+            w_dst[i] = wv < cvb ? __ldg(reinterpret_cast<const uint4*>(w + static_cast<long long>(tap) * p.C + wv * 8))
+                                : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    if (!dw_stage_wait(p, bar, abort_flag)) return;
 
     const int vv = threadIdx.x % p.cbv;
     const int cell = threadIdx.x / p.cbv;
     const int sx = cell % p.px, sy = cell / p.px;
     const int v = vb * p.cbv + vv;
-    const int qs = q0 + sx * TW;
-    const bool active = v < (p.C >> 3) && qs < p.Q;
+    const int pr = p0 + sy, qs = q0 + sx * TW;
+    const bool active = v < (p.C >> 3) && pr < p.P && qs < p.Q;
     float psum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int rr = 0; active && rr < p.rpt; ++rr) {
-        const int ly = sy * p.rpt + rr;          // output row inside the tile
-        const int pr = p0 + ly;
-        if (pr >= p.P) break;
-        unsigned long long acc[TW][4];      // fp32 accumulators as packed pairs
+    if (active) {
+        float acc[TW][8];                   // fp32 accumulators
         {
-            unsigned long long b2[4] = {0ull, 0ull, 0ull, 0ull};
+            float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (bias) {
                 const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + v * 8));
-                b2[0] = h2_to_f2(bv.x); b2[1] = h2_to_f2(bv.y); b2[2] = h2_to_f2(bv.z); b2[3] = h2_to_f2(bv.w);
+                f32_add_h2(b8[0], b8[1], bv.x); f32_add_h2(b8[2], b8[3], bv.y);
+                f32_add_h2(b8[4], b8[5], bv.z); f32_add_h2(b8[6], b8[7], bv.w);
             }
 #pragma unroll
             for (int j = 0; j < TW; ++j)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[j][k] = b2[k];
+                for (int k = 0; k < 8; ++k) acc[j][k] = b8[k];
         }
         constexpr int L = (TW - 1) * SW + S;      // staged columns one kernel row of this thread's strip reads
         const uint32_t pix = static_cast<uint32_t>(p.cbv) * 16u;
 #pragma unroll(S == 3 ? 3 : 1)
         for (int r = 0; r < S; ++r) {          // square filter: R == S; short filters unrolled (next row's loads issue early)
-            const __half* wrow = w + static_cast<long long>(r) * S * p.C + v * 8;
-            uint4 wr[S];
+            uint4 wr[S];                       // this kernel row of the block's weights, from shared memory
 #pragma unroll
-            for (int s2 = 0; s2 < S; ++s2)
-                wr[s2] = __ldg(reinterpret_cast<const uint4*>(wrow + static_cast<long long>(s2) * p.C));
+            for (int s2 = 0; s2 < S; ++s2) wr[s2] = lds128(w_s + static_cast<uint32_t>((r * S + s2) * p.cbv + vv) * 16u);
             __half2 racc[TW][4];
 #pragma unroll
             for (int j = 0; j < TW; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) racc[j][k] = __float2half2_rn(0.f);
-            const uint32_t row_addr = smem0 + static_cast<uint32_t>((ly * p.sh + r) * p.tile_w + sx * TW * SW) * pix +
+            const uint32_t row_addr = smem0 + static_cast<uint32_t>((sy * p.sh + r) * p.tile_w + sx * TW * SW) * pix +
                                       static_cast<uint32_t>(vv) * 16u;
 #pragma unroll
             for (int l = 0; l < L; ++l) {
@@ -172,7 +182,7 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
             for (int j = 0; j < TW; ++j)
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    acc[j][k] = f2_add(acc[j][k], h2_to_f2(*reinterpret_cast<const uint32_t*>(&racc[j][k])));
+                    f32_add_h2(acc[j][2 * k], acc[j][2 * k + 1], *reinterpret_cast<const uint32_t*>(&racc[j][k]));
         }
 #pragma unroll
         for (int j = 0; j < TW; ++j) {
@@ -183,12 +193,11 @@ dw_tile_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restr
                 for (int k = 0; k < 4; ++k) {
                     // the sum is rounded to fp16 first; relu acts on the fp16 pair, other activations are evaluated
                     // in fp32 on the rounded value and rounded again (reference: r3.cu:404-413)
-                    const uint32_t hv = f2_to_h2(acc[j][k]);
-                    o[k] = *reinterpret_cast<const __half2*>(&hv);
+                    o[k] = __floats2half2_rn(acc[j][2 * k], acc[j][2 * k + 1]);
                     if (ACT == 1) {
                         o[k] = __hmax2(o[k], __float2half2_rn(0.f));
-                    } else if (ACT == 3) {      // SiLU on the pair: packed multiplies, ex2 / rcp per element
-                        const uint32_t sv = f2_to_h2(f2_silu(h2_to_f2(hv)));
+                    } else if (ACT == 3) {      // SiLU on the fp16 pair (see h2_silu)
+                        const uint32_t sv = h2_silu(*reinterpret_cast<const uint32_t*>(&o[k]));
                         o[k] = *reinterpret_cast<const __half2*>(&sv);
                     } else if (ACT != 0) {
                         const float2 f = __half22float2(o[k]);
@@ -223,7 +232,8 @@ dw_any_kernel(const __grid_constant__ CUtensorMap tmap_x, const __half* __restri
     dw_decode_block(p, tx, ty, vb);
     const long long n = blockIdx.y;
     const int p0 = ty * p.py, q0 = tx * p.px;
-    if (!dw_stage(&tmap_x, p, smem0, bar, vb, q0 * p.sw - p.pw, p0 * p.sh - p.ph, static_cast<int>(n), abort_flag)) return;
+    dw_stage_issue(&tmap_x, p, smem0, bar, vb, q0 * p.sw - p.pw, p0 * p.sh - p.ph, static_cast<int>(n), abort_flag);
+    if (!dw_stage_wait(p, bar, abort_flag)) return;
 
     const int vv = threadIdx.x % p.cbv;
     const int cell = threadIdx.x / p.cbv;
@@ -327,7 +337,7 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
             const int tile_w = (px * unit - 1) * sw + (S - 1) * dw + 1;
             const int tile_h = (py - 1) * sh + (R - 1) * dh + 1;
             const size_t bytes = static_cast<size_t>(tile_h) * tile_w * cbv * 16;
-            if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 > static_cast<size_t>(DW_SMEM_LIMIT)) continue;
+            if (tile_w > 256 || tile_h > 256 || bytes + 128 + 16 + 4096 + 6272 > static_cast<size_t>(DW_SMEM_LIMIT)) continue;
             const int tiles_x = (p.Q + px * unit - 1) / (px * unit), tiles_y = (p.P + py - 1) / py;
             const double tile_eff = static_cast<double>(p.P) * p.Q / (static_cast<double>(tiles_y) * py * tiles_x * px * unit);
             Cand c = {cbv, px, py, tile_w, tile_h, tiles_x, tiles_y, vblocks, lane_eff * tile_eff,
@@ -342,9 +352,9 @@ static bool dw_plan(int N, int H, int W, int C, int R, int S, int ph, int pw, in
         if (cands[i].score >= 0.85 * best_score && (pick < 0 || cands[i].cost < cands[pick].cost)) pick = i;
     if (pick < 0) return false;
     const Cand& c = cands[pick];
-    p.cbv = c.cbv; p.px = c.px; p.py = c.py; p.rpt = 1; p.tile_w = c.tile_w; p.tile_h = c.tile_h;
+    p.cbv = c.cbv; p.px = c.px; p.py = c.py; p.tile_w = c.tile_w; p.tile_h = c.tile_h;
     p.tiles_x = c.tiles_x; p.tiles_y = c.tiles_y; p.vblocks = c.vblocks;
-    out->smem = 128 + c.bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float);
+    out->smem = 128 + c.bytes + 16 + static_cast<size_t>(DW_THREADS) * 8 * sizeof(float) + 6272;    // + up to 49 taps x 8 vectors of weights
     (void)N;
     return true;
 }

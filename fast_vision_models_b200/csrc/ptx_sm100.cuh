@@ -243,6 +243,29 @@ __device__ __forceinline__ unsigned long long f2_silu(unsigned long long x) {
     f2_unpack(d, lo, hi);
     return f2_mul(x, f2_pack(__float_as_uint(rcp_approx(lo)), __float_as_uint(rcp_approx(hi))));
 }
+// (a0, a1) += the two halves of an fp16x2 word, in fp32: the mixed-precision add of sm_100 converts and adds in one
+// instruction per element (no separate fp16 -> fp32 conversion).
+__device__ __forceinline__ void f32_add_h2(float& a0, float& a1, uint32_t h2) {
+    asm("{\n\t"
+        ".reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "add.rn.f32.f16 %0, lo, %0;\n\t"
+        "add.rn.f32.f16 %1, hi, %1;\n\t"
+        "}\n"
+        : "+f"(a0), "+f"(a1)
+        : "r"(h2));
+}
+// SiLU of an fp16 pair entirely in fp16x2: x * sigmoid(x) = h + h * tanh(h) with h = x / 2 (one multiply, one
+// tanh.approx.f16x2, one fused multiply-add per PAIR; the fp32 form costs about twelve instructions per pair). The
+// approximate tanh is good to 2^-11 absolute, so the result is within about one fp16 ulp of 1.0 * |x| / 2 of the fp32
+// value: inside the fp16 rounding of the activations it produces, and far inside the parity tolerance.
+__device__ __forceinline__ uint32_t h2_silu(uint32_t x) {
+    uint32_t h, t, y;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(h) : "r"(x), "r"(0x38003800u));      // * 0.5
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(h));
+    asm("fma.rn.f16x2 %0, %1, %2, %1;" : "=r"(y) : "r"(h), "r"(t));
+    return y;
+}
 // GELU (erf form) of an fp32 pair. erf by Abramowitz & Stegun 7.1.26 (absolute error below 1.5e-7, far inside the
 // fp16 result): with z = |x| / sqrt 2, t = 1 / (1 + p z), r = (a1 t + .. + a5 t^5) exp(-z^2) = 1 - erf(z),
 // gelu(x) = max(x, 0) - |x| r / 2  (for x >= 0: x (2 - r) / 2; for x < 0: x r / 2). The polynomial runs on packed
