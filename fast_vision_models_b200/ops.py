@@ -531,6 +531,51 @@ def stem_conv_s2(xs: torch.Tensor, w: torch.Tensor, bias, padding, act: int, out
     return out
 
 
+_STEM_WEIGHTS = {}
+
+
+def _stem_weights_from_rsck(w_t: torch.Tensor) -> torch.Tensor:
+    """The reference's raw-input stem weights w_t [R, S, C, K] (C <= 4; classification/fast/fused.py:73) as this
+    library's KRSC weights with the input channels zero-padded to 8. Re-packed once per weight tensor."""
+    key = (w_t.data_ptr(), tuple(w_t.shape), w_t.device.index, w_t._version)
+    w = _STEM_WEIGHTS.get(key)
+    if w is None:
+        R, S, C, K = w_t.shape
+        if C > 8:
+            raise FvmError("stem: at most 8 input channels")
+        w = torch.zeros((K, 8, R, S), dtype=torch.float16, device=w_t.device)
+        w[:, :C] = w_t.permute(3, 2, 0, 1)
+        w = w.contiguous(memory_format=torch.channels_last)
+        if len(_STEM_WEIGHTS) > 64:
+            _STEM_WEIGHTS.clear()
+        _STEM_WEIGHTS[key] = w
+    return w
+
+
+def stem_direct(x, w_t, bias=None, stride=(2, 2), pad=(1, 1), act: int = 0) -> torch.Tensor:
+    """clfmb::stem_direct(x, w_t, bias?, stride, pad, act) (classification/fast/csrc/mbconv.cu:1212-1241): the stem
+    convolution straight from the raw fp32 / fp16 NCHW image batch (C <= 4), w_t [R, S, C, K] fp16. Stride-2 stems on
+    even-width images run as `input_nhwc8_split` + `stem_conv_s2`, everything else as `input_nhwc8` + `conv_fused`."""
+    _require_cuda_half(w_t, "w_t")
+    if w_t.dim() != 4 or w_t.shape[2] != x.shape[1] or not w_t.is_contiguous():
+        raise FvmError("stem_direct: w_t must be a contiguous [R, S, C, K] tensor matching the image channels")
+    w = _stem_weights_from_rsck(w_t)
+    K, _, R, S = w.shape
+    sh, sw = _pair(stride)
+    ph, pw_ = _pair(pad)
+    if (sh, sw) == (2, 2) and x.shape[3] % 2 == 0 and R <= 8 and S <= 8 and K <= 256 and K % 8 == 0 and ph < R and pw_ < S \
+            and (R + R % 2) * S * ((K + 31) // 32 * 32) * 16 <= 96 * 1024:
+        return stem_conv_s2(input_nhwc8_split(x), w, bias, (ph, pw_), act)
+    return conv_fused(input_nhwc8(x), w, bias, None, (ph, pw_), (sh, sw), act)
+
+
+def stem_pool(x, w_t, bias, stride, pad, act: int, pk: int, ps: int, pp: int, ceil: bool = False) -> torch.Tensor:
+    """clfr3::stem_pool(x, w_t, bias?, stride, pad, act, pk, ps, pp, ceil) (classification/fast/csrc/r3.cu:584-630): stem
+    convolution from the raw image followed by a pk x pk max pool (stride ps, padding pp). The reference runs the pair
+    as one kernel; here it is the stem convolution and the pooling kernel back to back (two launches)."""
+    return maxpool(stem_direct(x, w_t, bias, stride, pad, act), (pk, pk), (ps, ps), (pp, pp), ceil)
+
+
 def bias_act_(y, bias=None, res=None, relu: bool = False) -> torch.Tensor:
     """segx::bias_act_(y, bias?, res?, relu) in place (segmentation/fast/csrc/segx_ops.cu:28-42)."""
     init(y.device)

@@ -1,8 +1,9 @@
 """`torch.ops` registration of the hot-path operators under the reference's namespaces and schemas.
 
-The reference's fx passes insert `torch.ops.clf.*`, `torch.ops.clfr3.*` and `torch.ops.segx.*` calls whose schemas are
+The reference's fx passes insert `torch.ops.clf.*`, `torch.ops.clfr3.*`, `torch.ops.clfmb.*` and `torch.ops.segx.*` calls whose schemas are
 defined by the `TORCH_LIBRARY` blocks of its CUDA extensions (classification/fast/csrc/fused_conv.cu:622-631,
-classification/fast/csrc/r3.cu:796-808, segmentation/fast/csrc/segx_conv.cu:619-629, segx_ops.cu:294-322).
+classification/fast/csrc/r3.cu:796-808, mbconv.cu:1243-1257, segmentation/fast/csrc/segx_conv.cu:619-629,
+segx_ops.cu:294-322).
 `register()` defines the same schema strings with `torch.library` and binds their CUDA implementations to the C-ABI
 calls of libfvm_b200.so (through `ops.py`), plus Meta implementations (output shapes only) so that the ops trace under
 fake tensors. Only the CUDA key is bound, as in the reference: a CPU tensor reaches no kernel and raises.
@@ -40,6 +41,10 @@ SCHEMAS = {
         "conv_tc_into(Tensor x, Tensor w, Tensor? bias, int[] stride, int[] pad, int act, Tensor(a!) out) -> ()",
         "dwconv2(Tensor x, Tensor w_rsc, Tensor? bias, int[] stride, int[] padding, int act) -> Tensor",
         "se_scale(Tensor x, Tensor s) -> Tensor",
+        "stem_pool(Tensor x, Tensor w_t, Tensor? bias, int[] stride, int[] pad, int act, int pk, int ps, int pp, bool ceil) -> Tensor",
+    ],
+    "clfmb": [
+        "stem_direct(Tensor x, Tensor w_t, Tensor? bias, int[] stride, int[] pad, int act) -> Tensor",
     ],
     "segx": [
         "input_nhwc8(Tensor x) -> Tensor",
@@ -127,6 +132,15 @@ def _cuda_impls():
     def up_meta(x, H, W, sf_h, sf_w, align):
         return _empty_cl(x, (x.shape[0], x.shape[1], H, W))
 
+    def stem_meta(x, w_t, bias, stride, pad, act):
+        N, _, H, W = x.shape
+        R, S, _, K = w_t.shape
+        return _empty_cl(x, (N, K, (H + 2 * pad[0] - R) // stride[0] + 1, (W + 2 * pad[1] - S) // stride[1] + 1))
+
+    def stem_pool_meta(x, w_t, bias, stride, pad, act, pk, ps, pp, ceil):
+        y = stem_meta(x, w_t, bias, stride, pad, act)
+        return _empty_cl(x, (y.shape[0], y.shape[1], ops._pool_out(y.shape[2], pk, ps, pp, ceil), ops._pool_out(y.shape[3], pk, ps, pp, ceil)))
+
     def up_argmax(s, H, W, align):
         # the reference passes the scores as an NHWC-shaped tensor [B, h, w, C] (segx_ops.cu:172-175)
         return ops.up_argmax(s.permute(0, 3, 1, 2), H, W, align)
@@ -151,6 +165,8 @@ def _cuda_impls():
         "conv_tc": (lambda x, w, bias, stride, pad, act, cfg=-1: ops.conv_tc(x, w, bias, stride, pad, act, cfg), conv_tc_meta),
         "conv_tc_into": (lambda x, w, bias, stride, pad, act, out: ops.conv_tc_into(x, w, bias, stride, pad, act, out), nothing),
         "se_scale": (ops.se_scale, same_meta),
+        "stem_direct": (ops.stem_direct, stem_meta),
+        "stem_pool": (ops.stem_pool, stem_pool_meta),
         "bias_act_": (lambda y, bias, res, relu: ops.bias_act_(y, bias, res, relu), lambda y, bias, res, relu: y),
         "segx.dwconv": (ops.segx_dwconv, segx_dw_meta),
         "upsample_bilinear": (lambda x, H, W, sf_h, sf_w, align: ops.upsample_bilinear(x, H, W, sf_h, sf_w, align), up_meta),

@@ -79,6 +79,16 @@ def test_torch_ops_follow_the_reference_schemas_and_match_the_oracle():
     yb = cl(gen((2, 24, 6, 7), 13)).clone(memory_format=torch.channels_last)
     want_b = R.bias_act_ref(yb.cpu(), gen((24,), 14), None, True)
     close(torch.ops.segx.bias_act_(yb, gen((24,), 14).to(DEV), None, True), want_b)
+    # clfmb::stem_direct(x raw NCHW, w_t [R,S,C,K], bias?, stride, pad, act) and clfr3::stem_pool(..., pk, ps, pp, ceil)
+    img = torch.randn(2, 3, 38, 46, generator=torch.Generator().manual_seed(15))
+    wk = gen((48, 3, 3, 3), 16, 0.1)
+    w_t = wk.permute(2, 3, 1, 0).contiguous().to(DEV)
+    w8 = torch.zeros(48, 8, 3, 3, dtype=torch.float16)
+    w8[:, :3] = wk
+    want_stem = R.conv_fused_ref(R.input_nhwc8_ref(img), w8, gen((48,), 17, 0.1), None, (1, 1), (2, 2), 3)
+    close(torch.ops.clfmb.stem_direct(img.to(DEV), w_t, gen((48,), 17, 0.1).to(DEV), [2, 2], [1, 1], 3), want_stem)
+    got = torch.ops.clfr3.stem_pool(img.to(DEV), w_t, gen((48,), 17, 0.1).to(DEV), [2, 2], [1, 1], 3, 3, 2, 1, False)
+    close(got, R.maxpool_ref(want_stem, 3, 2, 1, False), 2e-3)
     assert ops.last_status() == 0
     with pytest.raises((NotImplementedError, RuntimeError)):       # only the CUDA key is bound, as in the reference
         torch.ops.clf.conv_fused(x, w, None, None, [1, 1], [1, 1], 0)

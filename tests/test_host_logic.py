@@ -97,7 +97,7 @@ def test_torch_ops_registration_defines_the_reference_schemas():
     from fast_vision_models_b200 import torch_ops
     done = torch_ops.register()
     assert torch_ops.register() is done                     # idempotent
-    assert set(done) == {"clf", "clfr3", "segx"}
+    assert set(done) == {"clf", "clfr3", "clfmb", "segx"}
     want = {
         "clf::conv_fused": "clf::conv_fused(Tensor x, Tensor w, Tensor? bias, Tensor? res, int[] padding, int[] stride, int act, int cfg=-1) -> Tensor",
         "clf::avgpool": "clf::avgpool(Tensor x, int[] k, int[] stride, int[] pad, bool count_include_pad=True) -> Tensor",
