@@ -4,6 +4,8 @@
     python -m fast_vision_models_b200.opbench conv --n 64 --hw 56 --c 64 --k 64 --r 3 --pad 1 --tile 67108864
     python -m fast_vision_models_b200.opbench stem --n 64 --hw 224 --k 64 --r 7 --pad 3
     python -m fast_vision_models_b200.opbench dwconv --n 64 --hw 95 --c 192 --r 3 --pad 1 --act 3
+    python -m fast_vision_models_b200.opbench layernorm --n 64 --hw 56 --c 96
+    python -m fast_vision_models_b200.opbench gap --n 64 --hw 7 --c 2048        (also: se_scale, maxpool, up_argmax, wbatch)
 
 Default: the op is captured 20 times into a CUDA graph over 4 rotating buffer sets (so that inputs do not stay in
 L2), the graph is replayed and timed with CUDA events; prints microseconds per launch and the algorithmic GB/s
@@ -23,7 +25,7 @@ def _cl(t):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["conv", "stem", "dwconv"])
+    ap.add_argument("op", choices=["conv", "stem", "dwconv", "layernorm", "gap", "se_scale", "maxpool", "up_argmax", "wbatch"])
     ap.add_argument("--n", type=int, default=64)
     ap.add_argument("--hw", type=int, nargs="+", default=[56], help="height [width]")
     ap.add_argument("--c", type=int, default=64)
@@ -72,7 +74,7 @@ def main():
 
         def launch(i):
             ops.stem_conv_s2(xs[i], w, b, (a.pad, a.pad), a.act, out=ys[i])
-    else:
+    elif a.op == "dwconv":
         P = (H + 2 * a.pad - a.dil * (R - 1) - 1) // a.stride + 1
         Q = (W + 2 * a.pad - a.dil * (R - 1) - 1) // a.stride + 1
         xs = [_cl(rnd(N, C, H, W)) for _ in range(nbuf)]
@@ -82,6 +84,47 @@ def main():
 
         def launch(i):
             ops.dwconv(xs[i], w, b, (a.stride, a.stride), (a.pad, a.pad), a.act, dilation=(a.dil, a.dil))
+    elif a.op == "wbatch":
+        # squeeze-excite gate folded into per-image 1x1 weights + the project conv on them
+        xs = [_cl(rnd(N, C, H, W)) for _ in range(nbuf)]
+        w, b, s_ = _cl(rnd(K, C, 1, 1, scale=0.05)), rnd(K, scale=0.1), rnd(N, C, 1, 1)
+        rs = [_cl(rnd(N, K, H, W)) if a.res else None for _ in range(nbuf)]
+        nbytes = 2 * (N * H * W * C + N * K * C + K + N * H * W * K * (2 if a.res else 1))
+        flops = 2 * N * H * W * K * C
+
+        def launch(i):
+            ops.conv1x1_wbatch(xs[i], ops.gate_weights(w, s_), b, rs[i], 0)
+    else:
+        xs = [_cl(rnd(N, C, H, W)) for _ in range(nbuf)]
+        flops = 0
+        if a.op == "layernorm":
+            g_, b_ = torch.ones(C, dtype=torch.float16, device=dev), torch.zeros(C, dtype=torch.float16, device=dev)
+            nbytes = 4 * N * H * W * C
+
+            def launch(i):
+                ops.layernorm_cl(xs[i], g_, b_, 1e-6)
+        elif a.op == "gap":
+            nbytes = 2 * (N * H * W * C + N * C)
+
+            def launch(i):
+                ops.global_avgpool(xs[i])
+        elif a.op == "se_scale":
+            s_ = rnd(N, C, 1, 1)
+            nbytes = 4 * N * H * W * C
+
+            def launch(i):
+                ops.se_scale(xs[i], s_)
+        elif a.op == "maxpool":
+            P, Q = (H + 2 - 3) // 2 + 1, (W + 2 - 3) // 2 + 1
+            nbytes = 2 * (N * H * W * C + N * P * Q * C)
+
+            def launch(i):
+                ops.maxpool(xs[i], 3, 2, 1)
+        else:       # up_argmax: C score channels (K of them are classes) at H x W -> 8x the size
+            nbytes = 2 * N * H * W * C + 4 * N * H * 8 * W * 8
+
+            def launch(i):
+                ops.up_argmax(xs[i], H * 8, W * 8, False, K)
 
     if a.plain > 0:
         for i in range(a.plain):
