@@ -417,7 +417,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 int wb_img = 0, wb_row0 = 0;      // per-image weights: m_tile = (image, 128-pixel tile of that image)
                 if (p.wb) {
                     wb_img = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_tpi));
-                    wb_row0 = (m_tile - wb_img * p.wb_tpi) * BM;
+                    wb_row0 = (m_tile - wb_img * p.wb_tpi) * BM * p.mt;
                 }
                 // halo mode: m_tile = (image, patch row, patch column)
                 int himg = 0, hy0 = 0, hx0 = 0;
@@ -443,7 +443,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             const uint32_t dst = epi_base + static_cast<uint32_t>(e) * epi_bytes +
                                                  static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES;
                             if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg);
-                            else if (p.wb) tma_load_3d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, wb_row0, wb_img);
+                            else if (p.wb) tma_load_3d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, wb_row0 + mt * BM, wb_img);
                             else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
                         }
                     if (++e == p.nepi) e = 0;
@@ -833,9 +833,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 if (p.wb) {       // per-image weights: (channel, pixel of the image, image), clipped at the image's last pixel
                     const int wb_img = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_tpi));
-                    for (int sub = 0; sub < nsub; ++sub)
-                        tma_store_3d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
-                                     n0 + sub * 64, (m_tile - wb_img * p.wb_tpi) * BM, wb_img);
+                    const int wb_row0 = (m_tile - wb_img * p.wb_tpi) * BM * p.mt;
+                    for (int mt = 0; mt < p.mt && wb_row0 + mt * BM < p.P * p.Q; ++mt)
+                        for (int sub = 0; sub < nsub; ++sub)
+                            tma_store_3d(&tmap_y,
+                                         epi_base + static_cast<uint32_t>(e) * epi_bytes +
+                                             static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES,
+                                         n0 + sub * 64, wb_row0 + mt * BM, wb_img);
                 }
                 for (int mt = 0; !p.halo && !p.wb && mt < p.mt && m0 + mt * BM < p.M; ++mt)     // sub-tiles past the last row: nothing to store
                     for (int sub = 0; sub < nsub; ++sub)
@@ -1555,7 +1559,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.taps = R * S;
     if (w_per_image) {
         // w is [N][K][C]: 1x1 stride-1 only, tiles never straddle images
-        if (R != 1 || S != 1 || sh != 1 || sw != 1 || ph || pw || ph_hi || pw_hi || force_mt > 1 || force_halo == 1 ||
+        if (R != 1 || S != 1 || sh != 1 || sw != 1 || ph || pw || ph_hi || pw_hi || force_mt > 2 || force_halo == 1 ||
             force_bres == 1 || force_sk == 1)
             return FVM_ERR_ARG;
         p.wb = 1;
@@ -1615,7 +1619,18 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // Measured on B200: larger tiles did not pay for themselves on the layers tried (fewer, larger hand-offs but less
     // overlap between the roles), so the default stays at one sub-tile; the host's per-layer tuning may force more.
     p.mt = force_mt > 0 ? force_mt : 1;
+    if (p.wb && force_mt == 0 && p.kblocks <= 3 && p.BN <= 64 && p.m_tiles >= 8 * st->sms) {
+        // short reductions into narrow tiles on large maps (measured: 1x1 48->24 at 190x190, N = 64: 143 us with
+        // 128-pixel tiles, 81 us with 256-pixel tiles): halve the per-tile hand-offs when the plan still fits
+        SmemPlan tp;
+        if (plan_smem(p.BN, 2, p.kblocks, K, false, false, &tp)) p.mt = 2;
+    }
     if (p.mt != 1 && p.mt != 2 && p.mt != 4) return FVM_ERR_ARG;
+    if (p.wb) {
+        p.wb_tpi = (P * Q + BM * p.mt - 1) / (BM * p.mt);
+        p.div_tpi = fastdiv_init(static_cast<uint32_t>(p.wb_tpi));
+        p.m_tiles = N * p.wb_tpi;
+    }
     if (!p.halo && !p.wb) p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
     p.a_rows = BM * p.mt < 256 ? BM * p.mt : 256;
     p.a_loads = BM * p.mt / p.a_rows;
@@ -1752,7 +1767,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         const unsigned long long dims[3] = {static_cast<unsigned long long>(C), static_cast<unsigned long long>(P) * Q,
                                             static_cast<unsigned long long>(N)};
         const unsigned long long strides[2] = {static_cast<unsigned long long>(ldx) * 2, static_cast<unsigned long long>(P) * Q * ldx * 2};
-        const unsigned box[3] = {BK, BM, 1};
+        const unsigned box[3] = {BK, static_cast<unsigned>(p.a_rows), 1};
         if (encode_tiled_f16(&tmap_a, x, 3, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
     } else if (!p.im2col) {
         cuuint64_t dims[2] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(p.M)};
