@@ -85,6 +85,7 @@ extern "C" int fvm_init(void) {
             st->sk_floats = 0;
         }
     }
+    st->pair_clusters = conv_pair_capacity();
     st->ready = true;
     return FVM_OK;
 }
@@ -96,6 +97,7 @@ extern "C" long long fvm_query(int what) {
         case 1: return st ? st->sms : -1;
         case 2: return st ? st->max_smem : -1;
         case 3: return g_launches.load(std::memory_order_relaxed);
+        case 4: return st ? st->pair_clusters : -1;   // CTA pairs resident at once (0: pair kernel unavailable)
     }
     return -1;
 }

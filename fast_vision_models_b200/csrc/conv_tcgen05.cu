@@ -100,6 +100,7 @@ struct ConvParams {
     int wb, wb_tpi;
     FastDiv div_tpi;
     int sk;
+    int pair;      // conv_pair_kernel: two CTAs per tile of 256 pixels x BN channels (m_tiles counts 256-pixel tiles)
     uint32_t sk_units;
     FastDiv div_kb;
     float* sk_part;
@@ -1260,6 +1261,302 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
 }
 
+// ------------------------------------------------------------------------------------------------ CTA-pair variant
+// For layers whose time is the L2 -> shared-memory traffic of the weight tiles (few output pixels against a large
+// K x C x R x S weight tensor: the 14x14 and 7x7 stages of a ResNet at batch 64, deep 3x3 layers in general): two CTAs on
+// neighbouring SMs (a cluster of two) compute one tile of 256 pixels x BN channels with tcgen05.mma.cta_group::2. Each
+// CTA loads its own 128 rows of A and HALF of the B tile (BN/2 output channels), the MMA reads both halves across the
+// pair, and each CTA finishes its own 128 rows from its own TMEM (bias, residual, activation, store) as in the plain
+// kernel. Per k-block a CTA fetches 16 KB + BN x 64 B instead of 16 KB + BN x 128 B. No multicast anywhere: every load
+// lands in the shared memory of the CTA that issued it.
+// Protocol (even CTA = leader): `full` barriers live in the leader and count one arrive.expect_tx from each CTA's
+// producer plus the bytes of both CTAs' loads; `empty` and `tfull` barriers are per CTA and are signalled by the
+// leader's MMA thread with one commit per CTA; the leader's `tempty` barriers count the epilogue warps of both CTAs.
+// Plain mode only (A by tiled or im2col TMA, B streamed per k-block, one 128-pixel sub-tile per CTA).
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_y,
+                 const ConvParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t b_half_bytes = static_cast<uint32_t>(p.BN / 2) * BK * 2;     // this CTA's half of a weight k-block
+    const uint32_t stage_bytes = A_STAGE_BYTES + b_half_bytes;
+    const uint32_t epi_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+    const uint32_t epi_bytes = static_cast<uint32_t>(p.nsub) * SUB_BYTES;
+    const uint32_t bar_base = epi_base + static_cast<uint32_t>(p.nepi) * epi_bytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + MAX_ACC + a); };
+    auto res_full_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + e); };
+    auto epi_done_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + MAX_EPI + e); };
+    auto epi_free_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 2 * MAX_EPI + e); };
+    const uint32_t misc_off = (bar_base - smem_u32(smem_raw)) + 8u * NUM_BARRIERS;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + misc_off + 4);
+    const uint32_t bias_off = misc_off + MISC_BYTES;
+    const uint32_t bias_base = smem_u32(smem_raw) + bias_off;
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: its peer
+    const int pair = static_cast<int>(blockIdx.x >> 1), npairs = static_cast<int>(gridDim.x >> 1);
+    const int total_tiles = p.m_tiles * p.n_tiles;    // m_tiles counts 256-pixel tiles here
+    // Tile number `it` of this pair: pair, pair + npairs, ... with the n-tile fastest; this CTA's rows start at m0.
+    auto tile_at2 = [&](int it, int& m0, int& n0) {
+        const int tile = pair + it * npairs;
+        if (tile >= total_tiles) return false;
+        const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
+        n0 = (tile - m_tile * p.n_tiles) * p.BN;
+        m0 = (2 * m_tile + static_cast<int>(rank)) * BM;
+        return true;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar(s), 2);               // one arrive.expect_tx per CTA of the pair (used in the leader only)
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < p.nacc; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 2 * EPI_WARPS);  // the epilogue warps of both CTAs (used in the leader only)
+        }
+        for (int e = 0; e < p.nepi; ++e) {
+            mbar_init(res_full_bar(e), 1);
+            mbar_init(epi_done_bar(e), EPI_WARPS);
+            mbar_init(epi_free_bar(e), 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_y);
+        if (p.has_res) tma_prefetch_desc(&tmap_r);
+    }
+    if (warp == 1) {
+        tmem_pair_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), static_cast<uint32_t>(p.tmem_cols));
+        tmem_pair_relinquish();
+    }
+    // Both CTAs' barriers exist before either CTA signals one of the other's.
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int e = 0;
+            uint32_t e_phase = 0;
+            bool ok = true;
+            const int PQ = p.P * p.Q;
+            const uint32_t lead_full0 = mapa_shared(full_bar(0), 0);    // the leader's `full` barriers, 8 bytes apart
+            const int b_row0 = static_cast<int>(rank) * (p.BN / 2);     // this CTA's half of the n-tile
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            int m0, n0;
+            for (int pit = 0; ok && tile_at2(pit, m0, n0); ++pit) {
+                if (p.has_res) {
+                    if (!mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag)) {
+                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    e_phase ^= 1u << e;
+                    const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
+                    mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(nsub) * SUB_BYTES);
+                    for (int sub = 0; sub < nsub; ++sub)      // rows past M: zero fill
+                        tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0);
+                    if (++e == p.nepi) e = 0;
+                }
+                // a peer whose 128 rows lie past the last pixel loads the leader's rows instead (its results are dropped)
+                const int ml = m0 < p.M ? m0 : m0 - BM;
+                int img = 0, h0 = 0, w0 = 0;
+                if (p.im2col) {
+                    img = static_cast<int>(fastdiv(static_cast<uint32_t>(ml), p.div_pq));
+                    const int rem = ml - img * PQ;
+                    const int pp = static_cast<int>(fastdiv(static_cast<uint32_t>(rem), p.div_q));
+                    const int qq = rem - pp * p.Q;
+                    h0 = pp * p.sh - p.ph;
+                    w0 = qq * p.sw - p.pw;
+                }
+                int tap = 0, cc = 0, r = 0, s = 0;
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        atomicExch(p.status, STATUS_WAIT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
+                    const uint32_t bar = lead_full0 + 8u * static_cast<uint32_t>(stage);
+                    mbar_expect_tx_cluster(bar, stage_bytes);
+                    tma_pair_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, bar, cc * BK, tap, n0 + b_row0);
+                    if (p.im2col)
+                        tma_pair_load_im2col_4d(a_dst, &tmap_a, bar, cc * BK, w0, h0, img,
+                                                static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                    else
+                        tma_pair_load_2d(a_dst, &tmap_a, bar, cc * BK, ml);
+                    if (++cc == p.cchunks) {
+                        cc = 0;
+                        ++tap;
+                        if (++s == p.S) { s = 0; ++r; }
+                    }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (ok) {       // no bulk load of this CTA in flight, no MMA still reading its shared memory, when it exits
+                for (int i = 0; i < p.stages; ++i) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0 && elect_one()) {
+            const uint32_t idesc = umma_idesc_f16_f32(2 * BM, p.BN);
+            const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
+            auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
+            const uint32_t stage_step = stage_bytes >> 4;
+            const uint32_t a_lo0 = lo_of(smem_base);
+            const uint32_t peer_empty0 = mapa_shared(empty_bar(0), 1);
+            const uint32_t peer_tfull0 = mapa_shared(tfull_bar(0), 1);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t st_lo = a_lo0;
+            uint32_t acc_phase = 0;
+            int acc = -1;
+            bool failed = false;
+            uint32_t st_ready = 0;
+            int m0, n0;
+            for (int it = 0; tile_at2(it, m0, n0); ++it) {
+                if (++acc == p.nacc) acc = 0;
+                failed |= !mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag);
+                acc_phase ^= 1u << acc;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.acc_stride);
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!st_ready) failed |= !mbar_wait(full_bar(stage), phase, abort_flag);
+                    tc_fence_after();
+                    {
+                        const bool wrap = stage + 1 == p.stages;
+                        st_ready = mbar_test(full_bar(wrap ? 0 : stage + 1), wrap ? phase ^ 1u : phase);
+                    }
+                    umma_pair_f16_kblock(d_tmem, st_lo, hi128, st_lo + (A_STAGE_BYTES >> 4), hi128, idesc,
+                                         static_cast<uint32_t>(kb != 0));
+                    umma_pair_commit(empty_bar(stage));                                      // frees the stage in both CTAs
+                    umma_pair_commit(peer_empty0 + 8u * static_cast<uint32_t>(stage));
+                    st_lo += stage_step;
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }
+                }
+                umma_pair_commit(tfull_bar(acc));                                            // both halves of the accumulator
+                umma_pair_commit(peer_tfull0 + 8u * static_cast<uint32_t>(acc));
+            }
+            if (failed) atomicExch(p.status, STATUS_WAIT_MMA);
+        }
+        __syncwarp();
+    } else if (warp < STORE_WARP) {
+        // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const int lane_group = warp & 3;
+        const int group = (warp - 2) >> 2;
+        const int row = lane_group * 32 + lane;
+        const uint32_t row_xor = static_cast<uint32_t>(row & 7);
+        const uint32_t bias_s = bias_base;
+        const uint32_t stage0 = epi_base + static_cast<uint32_t>(row) * 128u;
+        {
+            float* bias_f = reinterpret_cast<float*>(smem_raw + bias_off);
+            for (int i = threadIdx.x - 64; i < p.bias_elems; i += EPI_WARPS * 32)
+                bias_f[i] = (p.bias != nullptr && i < p.K) ? __half2float(p.bias[i]) : 0.f;
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        }
+        const uint32_t lead_tempty0 = mapa_shared(tempty_bar(0), 0);
+        uint32_t acc_phase = 0, e_phase = 0;
+        int e = 0, acc = -1;
+        bool ok = true;
+        const int act_t = (p.act == 0 || p.act == 1 || p.act == 3 || p.act == 5) ? p.act : 2;
+        const int variant = act_t * 2 + (p.has_res ? 1 : 0);
+        int m0, n0;
+        for (int it = 0; ok && tile_at2(it, m0, n0); ++it) {
+            if (++acc == p.nacc) acc = 0;
+            const bool got_buf = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(e), (e_phase >> e) & 1u, abort_flag)
+                                           : mbar_wait<EPI_BACKOFF_NS>(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag);
+            if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag)) {
+                if (lane == 0) atomicExch(p.status, STATUS_WAIT_EPILOGUE);
+                ok = false;
+                break;
+            }
+            e_phase ^= 1u << e;
+            acc_phase ^= 1u << acc;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                                   static_cast<uint32_t>(acc * p.acc_stride);
+            const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
+            const int ncols = min(p.BN, p.K - n0);
+            switch (variant) {
+                case 0: epilogue_rows<0, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 1: epilogue_rows<0, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 2: epilogue_rows<1, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 3: epilogue_rows<1, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 4: epilogue_rows<2, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 5: epilogue_rows<2, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 6: epilogue_rows<3, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 7: epilogue_rows<3, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                case 10: epilogue_rows<5, false>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+                default: epilogue_rows<5, true>(p, t_row, stage_row0, row_xor, bias_s, n0, ncols, group); break;
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(lead_tempty0 + 8u * static_cast<uint32_t>(acc));   // this CTA's half may be overwritten
+                mbar_arrive(epi_done_bar(e));
+            }
+            if (++e == p.nepi) e = 0;
+        }
+    } else {
+        // ------------------------------------------------------------------ store warp (both CTAs)
+        if (elect_one()) {
+            uint32_t e_phase = 0;
+            int e = 0;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            bool ok = true;
+            int m0, n0;
+            for (int sit = 0; ok && tile_at2(sit, m0, n0); ++sit) {
+                if (!mbar_wait<EPI_BACKOFF_NS>(epi_done_bar(e), (e_phase >> e) & 1u, abort_flag)) {
+                    atomicExch(p.status, STATUS_WAIT_STORE);
+                    ok = false;
+                    break;
+                }
+                e_phase ^= 1u << e;
+                const int nsub = min(p.nsub, (p.K - n0 + 63) >> 6);
+                if (m0 < p.M) {
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_store_2d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                     n0 + sub * 64, m0);
+                    tma_store_commit();
+                    tma_store_wait_read();
+                }
+                mbar_arrive(epi_free_bar(e));
+                if (++e == p.nepi) e = 0;
+            }
+            tma_store_wait_read();
+        }
+    }
+
+    // Neither CTA leaves (or frees TMEM) while the other may still signal its barriers or read its shared memory.
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_pair_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- host side
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1296,9 +1593,33 @@ int conv_host_init() {
     if (cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
             cudaSuccess ||
         cudaFuncSetAttribute(conv_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
-            cudaSuccess)
+            cudaSuccess ||
+        cudaFuncSetAttribute(conv_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
         return FVM_ERR_SETUP;
     return FVM_OK;
+}
+
+// How many CTA pairs (clusters of two, one CTA per SM) the device runs at once: the pair kernel's grid never exceeds
+// it, so that every pair is resident from the start. 0 if clusters cannot be launched here.
+int conv_pair_capacity() {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2);
+    cfg.blockDim = dim3(CONV_THREADS);
+    cfg.dynamicSmemBytes = 227 * 1024;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, conv_pair_kernel, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
 }
 
 int encode_tiled_f16(CUtensorMap* map, const void* ptr, int rank, const unsigned long long* dims,
@@ -1325,11 +1646,12 @@ struct SmemPlan {
     int stages, nepi, nacc;
     size_t bytes;
 };
-static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, SmemPlan* out, uint32_t halo_bytes = 0) {
+static bool plan_smem(int BN, int MT, int kblocks, int K, bool tapk, bool bres, SmemPlan* out, uint32_t halo_bytes = 0,
+                      bool pair = false) {
     const int n_tiles = (K + BN - 1) / BN;
     // halo mode (halo_bytes > 0): the activations live in two staged input patches, the stages carry weights only
     const uint32_t stage_bytes = (halo_bytes ? 0u : static_cast<uint32_t>(MT) * A_STAGE_BYTES) +
-                                 ((tapk || bres) ? 0u : static_cast<uint32_t>(BN) * BK * 2);
+                                 ((tapk || bres) ? 0u : static_cast<uint32_t>(pair ? BN / 2 : BN) * BK * 2);   // a pair CTA holds half of B
     const uint32_t bres_bytes = tapk ? static_cast<uint32_t>(kblocks) * BN * BK * 2   // 8 x 16 B or 4 x 32 B per row
                                      : (bres ? static_cast<uint32_t>(kblocks) * BN * BK * 2 : 0u);
     const uint32_t epi_bytes = static_cast<uint32_t>(MT * ((BN + 63) / 64)) * SUB_BYTES;
@@ -1527,7 +1849,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (!x || !w || !y) return FVM_ERR_ARG;
     // force_bn: low 16 bits = output-channel tile (0 = choose), bits 16..23 = sub-tiles per tile (0 = choose),
     // bits 24..25 = weight-resident mode (0 = choose, 1 = on, 2 = off), bits 26..27 = halo mode, bits 28..29 = stream-K
-    // (same coding)
+    // (same coding), bit 30 = CTA pairs (conv_pair_kernel) on
+    const int force_pair = force_bn > 0 ? ((force_bn >> 30) & 1) : 0;
     const int force_sk = force_bn > 0 ? ((force_bn >> 28) & 3) : 0;
     const int force_halo = force_bn > 0 ? ((force_bn >> 26) & 3) : 0;
     const int force_bres = force_bn > 0 ? ((force_bn >> 24) & 3) : 0;
@@ -1583,7 +1906,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // Halo mode for 3x3 stride-1 convolutions (dilation up to 4): an m-tile is a 16 x 8 patch of output pixels of one
     // image. Chosen when few patch pixels fall outside the image (they are computed and clipped by the store).
     uint32_t halo_bytes = 0;
-    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1) {
+    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1 && !force_pair) {
         const int ty = (P + HALO_TH - 1) / HALO_TH, tx = (Q + HALO_TW - 1) / HALO_TW;
         const double eff = static_cast<double>(P) * Q / (static_cast<double>(ty) * tx * BM);
         // by default only for inputs of one 64-channel chunk: there the taps are accumulated in the same order as in
@@ -1634,6 +1957,13 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (!p.halo && !p.wb) p.m_tiles = (p.M + BM * p.mt - 1) / (BM * p.mt);
     p.a_rows = BM * p.mt < 256 ? BM * p.mt : 256;
     p.a_loads = BM * p.mt / p.a_rows;
+    // CTA pairs (conv_pair_kernel): on request only, plain mode only
+    if (force_pair) {
+        if (p.tapk || p.halo || p.wb || p.mt != 1 || force_bres == 1 || force_sk == 1 || st->pair_clusters <= 0)
+            return FVM_ERR_ARG;
+        p.pair = 1;
+        p.m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
+    }
 
     // Weight-resident mode: the weight tile of a CTA's n-tile (all k-blocks) is loaded once and kept; the stages then
     // carry activations only, so more tiles' worth of loads are in flight and the weights are not re-read from L2 for
@@ -1643,7 +1973,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     {
         const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
         const long long units = tiles * p.kblocks;
-        const bool can = !p.tapk && !p.halo && !p.wb && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
+        const bool can = !p.tapk && !p.halo && !p.wb && !p.pair && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
                          units >= st->sms && units < 0x7fffffffll &&
                          static_cast<size_t>(st->sms) * BM * p.BN <= st->sk_floats;
         if (force_sk == 1 && !can) return FVM_ERR_ARG;
@@ -1657,7 +1987,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     }
     SmemPlan sp;
     p.bres = 0;
-    if (!p.sk && !p.wb && !p.tapk && force_bres != 2 && p.n_tiles <= st->sms) {
+    if (!p.sk && !p.wb && !p.tapk && !p.pair && force_bres != 2 && p.n_tiles <= st->sms) {
         const long long wbytes = static_cast<long long>(p.kblocks) * p.BN * BK * 2;
         const int cta_per_n = st->sms / p.n_tiles;
         const bool worth = p.m_tiles >= 2 * cta_per_n;
@@ -1668,7 +1998,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
             p.bres = 1;
     }
     if (force_bres == 1 && !p.bres) return FVM_ERR_ARG;
-    if (!plan_smem(p.BN, p.mt, p.kblocks, K, p.tapk != 0, p.bres != 0, &sp, halo_bytes)) return FVM_ERR_ARG;
+    if (!plan_smem(p.BN, p.mt, p.kblocks, K, p.tapk != 0, p.bres != 0, &sp, halo_bytes, p.pair != 0)) return FVM_ERR_ARG;
     p.bias_elems = p.n_tiles * p.BN;
     p.stages = sp.stages;
     p.nepi = sp.nepi;
@@ -1742,7 +2072,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(R * S),
                               static_cast<cuuint64_t>(K) * (p.wb ? N : 1)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 2, static_cast<cuuint64_t>(R) * S * C * 2};
-        cuuint32_t box[3] = {static_cast<cuuint32_t>(p.tapk ? p.tapk : BK), 1, static_cast<cuuint32_t>(p.BN)};
+        cuuint32_t box[3] = {static_cast<cuuint32_t>(p.tapk ? p.tapk : BK), 1, static_cast<cuuint32_t>(p.pair ? p.BN / 2 : p.BN)};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = g_encode_tiled(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(w), dims, strides,
                                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1814,6 +2144,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         grid = cta_per_n * p.n_tiles;
     }
     if (p.sk) grid = st->sms;       // units >= SMs: every CTA gets at least one k-block
+    if (p.pair) grid = 2 * static_cast<int>(total_tiles < st->pair_clusters ? total_tiles : st->pair_clusters);
     return launch_conv_kernel(tmap_a, tmap_b, tmap_r, tmap_y, p, grid, smem, stream);
 }
 
@@ -1822,26 +2153,39 @@ static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap
     // Programmatic dependent launch: the grid may start (set-up only) while the previous kernel of the stream drains;
     // the kernel itself waits (griddepcontrol.wait) before it touches activations or outputs.
     static int use_pdl = [] { const char* v = getenv("FVM_B200_PDL"); return (v && v[0] == '0') ? 0 : 1; }();
-    if (use_pdl) {
+    if (use_pdl || p.pair) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(static_cast<unsigned>(grid));
         cfg.blockDim = dim3(CONV_THREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr.val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        const cudaError_t err = p.sk ? cudaLaunchKernelEx(&cfg, conv_streamk_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p)
-                                     : cudaLaunchKernelEx(&cfg, conv_tcgen05_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p);
+        cudaLaunchAttribute attrs[2];
+        int na = 0;
+        if (use_pdl) {
+            attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        if (p.pair) {       // clusters of two CTAs: blocks 2i and 2i + 1 share a tile
+            attrs[na].id = cudaLaunchAttributeClusterDimension;
+            attrs[na].val.clusterDim.x = 2;
+            attrs[na].val.clusterDim.y = 1;
+            attrs[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        cfg.attrs = attrs;
+        cfg.numAttrs = static_cast<unsigned>(na);
+        const cudaError_t err = p.pair ? cudaLaunchKernelEx(&cfg, conv_pair_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p)
+                                : p.sk ? cudaLaunchKernelEx(&cfg, conv_streamk_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p)
+                                       : cudaLaunchKernelEx(&cfg, conv_tcgen05_kernel, tmap_a, tmap_b, tmap_r, tmap_y, p);
         if (err == cudaSuccess) {
             count_launch();
             return FVM_OK;
         }
-        (void)cudaGetLastError();   // not accepted here (e.g. by an older driver during capture): plain launches from now on
-        use_pdl = 0;
+        (void)cudaGetLastError();
+        if (p.pair) return FVM_ERR_LAUNCH;
+        use_pdl = 0;      // not accepted here (e.g. by an older driver during capture): plain launches from now on
     }
     if (p.sk) conv_streamk_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
     else conv_tcgen05_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);

@@ -17,6 +17,7 @@ struct DeviceState {
     float* sk_part = nullptr;
     int* sk_flags = nullptr;
     size_t sk_floats = 0;
+    int pair_clusters = 0;        // CTA pairs (clusters of two) the device runs at once; 0: pair kernel unavailable
     bool ready = false;
 };
 
@@ -25,6 +26,7 @@ DeviceState* device_state();
 void count_launch();
 
 int conv_host_init();
+int conv_pair_capacity();
 // cuTensorMapEncodeTiled for an fp16 tensor of `rank` dimensions (innermost first): sizes, byte strides of dimensions
 // 1.., box; no interleave, 128-byte swizzle or none, zero fill outside the tensor. Returns an FVM_* status.
 int encode_tiled_f16(CUtensorMap* map, const void* ptr, int rank, const unsigned long long* dims,

@@ -493,6 +493,107 @@ __host__ __device__ inline uint32_t umma_idesc_f16_f32(int m, int n) {
     return d;
 }
 
+// ---------------------------------------------------------------- CTA pairs (thread-block clusters of two)
+// A pair of CTAs on neighbouring SMs shares one MMA: tcgen05.mma.cta_group::2 with M = 256 is issued by one thread of
+// the even CTA, reads rows 0..127 of A and the first N/2 rows of B from that CTA's shared memory and rows 128..255 /
+// the second N/2 rows of B from the odd CTA's (same shared-memory offsets in both), and leaves rows 0..127 of D in the
+// even CTA's TMEM and rows 128..255 in the odd CTA's. Each SM therefore fetches only half of the B tile.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// All threads of all CTAs of the cluster (also a CTA-wide barrier); release / acquire at cluster scope.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrivals on an mbarrier of another CTA of the cluster (`bar` from mapa_shared). Default semantics (release at CTA
+// scope), as for the local forms: what crosses the pair is ordered by the tcgen05 fences and the async proxy, and a
+// cluster-scope acquire in the MMA thread's waits cost about 0.7 us per k-block when it was tried.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+// Bulk tensor loads whose completion is counted on an mbarrier of either CTA of the pair (`bar`: a shared::cluster
+// address); the destination is this CTA's shared memory. No multicast: each CTA fetches its own boxes.
+__device__ __forceinline__ void tma_pair_load_2d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_3d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_im2col_4d(uint32_t dst, const void* desc, uint32_t bar, int c, int w, int h,
+                                                        int n, uint16_t off_w, uint16_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+        "h"(off_h)
+        : "memory");
+}
+// TMEM of both CTAs of the pair: executed by the same warp of each CTA with the same arguments.
+__device__ __forceinline__ void tmem_pair_alloc(uint32_t smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_pair_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_pair_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// The four MMAs (256 x N x 16 each, over both CTAs) of one 64-half k-block; see umma_f16_kblock.
+__device__ __forceinline__ void umma_pair_f16_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                     uint32_t b_hi, uint32_t idesc, uint32_t acc0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 al, bl;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t"
+        "add.u32 al, %1, 2;\n\t"
+        "add.u32 bl, %3, 2;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, 1;\n\t"
+        "add.u32 al, %1, 4;\n\t"
+        "add.u32 bl, %3, 4;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, 1;\n\t"
+        "add.u32 al, %1, 6;\n\t"
+        "add.u32 bl, %3, 6;\n\t"
+        "mov.b64 da, {al, %2};\n\t"
+        "mov.b64 db, {bl, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, 1;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc0)
+        : "memory");
+}
+// Arrive on an mbarrier of either CTA of the pair (`bar`: shared::cluster address) once every pair MMA issued so far
+// by this thread has finished.
+__device__ __forceinline__ void umma_pair_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // ---------------------------------------------------------------- activations shared by every kernel
 // Codes follow the reference's act_f (classification/fast/csrc/fused_conv.cu:33-43):
 // 0 none, 1 relu, 2 relu6, 3 silu, 4 hardswish, 5 gelu (erf), 6 gelu (tanh).

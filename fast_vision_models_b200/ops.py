@@ -79,6 +79,11 @@ def launches() -> int:
     return int(lib().fvm_query(3))
 
 
+def query(what: int) -> int:
+    """fvm_query: 0 version, 1 SM count, 2 max dynamic shared memory, 3 launches, 4 CTA pairs resident at once."""
+    return int(lib().fvm_query(int(what)))
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 

@@ -44,7 +44,8 @@ extern "C" {
 int fvm_init(void);
 
 /* what: 0 library version, 1 SM count of the current device, 2 max dynamic shared memory per block (bytes),
- * 3 number of kernels launched by this library since load (all devices). */
+ * 3 number of kernels launched by this library since load (all devices), 4 number of two-CTA clusters the current
+ * device runs at once (0: the CTA-pair convolution kernel is unavailable). */
 long long fvm_query(int what);
 
 /* Reads and clears the asynchronous status word of the current device (0 = no fault). Call after synchronising. */
@@ -75,7 +76,10 @@ int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* r
  * border) once per 64 channels instead of once per filter tap; bits 28..29 = stream-K, same coding: the k-blocks of all
  * tiles are cut into one equal run per SM (for layers with fewer tiles than SMs); tiles whose k-blocks fall into
  * several runs are summed in fp32 through a per-device scratch buffer that all streams share, so two stream-K launches
- * on different streams of one device must not overlap in time. Shapes that do not fit return 1. */
+ * on different streams of one device must not overlap in time; bit 30 = CTA pairs: two CTAs on neighbouring SMs (a
+ * cluster of two) share each tile of 256 pixels x tile_n channels through tcgen05.mma.cta_group::2 and each loads only
+ * half of the weight tile (for layers bound by re-reading the weights from L2; same results as the single-CTA kernel
+ * bit for bit; not with sub-tiles, halo, weight-resident or stream-K mode). Shapes that do not fit return 1. */
 int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y,
                         int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                         long long ldx, long long ldy, long long ldr, int act, int tile_n, void* stream);

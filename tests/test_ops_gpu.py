@@ -174,6 +174,56 @@ def test_conv_stream_k_is_refused_where_it_does_not_apply():
         ops.conv_fused(x8, w8, None, None, (3, 3), (2, 2), 0, tile_n=1 << 28)        # tap-packed stem
 
 
+PAIR_CASES = [
+    # N, H, W, C, K, R, pad, stride, res, act, tile width (0 = library's choice)
+    (64, 14, 14, 1024, 256, 1, 0, 1, False, 1, 256),   # 49 tiles of 256 pixels x 256 channels, 16 k-blocks
+    (64, 14, 14, 256, 256, 3, 1, 1, False, 1, 256),    # im2col loads in both CTAs, 36 k-blocks
+    (64, 14, 14, 256, 1024, 1, 0, 1, True, 1, 128),    # residual, 8 n-tiles
+    (64, 7, 7, 2048, 512, 1, 0, 1, False, 1, 256),     # M = 3136 = 12.25 tiles: the last peer CTA has no rows
+    (64, 7, 7, 512, 2048, 1, 0, 1, True, 1, 0),
+    (64, 7, 7, 512, 512, 3, 1, 1, False, 1, 128),
+    (64, 1, 1, 2048, 1000, 1, 0, 1, False, 0, 128),    # classifier GEMM: 64 rows, ragged last column tile
+    (64, 14, 14, 1024, 512, 1, 0, 2, False, 0, 256),   # stride-2 downsample (im2col map)
+    (37, 9, 11, 128, 192, 1, 0, 1, True, 3, 64),       # ragged rows, SiLU
+    (12, 10, 10, 96, 40, 3, 1, 1, False, 5, 0),        # ragged channels on both sides, GELU
+    (3, 40, 40, 64, 32, 3, 2, 1, False, 1, 32),        # padding 2, one narrow tile
+]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES)
+def test_conv_cta_pairs_match_oracle_and_single_cta_kernel(case):
+    # two CTAs per 256-pixel tile, each loading half of the weight tile (tcgen05.mma.cta_group::2). Against the oracle
+    # (first and last image) and bit for bit against the single-CTA kernel (same products, same order of the k-blocks).
+    ops.init(DEV)
+    if ops.query(4) <= 0:
+        pytest.skip("this device cannot launch CTA pairs")
+    N, H, W, C, K, Rr, pad, stride, res, act, bn = case
+    x, w, b = gen((N, C, H, W), 31), gen((K, C, Rr, Rr), 32, 0.02), gen((K,), 33, 0.1)
+    P = (H + 2 * pad - Rr) // stride + 1
+    Q = (W + 2 * pad - Rr) // stride + 1
+    r = gen((N, K, P, Q), 34) if res else None
+    args = (cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (stride, stride), act)
+    y_pair = ops.conv_fused(*args, tile_n=(1 << 30) | bn)
+    assert ops.last_status() == 0
+    y_one = ops.conv_fused(*args, tile_n=(2 << 28) | (2 << 26) | (2 << 24) | bn)     # plain schedule, im2col, streamed weights
+    assert ops.last_status() == 0
+    for img in (0, N - 1):
+        ref = R.conv_fused_ref(x[img:img + 1], w, b, None if r is None else r[img:img + 1], (pad, pad), (stride, stride), act)
+        close(y_pair[img:img + 1], ref)
+    assert torch.equal(y_pair, y_one)
+
+
+def test_conv_cta_pairs_are_refused_where_they_do_not_apply():
+    x8, w8 = cl(gen((2, 8, 32, 32), 1)), cl(gen((64, 8, 7, 7), 2, 0.05))
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x8, w8, None, None, (3, 3), (2, 2), 0, tile_n=1 << 30)                  # tap-packed stem
+    x, w = cl(gen((2, 64, 16, 16), 1)), cl(gen((64, 64, 3, 3), 2, 0.05))
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x, w, None, None, (1, 1), (1, 1), 0, tile_n=(1 << 30) | (1 << 28))      # with stream-K
+    with pytest.raises(ops.FvmError):
+        ops.conv_fused(x, w, None, None, (1, 1), (1, 1), 0, tile_n=(1 << 30) | (2 << 16))      # with two sub-tiles
+
+
 HALO_CASES = [
     # N, H, W, C, K, dil, res, tile, weight-resident (0 choose / 1 on / 2 off)
     (2, 16, 8, 64, 64, 1, False, 0, 2),        # exactly one patch per image
