@@ -1355,8 +1355,22 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int PQ = p.P * p.Q;
             const uint32_t lead_full0 = mapa_shared(full_bar(0), 0);    // the leader's `full` barriers, 8 bytes apart
             const int b_row0 = static_cast<int>(rank) * (p.BN / 2);     // this CTA's half of the n-tile
-            asm volatile("griddepcontrol.wait;" ::: "memory");
             int m0, n0;
+            // Weights are constants: the B halves of the first k-blocks (one per pipeline stage) are requested before the
+            // wait for the preceding kernel, their barriers armed for the whole stage; the A tiles follow after the wait.
+            int pre = 0;
+            for (int pit = 0; pre < p.stages && tile_at2(pit, m0, n0); ++pit) {
+                int tap = 0, cc = 0;
+                for (int kb = 0; kb < p.kblocks && pre < p.stages; ++kb, ++pre) {
+                    const uint32_t bar = lead_full0 + 8u * static_cast<uint32_t>(pre);
+                    mbar_expect_tx_cluster(bar, stage_bytes);
+                    tma_pair_load_3d(smem_base + static_cast<uint32_t>(pre) * stage_bytes + A_STAGE_BYTES, &tmap_b, bar, cc * BK,
+                                     tap, n0 + b_row0);
+                    if (++cc == p.cchunks) { cc = 0; ++tap; }
+                }
+            }
+            int issued = 0;       // k-blocks issued so far (the first `pre` have their barrier armed and B on the way)
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int pit = 0; ok && tile_at2(pit, m0, n0); ++pit) {
                 if (p.has_res) {
                     if (!mbar_wait(epi_free_bar(e), ((e_phase >> e) & 1u) ^ 1u, abort_flag)) {
@@ -1385,15 +1399,19 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                    const bool armed = issued < pre;      // this stage's barrier and B half were set up before the wait
+                    ++issued;
+                    if (!armed && !mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         atomicExch(p.status, STATUS_WAIT_PRODUCER);
                         ok = false;
                         break;
                     }
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
                     const uint32_t bar = lead_full0 + 8u * static_cast<uint32_t>(stage);
-                    mbar_expect_tx_cluster(bar, stage_bytes);
-                    tma_pair_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, bar, cc * BK, tap, n0 + b_row0);
+                    if (!armed) {
+                        mbar_expect_tx_cluster(bar, stage_bytes);
+                        tma_pair_load_3d(a_dst + A_STAGE_BYTES, &tmap_b, bar, cc * BK, tap, n0 + b_row0);
+                    }
                     if (p.im2col)
                         tma_pair_load_im2col_4d(a_dst, &tmap_a, bar, cc * BK, w0, h0, img,
                                                 static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));

@@ -200,6 +200,9 @@ class FusedConv(nn.Module):
             # few tiles per SM: stream-K (bits 28..29 = 1) spreads the k-blocks of all tiles evenly over the SMs; offered
             # per tile width against the plain schedule (= 2)
             cands += [c | (1 << 28) for c in widths] + [c | (2 << 28) for c in widths]
+        if self.w.shape[1] > 16 and ops.query(4) > 0:
+            # CTA pairs (bit 30): two SMs share each tile of 256 pixels and each fetches half of the weight tile; same bits
+            cands += [c | (1 << 30) for c in widths]
         best = 0
         if len(cands) > 1:
             # Candidates are timed in rounds (every candidate once per round, best burst kept), so that a drift of the
