@@ -22,6 +22,7 @@ an on-device second opinion in tests). Every returned module maps fp32 NCHW inpu
 from __future__ import annotations
 
 import copy
+import os
 from typing import Optional
 
 import torch
@@ -30,6 +31,8 @@ from torch import nn
 from .. import fold, ops
 from ..layers import GATE_IN_WEIGHTS, DepthwiseConv, FusedConv, LayerNormCL, SqueezeExcite, act_code
 from ..runtime import GraphRunner
+
+CHAIN_RESNET = os.environ.get("FVM_B200_CHAIN_RESNET", "1") != "0"
 
 
 # ------------------------------------------------------------------------------------------------ ResNet
@@ -60,6 +63,9 @@ class ResNetTrunk(nn.Module):
             self.stage_ends.append(len(blocks))
         self.blocks = nn.ModuleList(blocks)
         self.out_channels = self.blocks[-1]["convs"][-1].out_channels
+        # first block whose convolutions run as chain launches: the second stage (the first stage's 3x3 layers over 64
+        # channels are faster on staged input patches, a mode the chain kernel does not have)
+        self.chain_from = self.stage_ends[int(os.environ.get('FVM_B200_CHAIN_STAGE', '1')) - 1] if CHAIN_RESNET else len(blocks)
 
     def forward(self, x: torch.Tensor, want_stage3: bool = False):
         # fp32 / fp16 NCHW image batch (fewer than 8 channels), or an fp16 NHWC8 tensor (clf::input_nhwc8's output)
@@ -67,15 +73,24 @@ class ResNetTrunk(nn.Module):
         k, s, p, ceil = self.pool
         x = ops.maxpool(x, k, s, p, ceil)
         aux = None
-        for i, blk in enumerate(self.blocks):
-            identity = blk["ds"](x) if "ds" in blk else x
-            y = x
-            convs = blk["convs"]
-            for c in convs[:-1]:
-                y = c(y)
-            x = convs[-1](y, res=identity)
-            if want_stage3 and i + 1 == self.stage_ends[2]:
-                aux = x
+        chained = False
+        try:
+            for i, blk in enumerate(self.blocks):
+                if i == self.chain_from:
+                    # from here on the convolutions are recorded and go out as chain launches (one kernel per run of up
+                    # to 48 layers, tiles ordered by their data dependencies) instead of one launch per layer
+                    chained = ops.chain_begin()
+                identity = blk["ds"](x) if "ds" in blk else x
+                y = x
+                convs = blk["convs"]
+                for c in convs[:-1]:
+                    y = c(y)
+                x = convs[-1](y, res=identity)
+                if want_stage3 and i + 1 == self.stage_ends[2]:
+                    aux = x
+        finally:
+            if chained:
+                ops.chain_end()
         return (x, aux) if want_stage3 else x
 
 

@@ -86,6 +86,15 @@ extern "C" int fvm_init(void) {
         }
     }
     st->pair_clusters = conv_pair_capacity();
+    {
+        const int count = 1 << 16;
+        if (cudaMalloc(reinterpret_cast<void**>(&st->chain_flags), static_cast<size_t>(count) * sizeof(int)) == cudaSuccess) {
+            st->chain_flag_count = count;
+        } else {
+            (void)cudaGetLastError();
+            st->chain_flags = nullptr;
+        }
+    }
     st->ready = true;
     return FVM_OK;
 }
@@ -110,6 +119,10 @@ extern "C" int fvm_last_status(int* code) {
     // a kernel that gave up may have left stream-K counters raised: clear them so that later launches start clean
     if (*code != 0 && st->sk_flags) cudaMemset(st->sk_flags, 0, static_cast<size_t>(st->sms) * sizeof(int));
     return FVM_OK;
+}
+
+extern "C" int fvm_conv_chain_f16(const fvm_chain_layer* layers, int n_layers, void* stream) {
+    return conv_chain_launch(layers, n_layers, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* res, const float* scale,

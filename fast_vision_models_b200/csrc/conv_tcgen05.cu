@@ -28,6 +28,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "fvm_internal.h"
 #include "ptx_sm100.cuh"
@@ -1575,6 +1576,466 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------------------------------------ layer chains
+// A run of consecutive convolutions (the bottleneck blocks of a ResNet stage, say) as ONE launch of CTA pairs: the
+// tiles of all layers form one sequence (layer by layer, 256 pixels x BN channels each, as in conv_pair_kernel), pair
+// i takes tiles i, i + pairs, i + 2 pairs, ..., and a tile starts as soon as the tiles of earlier layers that hold its
+// input pixels (and its residual tile) are complete. What this removes against one launch per layer: the launch /
+// set-up / drain latency between layers (about 3.5 us each), the idle SMs of every layer's last partial wave (the next
+// layer's first tiles run there), and the cold start of each layer's pipeline (weights of the next tile are requested
+// while the dependency is still being waited for).
+// Completion is tracked per layer and 256-row tile by a counter in global memory: the store thread of each of the
+// tile's 2 * n_tiles CTA-tiles adds one after its bulk stores have completed (cp.async.bulk.wait_group 0, proxy fence,
+// release at GPU scope); a producer thread that needs rows [lo, hi] of an earlier layer's output polls (bounded) the
+// counters of the tiles that hold them (acquire at GPU scope, then a proxy fence before its bulk loads). Every pair
+// walks its tiles in increasing order and a tile depends on tiles of earlier layers only, so the pair that holds the
+// lowest unfinished tile can always proceed: no deadlock as long as all pairs are resident, which the grid size
+// (at most the number of clusters the device runs at once) guarantees. The host zeroes the counters before the launch
+// and makes sure no buffer of the chain aliases another (layers no longer run in stream order).
+// Shared-memory map: [stages x slot (A 16 KB | B half up to maxBN x 64 B)] [staging region, cut per layer into
+// buffers of nsub x 16 KB] [barriers] [tmem slot, abort flag, released-tile counter] [bias copy of the current layer].
+// A staging buffer is free once the store thread has counted the tile that used it last; where consecutive layers
+// cut the region differently (tiles of another width) the first tile of the new cut waits for all earlier tiles.
+static constexpr int CHAIN_MAX_LAYERS = 48;
+static constexpr int CHAIN_MAX_EXT_RES = 4;
+static constexpr int STATUS_WAIT_CHAIN = 0x108;
+
+struct ChainLayer {
+    CUtensorMap tmap_a, tmap_b, tmap_y;   // the residual of a layer is read through the output map of layer res_layer
+    const __half* bias;
+    const float* scale;
+    int M, K, P, Q, H, W, S;       // output rows / channels / map, input map, filter width
+    int sh, sw, ph, pw, dh, dw, rspan;   // rspan = (R - 1) * dh
+    int cchunks, kblocks, BN, n_tiles, m_tiles, nsub, nepi, im2col, act, has_res;
+    int tile0;                     // index of the layer's first tile in the chain's tile sequence
+    int in_layer, res_layer;       // layers of the chain that produce this layer's input / residual (-1: from outside)
+    int res_ext;                   // residual from outside the chain: index into ChainParams::ext_res
+    int flag0;                     // index of the layer's first completion counter (one per 256-row tile)
+    int done_count;                // 2 * n_tiles: arrivals that complete one 256-row tile
+    int bias_elems;
+    FastDiv div_ntiles, div_pq, div_q;
+};
+struct ChainParams {
+    int n_layers, total_tiles, stages;
+    uint32_t stage_bytes, epi_region_bytes;
+    int* flags;
+    int* status;
+    CUtensorMap ext_res[CHAIN_MAX_EXT_RES];   // residuals that no layer of the chain produces
+    ChainLayer L[CHAIN_MAX_LAYERS];
+};
+static_assert(sizeof(ChainParams) <= 32 * 1024 - 256, "kernel parameters are limited to 32764 bytes");
+
+// Bounded wait until *flag >= need. Returns false (and raises the CTA's abort flag) when it gives up.
+__device__ __forceinline__ bool chain_wait_flag(const int* flag, int need, volatile int* abort_flag) {
+    if (ld_acquire_gpu(flag) >= need) return true;
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    for (;;) {
+        __nanosleep(32);
+        if (ld_acquire_gpu(flag) >= need) return true;
+        if ((++spins & 0x3f) == 0) {
+            if (*abort_flag) return false;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv_chain_kernel(const __grid_constant__ ChainParams cp) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t stage_bytes = cp.stage_bytes;
+    const uint32_t epi_base = smem_base + static_cast<uint32_t>(cp.stages) * stage_bytes;
+    const uint32_t bar_base = epi_base + cp.epi_region_bytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + MAX_ACC + a); };
+    auto res_full_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + e); };
+    auto epi_done_bar = [&](int e) { return bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + MAX_EPI + e); };
+    const uint32_t epi_sync_bar = bar_base + 8u * (2 * MAX_STAGES + 2 * MAX_ACC + 3 * MAX_EPI);   // the epilogue warps among themselves
+    const uint32_t misc_off = (bar_base - smem_u32(smem_raw)) + 8u * NUM_BARRIERS;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + misc_off + 4);
+    // number of this CTA's tiles whose staging buffer the store thread has released. A role that starts a layer whose
+    // staging buffers are cut differently waits until every earlier tile is counted here: barrier parities cannot say
+    // that, a role that did not take the buffers itself may be several uses ahead of their release.
+    volatile int* released = reinterpret_cast<volatile int*>(smem_raw + misc_off + 8);
+    static_assert(MISC_BYTES >= 12, "tmem slot, abort flag, released-tile counter");
+    const uint32_t bias_off = misc_off + MISC_BYTES;
+    const uint32_t bias_base = smem_u32(smem_raw) + bias_off;
+    constexpr int NACC = 2;
+    constexpr uint32_t ACC_STRIDE = 256;
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = static_cast<int>(blockIdx.x >> 1), npairs = static_cast<int>(gridDim.x >> 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < cp.stages; ++s) {
+            mbar_init(full_bar(s), 2);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < NACC; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 2 * EPI_WARPS);
+        }
+        for (int e = 0; e < MAX_EPI; ++e) {
+            mbar_init(res_full_bar(e), 1);
+            mbar_init(epi_done_bar(e), EPI_WARPS);
+        }
+        mbar_init(epi_sync_bar, EPI_WARPS);
+        *abort_flag = 0;
+        *released = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_pair_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), NACC * ACC_STRIDE);
+        tmem_pair_relinquish();
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // Layer of tile g, given the layer of the previous (lower) tile of this thread.
+    auto advance = [&](int g, int l) {
+        while (l + 1 < cp.n_layers && g >= cp.L[l + 1].tile0) ++l;
+        return l;
+    };
+
+    // Bounded wait until the store thread has released the staging buffers of this CTA's first `need` tiles.
+    auto wait_released = [&](int need) {
+        unsigned long long t0 = 0;
+        uint32_t spins = 0;
+        while (*released < need) {
+            __nanosleep(32);
+            if ((++spins & 0x3f) == 0) {
+                if (*abort_flag) return false;
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+            }
+        }
+        __threadfence_block();
+        return true;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int e = 0;
+            bool ok = true;
+            const uint32_t lead_full0 = mapa_shared(full_bar(0), 0);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            int l = -1;
+            int it = 0;               // tiles of this CTA before the current one
+            int cut = 0, it0 = 0;     // how the staging region is cut (sub-tiles per buffer) and since which tile
+            for (int g = pair; ok && g < cp.total_tiles; g += npairs, ++it) {
+                const int nl = advance(g, l < 0 ? 0 : l);
+                const bool switched = nl != l;
+                l = nl;
+                const ChainLayer& L = cp.L[l];
+                if (switched) {
+                    tma_prefetch_desc(&L.tmap_a);
+                    tma_prefetch_desc(&L.tmap_b);
+                    if (L.nsub != cut) { cut = L.nsub; e = 0; it0 = it; }
+                }
+                const int t = g - L.tile0;
+                const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(t), L.div_ntiles));
+                const int n0 = (t - m_tile * L.n_tiles) * L.BN;
+                const int m0 = (2 * m_tile + static_cast<int>(rank)) * BM;
+                const uint32_t b_half_bytes = static_cast<uint32_t>(L.BN / 2) * BK * 2;
+                const uint32_t tx_bytes = A_STAGE_BYTES + b_half_bytes;
+                const uint32_t epi_bytes = static_cast<uint32_t>(L.nsub) * SUB_BYTES;
+                if (L.has_res) {
+                    // staging buffer e: free once the tile that used it last (nepi tiles ago) has been stored; after a
+                    // change of the cut, once every earlier tile has been
+                    if (!wait_released(max(it0, it - L.nepi + 1))) {
+                        atomicExch(cp.status, STATUS_WAIT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    if (L.res_layer >= 0) {
+                        const ChainLayer& R = cp.L[L.res_layer];
+                        if (!chain_wait_flag(cp.flags + R.flag0 + m_tile, R.done_count, abort_flag)) {
+                            atomicExch(cp.status, STATUS_WAIT_CHAIN);
+                            ok = false;
+                            break;
+                        }
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    }
+                    const CUtensorMap* rmap = L.res_layer >= 0 ? &cp.L[L.res_layer].tmap_y : &cp.ext_res[L.res_ext];
+                    const int nsub = min(L.nsub, (L.K - n0 + 63) >> 6);
+                    mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(nsub) * SUB_BYTES);
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                    rmap, res_full_bar(e), n0 + sub * 64, m0);
+                }
+                if (++e == L.nepi) e = 0;
+
+                const int ml = m0 < L.M ? m0 : m0 - BM;     // a peer without rows loads the leader's (results dropped)
+                const int PQ = L.P * L.Q;
+                int img = 0, pp = 0, h0 = 0, w0 = 0;
+                {
+                    img = static_cast<int>(fastdiv(static_cast<uint32_t>(ml), L.div_pq));
+                    const int rem = ml - img * PQ;
+                    pp = static_cast<int>(fastdiv(static_cast<uint32_t>(rem), L.div_q));
+                    const int qq = rem - pp * L.Q;
+                    h0 = pp * L.sh - L.ph;
+                    w0 = qq * L.sw - L.pw;
+                }
+                const int b_row0 = n0 + static_cast<int>(rank) * (L.BN / 2);
+                int tap = 0, cc = 0, r = 0, s = 0;
+                for (int kb = 0; kb < L.kblocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        atomicExch(cp.status, STATUS_WAIT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * stage_bytes;
+                    const uint32_t bar = lead_full0 + 8u * static_cast<uint32_t>(stage);
+                    mbar_expect_tx_cluster(bar, tx_bytes);
+                    tma_pair_load_3d(a_dst + A_STAGE_BYTES, &L.tmap_b, bar, cc * BK, tap, b_row0);    // weights: no dependency
+                    if (kb == 0 && L.in_layer >= 0) {
+                        // input pixels of this CTA's rows [ml, last]: from the first needed input row of the first image to
+                        // the last needed input row of the last image, as rows of the producing layer's output
+                        const ChainLayer& I = cp.L[L.in_layer];
+                        const int last = min(ml + BM, L.M) - 1;
+                        const int img1 = static_cast<int>(fastdiv(static_cast<uint32_t>(last), L.div_pq));
+                        const int pp1 = static_cast<int>(fastdiv(static_cast<uint32_t>(last - img1 * PQ), L.div_q));
+                        const int HW = L.H * L.W;
+                        const int lo = img * HW + max(0, pp * L.sh - L.ph) * L.W;
+                        const int hi = img1 * HW + min(L.H - 1, pp1 * L.sh - L.ph + L.rspan) * L.W + L.W - 1;
+                        bool seen = true;
+                        for (int f = lo >> 8; seen && f <= (hi >> 8); ++f)
+                            seen = chain_wait_flag(cp.flags + I.flag0 + f, I.done_count, abort_flag);
+                        if (!seen) {
+                            atomicExch(cp.status, STATUS_WAIT_CHAIN);
+                            ok = false;
+                            break;
+                        }
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    }
+                    if (L.im2col)
+                        tma_pair_load_im2col_4d(a_dst, &L.tmap_a, bar, cc * BK, w0, h0, img,
+                                                static_cast<uint16_t>(s * L.dw), static_cast<uint16_t>(r * L.dh));
+                    else
+                        tma_pair_load_2d(a_dst, &L.tmap_a, bar, cc * BK, ml);
+                    if (++cc == L.cchunks) {
+                        cc = 0;
+                        ++tap;
+                        if (++s == L.S) { s = 0; ++r; }
+                    }
+                    if (++stage == cp.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (ok) {
+                for (int i = 0; i < cp.stages; ++i) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) break;
+                    if (++stage == cp.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0 && elect_one()) {
+            const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
+            auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
+            const uint32_t stage_step = stage_bytes >> 4;
+            const uint32_t a_lo0 = lo_of(smem_base);
+            const uint32_t peer_empty0 = mapa_shared(empty_bar(0), 1);
+            const uint32_t peer_tfull0 = mapa_shared(tfull_bar(0), 1);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t st_lo = a_lo0;
+            uint32_t acc_phase = 0;
+            int acc = -1;
+            bool failed = false;
+            uint32_t st_ready = 0;
+            int l = 0;
+            for (int g = pair; g < cp.total_tiles; g += npairs) {
+                l = advance(g, l);
+                const int kblocks = cp.L[l].kblocks;
+                const uint32_t idesc = umma_idesc_f16_f32(2 * BM, cp.L[l].BN);
+                if (++acc == NACC) acc = 0;
+                failed |= !mbar_wait(tempty_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag);
+                acc_phase ^= 1u << acc;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * ACC_STRIDE;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!st_ready) failed |= !mbar_wait(full_bar(stage), phase, abort_flag);
+                    tc_fence_after();
+                    {
+                        const bool wrap = stage + 1 == cp.stages;
+                        st_ready = mbar_test(full_bar(wrap ? 0 : stage + 1), wrap ? phase ^ 1u : phase);
+                    }
+                    umma_pair_f16_kblock(d_tmem, st_lo, hi128, st_lo + (A_STAGE_BYTES >> 4), hi128, idesc,
+                                         static_cast<uint32_t>(kb != 0));
+                    umma_pair_commit(empty_bar(stage));
+                    umma_pair_commit(peer_empty0 + 8u * static_cast<uint32_t>(stage));
+                    st_lo += stage_step;
+                    if (++stage == cp.stages) { stage = 0; phase ^= 1u; st_lo = a_lo0; }
+                }
+                umma_pair_commit(tfull_bar(acc));
+                umma_pair_commit(peer_tfull0 + 8u * static_cast<uint32_t>(acc));
+            }
+            if (failed) atomicExch(cp.status, STATUS_WAIT_MMA);
+        }
+        __syncwarp();
+    } else if (warp < STORE_WARP) {
+        // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const int lane_group = warp & 3;
+        const int group = (warp - 2) >> 2;
+        const int row = lane_group * 32 + lane;
+        const uint32_t row_xor = static_cast<uint32_t>(row & 7);
+        const uint32_t stage0 = epi_base + static_cast<uint32_t>(row) * 128u;
+        float* bias_f = reinterpret_cast<float*>(smem_raw + bias_off);
+        const uint32_t lead_tempty0 = mapa_shared(tempty_bar(0), 0);
+        uint32_t acc_phase = 0, r_phase = 0, sync_phase = 0;
+        int e = 0, acc = -1;
+        bool ok = true;
+        int l = -1;
+        int it = 0, cut = 0, it0 = 0;
+        // All epilogue warps meet (a bounded wait on an mbarrier, not bar.sync: a warp that has given up never arrives).
+        auto epi_sync = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_sync_bar);
+            const bool met = mbar_wait<EPI_BACKOFF_NS>(epi_sync_bar, sync_phase, abort_flag);
+            sync_phase ^= 1u;
+            return met;
+        };
+        ConvParams ep;       // the epilogue code reads the activation code and the scale pointer from here
+        ep.act = 0;
+        ep.scale = nullptr;
+        int variant = 0;
+        for (int g = pair; ok && g < cp.total_tiles; g += npairs, ++it) {
+            const int nl = advance(g, l < 0 ? 0 : l);
+            const bool switched = nl != l;
+            l = nl;
+            const ChainLayer& L = cp.L[l];
+            if (switched) {
+                // every epilogue warp is past the previous layer's last tile before its bias copy is replaced
+                ok = epi_sync();
+                for (int i = threadIdx.x - 64; i < L.bias_elems; i += EPI_WARPS * 32)
+                    bias_f[i] = (L.bias != nullptr && i < L.K) ? __half2float(L.bias[i]) : 0.f;
+                ok = epi_sync() && ok;
+                ep.act = L.act;
+                ep.scale = L.scale;
+                const int act_t = (L.act == 0 || L.act == 1 || L.act == 3 || L.act == 5) ? L.act : 2;
+                variant = act_t * 2 + (L.has_res ? 1 : 0);
+                if (L.nsub != cut) { cut = L.nsub; e = 0; it0 = it; }
+            }
+            const int t = g - L.tile0;
+            const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(t), L.div_ntiles));
+            const int n0 = (t - m_tile * L.n_tiles) * L.BN;
+            const uint32_t epi_bytes = static_cast<uint32_t>(L.nsub) * SUB_BYTES;
+            if (++acc == NACC) acc = 0;
+            bool got_buf = ok;
+            if (got_buf) {
+                if (L.has_res) {
+                    got_buf = mbar_wait<EPI_BACKOFF_NS>(res_full_bar(e), (r_phase >> e) & 1u, abort_flag);
+                    r_phase ^= 1u << e;
+                } else {
+                    got_buf = wait_released(max(it0, it - L.nepi + 1));
+                }
+            }
+            if (!got_buf || !mbar_wait<EPI_BACKOFF_NS>(tfull_bar(acc), (acc_phase >> acc) & 1u, abort_flag)) {
+                if (lane == 0) atomicExch(cp.status, STATUS_WAIT_EPILOGUE);
+                ok = false;
+                break;
+            }
+            acc_phase ^= 1u << acc;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc) * ACC_STRIDE;
+            const uint32_t stage_row0 = stage0 + static_cast<uint32_t>(e) * epi_bytes;
+            const int ncols = min(L.BN, L.K - n0);
+            // epilogue_rows lays a tile's 64-channel sub-tiles SUB_BYTES apart, as this layer's staging buffers are
+            switch (variant) {
+                case 0: epilogue_rows<0, false>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 1: epilogue_rows<0, true>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 2: epilogue_rows<1, false>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 3: epilogue_rows<1, true>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 4: epilogue_rows<2, false>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 5: epilogue_rows<2, true>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 6: epilogue_rows<3, false>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 7: epilogue_rows<3, true>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                case 10: epilogue_rows<5, false>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+                default: epilogue_rows<5, true>(ep, t_row, stage_row0, row_xor, bias_base, n0, ncols, group); break;
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(lead_tempty0 + 8u * static_cast<uint32_t>(acc));
+                mbar_arrive(epi_done_bar(e));
+            }
+            if (++e == L.nepi) e = 0;
+        }
+    } else {
+        // ------------------------------------------------------------------ store warp (both CTAs)
+        if (elect_one()) {
+            uint32_t d_phase = 0;
+            int e = 0;
+            int n_released = 0;
+            int cut = 0;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            bool ok = true;
+            int l = -1;
+            for (int g = pair; ok && g < cp.total_tiles; g += npairs) {
+                const int nl = advance(g, l < 0 ? 0 : l);
+                if (nl != l) {
+                    l = nl;
+                    if (cp.L[l].nsub != cut) { cut = cp.L[l].nsub; e = 0; }
+                    tma_prefetch_desc(&cp.L[l].tmap_y);
+                }
+                const ChainLayer& L = cp.L[l];
+                const int t = g - L.tile0;
+                const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(t), L.div_ntiles));
+                const int n0 = (t - m_tile * L.n_tiles) * L.BN;
+                const int m0 = (2 * m_tile + static_cast<int>(rank)) * BM;
+                const uint32_t epi_bytes = static_cast<uint32_t>(L.nsub) * SUB_BYTES;
+                if (!mbar_wait<EPI_BACKOFF_NS>(epi_done_bar(e), (d_phase >> e) & 1u, abort_flag)) {
+                    atomicExch(cp.status, STATUS_WAIT_STORE);
+                    ok = false;
+                    break;
+                }
+                d_phase ^= 1u << e;
+                if (m0 < L.M) {
+                    const int nsub = min(L.nsub, (L.K - n0 + 63) >> 6);
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_store_2d(&L.tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
+                                     n0 + sub * 64, m0);
+                    tma_store_commit();
+                    tma_store_wait_read();
+                }
+                __threadfence_block();
+                *released = ++n_released;      // the staging buffer may be refilled
+                // this CTA's part of the tile is in global memory: count it for the layers that read it
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async;" ::: "memory");
+                asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(cp.flags + L.flag0 + m_tile) : "memory");
+                if (++e == L.nepi) e = 0;
+            }
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_pair_dealloc(tmem_base, NACC * ACC_STRIDE);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- host side
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1612,7 +2073,8 @@ int conv_host_init() {
             cudaSuccess ||
         cudaFuncSetAttribute(conv_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(conv_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+        cudaFuncSetAttribute(conv_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
         return FVM_ERR_SETUP;
     return FVM_OK;
 }
@@ -2209,6 +2671,207 @@ static int launch_conv_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap
     else conv_tcgen05_kernel<<<grid, CONV_THREADS, smem, stream>>>(tmap_a, tmap_b, tmap_r, tmap_y, p);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? FVM_OK : FVM_ERR_LAUNCH;
+}
+
+// ------------------------------------------------------------------------------------------------ chain launch
+static bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb) {
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+    return a0 < b0 + nb && b0 < a0 + na;
+}
+
+// A run of convolutions as one launch of conv_chain_kernel. Layer i may read (as input or residual) the output of an
+// earlier layer of the chain, which is recognised by its pointer, shape and row stride; anything else it reads must be
+// complete before the launch (stream order). Refused (FVM_ERR_ARG, nothing launched): layers the pair kernel does not
+// take (fewer than 24 input channels, per-image weights), more than CHAIN_MAX_EXT_RES residuals that no layer of the
+// chain produces, buffers that alias one another in a way the dependency tracking cannot express, more than
+// CHAIN_MAX_LAYERS layers.
+int conv_chain_launch(const fvm_chain_layer* layers, int n, cudaStream_t stream) {
+    DeviceState* st = device_state();
+    if (!st) return FVM_ERR_SETUP;
+    if (!layers || n <= 0 || n > CHAIN_MAX_LAYERS) return FVM_ERR_ARG;
+    if (st->pair_clusters <= 0 || !st->chain_flags) return FVM_ERR_ARG;
+    static ChainParams cp;      // 28 KB: kept off the stack; guarded by the mutex below
+    static std::mutex cp_mutex;
+    std::lock_guard<std::mutex> lock(cp_mutex);
+    memset(&cp, 0, sizeof(cp));
+    cp.n_layers = n;
+    int max_bn = 0, max_bias = 0, tiles = 0, flags = 0, n_ext = 0;
+    size_t xbytes[CHAIN_MAX_LAYERS], ybytes[CHAIN_MAX_LAYERS];
+    for (int i = 0; i < n; ++i) {
+        const fvm_chain_layer& a = layers[i];
+        ChainLayer& L = cp.L[i];
+        if (!a.x || !a.w || !a.y) return FVM_ERR_ARG;
+        if (a.N <= 0 || a.H <= 0 || a.W <= 0 || a.C < 24 || a.K <= 0 || a.R <= 0 || a.S <= 0) return FVM_ERR_ARG;
+        if ((a.C & 7) || (a.K & 7) || (a.ldx & 7) || (a.ldy & 7) || (a.res && (a.ldr & 7))) return FVM_ERR_ARG;
+        if (a.sh <= 0 || a.sw <= 0 || a.dh <= 0 || a.dw <= 0 || a.ph < 0 || a.pw < 0) return FVM_ERR_ARG;
+        if (a.ldx < a.C || a.ldy < a.K || (a.res && a.ldr < a.K)) return FVM_ERR_ARG;
+        if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (reinterpret_cast<uintptr_t>(a.w) & 15) ||
+            (reinterpret_cast<uintptr_t>(a.y) & 15) || (reinterpret_cast<uintptr_t>(a.res) & 15) ||
+            (reinterpret_cast<uintptr_t>(a.bias) & 15) || (reinterpret_cast<uintptr_t>(a.scale) & 15))
+            return FVM_ERR_ARG;
+        if (a.act < 0 || a.act > 6) return FVM_ERR_ARG;
+        const int P = (a.H + 2 * a.ph - a.dh * (a.R - 1) - 1) / a.sh + 1;
+        const int Q = (a.W + 2 * a.pw - a.dw * (a.S - 1) - 1) / a.sw + 1;
+        if (P <= 0 || Q <= 0) return FVM_ERR_ARG;
+        const long long M_ll = static_cast<long long>(a.N) * P * Q;
+        if (M_ll > 0x3fffff00ll || static_cast<long long>(a.N) * a.H * a.W > 0x3fffff00ll) return FVM_ERR_ARG;
+        L.M = static_cast<int>(M_ll);
+        L.K = a.K; L.P = P; L.Q = Q; L.H = a.H; L.W = a.W; L.S = a.S;
+        L.sh = a.sh; L.sw = a.sw; L.ph = a.ph; L.pw = a.pw; L.dh = a.dh; L.dw = a.dw;
+        L.rspan = (a.R - 1) * a.dh;
+        L.cchunks = (a.C + BK - 1) / BK;
+        L.kblocks = a.R * a.S * L.cchunks;
+        int bn = a.tile_n & 0xffff;
+        // 128-wide tiles: one cut of the staging region for all layers, three buffers of it, many tiles per layer
+        if (bn == 0) bn = a.K <= 128 ? (a.K + 31) / 32 * 32 : 128;
+        if (bn < 32 || bn > 256 || (bn & 31)) return FVM_ERR_ARG;
+        L.BN = bn;
+        L.n_tiles = (a.K + bn - 1) / bn;
+        if (L.n_tiles > 1 && (bn & 63)) return FVM_ERR_ARG;
+        L.m_tiles = (L.M + 2 * BM - 1) / (2 * BM);
+        L.nsub = (bn + 63) / 64;
+        L.im2col = !(a.R == 1 && a.S == 1 && a.sh == 1 && a.sw == 1 && a.ph == 0 && a.pw == 0);
+        L.act = a.act;
+        L.has_res = a.res != nullptr;
+        L.bias = static_cast<const __half*>(a.bias);
+        L.scale = a.scale;
+        L.bias_elems = L.n_tiles * bn;
+        L.div_ntiles = fastdiv_init(static_cast<uint32_t>(L.n_tiles));
+        L.div_pq = fastdiv_init(static_cast<uint32_t>(P) * Q);
+        L.div_q = fastdiv_init(static_cast<uint32_t>(Q));
+        L.done_count = 2 * L.n_tiles;
+        L.tile0 = tiles;
+        L.flag0 = flags;
+        const long long lt = static_cast<long long>(L.m_tiles) * L.n_tiles;
+        if (tiles + lt > 0x3fffffffll) return FVM_ERR_ARG;
+        tiles += static_cast<int>(lt);
+        flags += L.m_tiles;
+        if (bn > max_bn) max_bn = bn;
+        if (L.bias_elems > max_bias) max_bias = L.bias_elems;
+        xbytes[i] = (static_cast<size_t>(a.N) * a.H * a.W - 1) * a.ldx * 2 + static_cast<size_t>(a.C) * 2;
+        ybytes[i] = (static_cast<size_t>(L.M) - 1) * a.ldy * 2 + static_cast<size_t>(a.K) * 2;
+        // producers: the latest earlier layer whose output is exactly this layer's input / residual
+        L.in_layer = L.res_layer = -1;
+        for (int j = i - 1; j >= 0; --j) {
+            const fvm_chain_layer& b = layers[j];
+            const ChainLayer& J = cp.L[j];
+            if (L.in_layer < 0 && b.y == a.x) {
+                if (b.ldy != a.ldx || b.K != a.C || J.P != a.H || J.Q != a.W || b.N != a.N) return FVM_ERR_ARG;
+                L.in_layer = j;
+            }
+            if (a.res && L.res_layer < 0 && b.y == a.res) {
+                if (b.ldy != a.ldr || b.K != a.K || J.M != L.M) return FVM_ERR_ARG;
+                L.res_layer = j;
+            }
+        }
+        if (a.res && L.res_layer < 0) {
+            // a residual from outside the chain (complete before the launch): its own map
+            if (n_ext == CHAIN_MAX_EXT_RES) return FVM_ERR_ARG;
+            const unsigned long long dims[2] = {static_cast<unsigned long long>(a.K), static_cast<unsigned long long>(L.M)};
+            const unsigned long long strides[1] = {static_cast<unsigned long long>(a.ldr) * 2};
+            const unsigned box[2] = {64, BM};
+            if (encode_tiled_f16(&cp.ext_res[n_ext], a.res, 2, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+            L.res_ext = n_ext++;
+        }
+        for (int j = 0; j < i; ++j) {
+            const fvm_chain_layer& b = layers[j];
+            // an input that overlaps an earlier output without being that output; an output that overlaps anything an
+            // earlier layer reads or writes, or this layer's own operands
+            if (j != L.in_layer && ranges_overlap(a.x, xbytes[i], b.y, ybytes[j])) return FVM_ERR_ARG;
+            if (a.res && j != L.res_layer && ranges_overlap(a.res, ybytes[i], b.y, ybytes[j])) return FVM_ERR_ARG;
+            if (ranges_overlap(a.y, ybytes[i], b.y, ybytes[j]) || ranges_overlap(a.y, ybytes[i], b.x, xbytes[j]) ||
+                (b.res && ranges_overlap(a.y, ybytes[i], b.res, ybytes[j])))
+                return FVM_ERR_ARG;
+        }
+        if (ranges_overlap(a.y, ybytes[i], a.x, xbytes[i])) return FVM_ERR_ARG;
+    }
+    if (flags > st->chain_flag_count) return FVM_ERR_ARG;
+    cp.total_tiles = tiles;
+    cp.flags = st->chain_flags;
+    cp.status = st->status_dev;
+    // shared memory: slots sized for the widest tile of the chain; three staging buffers of the widest tile if four
+    // slots still fit beside them, else two, else one
+    cp.stage_bytes = A_STAGE_BYTES + static_cast<uint32_t>(max_bn / 2) * BK * 2;
+    const uint32_t max_epi = static_cast<uint32_t>((max_bn + 63) / 64) * SUB_BYTES;
+    const uint32_t bias_bytes = (static_cast<uint32_t>(max_bias) * 4 + 15u) & ~15u;
+    if (bias_bytes > MAX_BIAS_BYTES) return FVM_ERR_ARG;
+    const uint32_t fixed = 1024 + 8 * NUM_BARRIERS + MISC_BYTES + bias_bytes;
+    const uint32_t total = 227 * 1024;
+    int nbuf = 3;
+    while (nbuf > 1 && fixed + static_cast<uint32_t>(nbuf) * max_epi + 4 * cp.stage_bytes > total) --nbuf;
+    if (fixed + static_cast<uint32_t>(nbuf) * max_epi + 2 * cp.stage_bytes > total) return FVM_ERR_ARG;
+    cp.epi_region_bytes = static_cast<uint32_t>(nbuf) * max_epi;
+    cp.stages = static_cast<int>((total - fixed - cp.epi_region_bytes) / cp.stage_bytes);
+    if (cp.stages > MAX_STAGES) cp.stages = MAX_STAGES;
+    const size_t smem = fixed + static_cast<size_t>(cp.stages) * cp.stage_bytes + cp.epi_region_bytes;
+    for (int i = 0; i < n; ++i) {
+        const fvm_chain_layer& a = layers[i];
+        ChainLayer& L = cp.L[i];
+        const uint32_t epi_bytes = static_cast<uint32_t>(L.nsub) * SUB_BYTES;
+        L.nepi = static_cast<int>(cp.epi_region_bytes / epi_bytes);
+        if (L.nepi > MAX_EPI) L.nepi = MAX_EPI;
+        {   // output [M, K], row stride ldy: 64-channel x 128-row boxes (also read as the residual of later layers)
+            const unsigned long long dims[2] = {static_cast<unsigned long long>(a.K), static_cast<unsigned long long>(L.M)};
+            const unsigned long long strides[1] = {static_cast<unsigned long long>(a.ldy) * 2};
+            const unsigned box[2] = {64, BM};
+            if (encode_tiled_f16(&L.tmap_y, a.y, 2, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        }
+        {   // weights [K][R*S][C]: this CTA's half of an n-tile per load
+            const unsigned long long dims[3] = {static_cast<unsigned long long>(a.C), static_cast<unsigned long long>(a.R) * a.S,
+                                                static_cast<unsigned long long>(a.K)};
+            const unsigned long long strides[2] = {static_cast<unsigned long long>(a.C) * 2,
+                                                   static_cast<unsigned long long>(a.R) * a.S * a.C * 2};
+            const unsigned box[3] = {BK, 1, static_cast<unsigned>(L.BN / 2)};
+            if (encode_tiled_f16(&L.tmap_b, a.w, 3, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        }
+        if (!L.im2col) {
+            const unsigned long long dims[2] = {static_cast<unsigned long long>(a.C), static_cast<unsigned long long>(L.M)};
+            const unsigned long long strides[1] = {static_cast<unsigned long long>(a.ldx) * 2};
+            const unsigned box[2] = {BK, BM};
+            if (encode_tiled_f16(&L.tmap_a, a.x, 2, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        } else {
+            const int up_w = a.pw - (a.S - 1) * a.dw, up_h = a.ph - (a.R - 1) * a.dh;
+            if (a.pw > 127 || a.ph > 127 || up_w < -128 || up_h < -128 || (a.S - 1) * a.dw > 255 || (a.R - 1) * a.dh > 255)
+                return FVM_ERR_ARG;
+            cuuint64_t dims[4] = {static_cast<cuuint64_t>(a.C), static_cast<cuuint64_t>(a.W), static_cast<cuuint64_t>(a.H),
+                                  static_cast<cuuint64_t>(a.N)};
+            cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.ldx) * 2, static_cast<cuuint64_t>(a.W) * a.ldx * 2,
+                                     static_cast<cuuint64_t>(a.H) * a.W * a.ldx * 2};
+            int lower[2] = {-a.pw, -a.ph};
+            int upper[2] = {up_w, up_h};
+            cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(a.sw), static_cast<cuuint32_t>(a.sh), 1};
+            CUresult r = g_encode_im2col(&L.tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(a.x), dims, strides,
+                                         lower, upper, BK, BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return FVM_ERR_TMAP;
+            const unsigned long long bytes = static_cast<unsigned long long>(a.N) * a.H * a.W * a.ldx * 2;
+            if (g_driver_version <= 13010 && bytes < 131072ull)      // see conv2d_launch
+                reinterpret_cast<uint64_t*>(&L.tmap_a)[1] &= ~(1ull << 21);
+        }
+    }
+    if (cudaMemsetAsync(st->chain_flags, 0, static_cast<size_t>(flags) * sizeof(int), stream) != cudaSuccess)
+        return FVM_ERR_LAUNCH;
+    const int pairs = tiles < st->pair_clusters ? tiles : st->pair_clusters;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(CONV_THREADS);
+    cfg.dynamicSmemBytes = smem < 120 * 1024 ? 120 * 1024 : smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, conv_chain_kernel, cp) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return FVM_ERR_LAUNCH;
+    }
+    count_launch();
+    return FVM_OK;
 }
 
 }  // namespace fvm

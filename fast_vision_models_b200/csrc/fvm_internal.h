@@ -17,6 +17,10 @@ struct DeviceState {
     float* sk_part = nullptr;
     int* sk_flags = nullptr;
     size_t sk_floats = 0;
+    // completion counters of the layer-chain kernel (one per layer and 256-row tile), zeroed before every chain launch;
+    // shared by every stream of the device: chain launches on different streams must not overlap in time
+    int* chain_flags = nullptr;
+    int chain_flag_count = 0;
     int pair_clusters = 0;        // CTA pairs (clusters of two) the device runs at once; 0: pair kernel unavailable
     bool ready = false;
 };
@@ -37,5 +41,6 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
                   cudaStream_t stream, int w_per_image = 0);
+int conv_chain_launch(const fvm_chain_layer* layers, int n, cudaStream_t stream);
 
 }  // namespace fvm

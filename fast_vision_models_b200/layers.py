@@ -175,8 +175,8 @@ class FusedConv(nn.Module):
         if cached is not None:
             self._tiles[key] = cached
             return cached
-        if torch.cuda.is_current_stream_capturing():
-            return 0
+        if torch.cuda.is_current_stream_capturing() or ops.chain_active():
+            return 0          # no timing while a graph is captured or while layers are recorded for a chain launch
         K = self.w.shape[0]
         # tile code: low 16 bits = output-channel tile (0 = library's choice), bits 16.. = 128-pixel sub-tiles per tile
         widths = [0] + [c for c in (64, 128, 256) if c < K or (c == 256 and K > 256)]

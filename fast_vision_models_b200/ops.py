@@ -10,6 +10,7 @@ library that is missing, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -85,7 +86,79 @@ def query(what: int) -> int:
 
 
 def _stream() -> int:
+    # every launch of this module asks for the stream first: convolutions recorded for a chain launch go out before
+    # anything else that could read their outputs
+    if _chain is not None and _chain.layers:
+        _chain.flush()
     return torch.cuda.current_stream().cuda_stream
+
+
+# ------------------------------------------------------------------------------------------------ layer chains
+CHAIN_MAX_LAYERS = 48
+CHAINS = os.environ.get("FVM_B200_CHAIN", "1") != "0"
+_CHAIN_BN = int(os.environ.get("FVM_B200_CHAIN_BN", "0"))
+
+
+class _Chain:
+    """Convolutions recorded between chain_begin() and chain_end(): launched together by fvm_conv_chain_f16 (one kernel
+    whose tiles follow the layers' data dependencies), or one by one where the library cannot express the run."""
+
+    def __init__(self):
+        self.layers = []      # (argument list of fvm_conv2d_f16, tile code, tensors kept alive)
+
+    def add(self, args, tile_n, keep) -> None:
+        self.layers.append((args, int(tile_n), keep))
+        if len(self.layers) == CHAIN_MAX_LAYERS:
+            self.flush()
+
+    def flush(self) -> None:
+        layers, self.layers = self.layers, []
+        if not layers:
+            return
+        L = lib()
+        stream = torch.cuda.current_stream().cuda_stream
+        if len(layers) > 1:
+            arr = (_lib.ChainLayer * len(layers))()
+            for c, (a, tile_n, _keep) in zip(arr, layers):
+                (c.x, c.w, c.bias, c.res, c.scale, c.y, c.N, c.H, c.W, c.C, c.K, c.R, c.S, c.ph, c.pw, c.sh, c.sw, c.dh,
+                 c.dw, c.ldx, c.ldy, c.ldr, c.act) = a
+                c.tile_n = (tile_n & 0xffff) if (tile_n >> 30) & 1 else 0     # a width that was chosen for CTA pairs
+                if _CHAIN_BN and c.K > 128:
+                    c.tile_n = 256 if (_CHAIN_BN == 256 and c.K == 256) else (_CHAIN_BN if _CHAIN_BN != 256 else 128)
+            rc = L.fvm_conv_chain_f16(arr, len(layers), stream)
+            if rc == 0:
+                return
+            if rc != 1:
+                _check(rc, "conv_chain_f16")
+        for a, tile_n, _keep in layers:        # not expressible as a chain (or a single layer): stream order
+            rc = L.fvm_conv2d_f16_tile(*a, tile_n, stream) if tile_n else L.fvm_conv2d_f16(*a, stream)
+            _check(rc, "conv2d_f16")
+
+
+_chain: Optional[_Chain] = None
+
+
+def chain_begin() -> bool:
+    """Starts recording: conv_fused_into calls with at least 24 input channels are collected instead of launched, until
+    chain_end() (or any other launch of this module, or 48 layers) sends them out as one chain launch. Outputs must not
+    be read by anything but this module before that. Returns False (and records nothing) when chains are switched off
+    (FVM_B200_CHAIN=0), the device cannot run CTA pairs, or a recording is already open."""
+    global _chain
+    if not CHAINS or _chain is not None or query(4) <= 0:
+        return False
+    _chain = _Chain()
+    return True
+
+
+def chain_end() -> None:
+    global _chain
+    c, _chain = _chain, None
+    if c is not None:
+        c.flush()
+
+
+def chain_active() -> bool:
+    return _chain is not None
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -178,9 +251,12 @@ def conv_fused_into(x, w, bias, res, padding, stride, act: int, out: torch.Tenso
         if scale.dtype != torch.float32 or not scale.is_cuda:
             raise FvmError("conv_fused: scale must be an fp32 CUDA tensor")
         scale = scale.contiguous()
-    L = lib()
     args = [x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(res), _ptr(scale), out.data_ptr(), N, H, W, C, K, R, S, ph, pw,
             sh, sw, dh, dw, ldx, ldy, ldr, int(act)]
+    if _chain is not None and pad_hi is None and C >= 24:
+        _chain.add(args, tile_n, (x, w, bias, res, scale, out))
+        return
+    L = lib()
     if pad_hi is not None:
         rc = L.fvm_conv2d_f16_pad(*args, int(tile_n), ph_hi, pw_hi, _stream())
     elif tile_n:

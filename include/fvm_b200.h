@@ -84,6 +84,30 @@ int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const vo
                         int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                         long long ldx, long long ldy, long long ldr, int act, int tile_n, void* stream);
 
+/* A run of dense convolutions as ONE launch -- no counterpart in the reference, which launches one kernel per layer
+ * (classification/fast/csrc/fused_conv.cu:231-306): the bottleneck blocks of a ResNet stage, say. Each entry is one
+ * fvm_conv2d_f16 call (same operands, same arithmetic, same bits as the CTA-pair kernel of fvm_conv2d_f16_tile); layer
+ * i may read, as input or residual, the output of an earlier entry (recognised by pointer, shape and row stride), and
+ * its tiles start as soon as the tiles that hold those pixels are complete, so consecutive layers overlap instead of
+ * paying a launch, a pipeline start and a partial last wave each. Everything else a layer reads must be complete
+ * before the call (stream order). Returns 1 with nothing launched when the chain cannot be expressed: more than 48
+ * layers, fewer than 24 input channels, more than 4 residuals that no entry produces, or buffers that alias one another
+ * (an output that overlaps any other operand of the chain; layers do not run in stream order). tile_n: output-channel tile
+ * (0 = choose). Chain launches on different streams of one device must not overlap in time (shared counters). */
+typedef struct fvm_chain_layer {
+    const void* x;
+    const void* w;
+    const void* bias;
+    const void* res;
+    const float* scale;
+    void* y;
+    int N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw;
+    long long ldx, ldy, ldr;
+    int act;
+    int tile_n;
+} fvm_chain_layer;
+int fvm_conv_chain_f16(const fvm_chain_layer* layers, int n_layers, void* stream);
+
 /* fvm_conv2d_f16_tile with separate bottom / right padding (ph_hi, pw_hi; negative = same as top / left). The host
  * uses it to run a stride-2 RGB stem (reference: the zero-padded 8-channel stem, fused.py:90-105) over column pairs:
  * the NHWC8 input viewed as [N, H, W/2, 16] with re-packed weights, which halves the rows the TMA unit gathers. */

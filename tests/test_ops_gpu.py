@@ -224,6 +224,121 @@ def test_conv_cta_pairs_are_refused_where_they_do_not_apply():
         ops.conv_fused(x, w, None, None, (1, 1), (1, 1), 0, tile_n=(1 << 30) | (2 << 16))      # with two sub-tiles
 
 
+def _resnet_stage(N, H, W, cin, mid, blocks, stride, seed):
+    """Weights and a runner for a ResNet bottleneck stage (torchvision layout: the stride sits on the 3x3 convolution
+    and on the 1x1 downsample of the first block). run() returns every layer's output, in launch order."""
+    x = cl(gen((N, cin, H, W), seed))
+    ws = []
+    c = cin
+    for b in range(blocks):
+        s_ = stride if b == 0 else 1
+        blk = {"c1": (cl(gen((mid, c, 1, 1), seed + 10 * b + 1, 0.05)), gen((mid,), seed + 10 * b + 2, 0.1).to(DEV)),
+               "c2": (cl(gen((mid, mid, 3, 3), seed + 10 * b + 3, 0.03)), gen((mid,), seed + 10 * b + 4, 0.1).to(DEV)),
+               "c3": (cl(gen((4 * mid, mid, 1, 1), seed + 10 * b + 5, 0.05)), gen((4 * mid,), seed + 10 * b + 6, 0.1).to(DEV)),
+               "stride": s_}
+        if b == 0:
+            blk["ds"] = (cl(gen((4 * mid, c, 1, 1), seed + 7, 0.05)), gen((4 * mid,), seed + 8, 0.1).to(DEV))
+        ws.append(blk)
+        c = 4 * mid
+
+    def run():
+        outs = []
+        y = x
+        for blk in ws:
+            s_ = blk["stride"]
+            idn = y
+            if "ds" in blk:
+                idn = ops.conv_fused(y, blk["ds"][0], blk["ds"][1], None, (0, 0), (s_, s_), 0)
+                outs.append(idn)
+            a = ops.conv_fused(y, blk["c1"][0], blk["c1"][1], None, (0, 0), (1, 1), 1)
+            b_ = ops.conv_fused(a, blk["c2"][0], blk["c2"][1], None, (1, 1), (s_, s_), 1)
+            y = ops.conv_fused(b_, blk["c3"][0], blk["c3"][1], idn, (0, 0), (1, 1), 1)
+            outs += [a, b_, y]
+        return outs
+    return run
+
+
+CHAIN_CASES = [
+    # N, H, W, input channels, bottleneck width, blocks, stride of the first block
+    (64, 28, 28, 512, 256, 3, 2),      # ResNet-50 stage 3 (first three blocks): 28x28 -> 14x14
+    (64, 14, 14, 1024, 512, 3, 2),     # stage 4: 14x14 -> 7x7, 2048 output channels
+    (64, 56, 56, 256, 128, 2, 2),      # stage 2: 56x56 -> 28x28
+    (5, 20, 12, 96, 40, 2, 1),         # ragged rows and channels, no stride
+    (3, 9, 9, 64, 32, 17, 1),          # 52 layers: sent out as two chain launches
+]
+
+
+@pytest.mark.parametrize("case", CHAIN_CASES)
+def test_conv_chain_matches_layer_by_layer_launches(case):
+    # the same convolutions recorded and sent out as chain launches (tiles ordered by their data dependencies inside
+    # one kernel) against one launch per layer in stream order: same bits for every layer's output, twice in a row
+    # (the completion counters are zeroed before every chain launch)
+    ops.init(DEV)
+    if ops.query(4) <= 0:
+        pytest.skip("this device cannot launch CTA pairs")
+    run = _resnet_stage(*case, seed=40)
+    ref = run()
+    assert ops.last_status() == 0
+    for _ in range(2):
+        before = ops.launches()
+        assert ops.chain_begin()
+        try:
+            got = run()
+        finally:
+            ops.chain_end()
+        assert ops.last_status() == 0
+        n_launch = ops.launches() - before
+        assert n_launch == (len(ref) + ops.CHAIN_MAX_LAYERS - 1) // ops.CHAIN_MAX_LAYERS, n_launch
+        for i, (a, b) in enumerate(zip(got, ref)):
+            assert torch.equal(a, b), f"layer {i}: {(a.float() - b.float()).abs().max().item()}"
+
+
+def test_conv_chain_against_the_oracle():
+    ops.init(DEV)
+    if ops.query(4) <= 0:
+        pytest.skip("this device cannot launch CTA pairs")
+    N, C, H, W = 2, 64, 12, 10
+    x, w1, b1 = gen((N, C, H, W), 51), gen((96, C, 3, 3), 52, 0.04), gen((96,), 53, 0.1)
+    w2, b2 = gen((64, 96, 1, 1), 54, 0.08), gen((64,), 55, 0.1)
+    assert ops.chain_begin()
+    try:
+        y1 = ops.conv_fused(cl(x), cl(w1), b1.to(DEV), None, (1, 1), (1, 1), 1)
+        y2 = ops.conv_fused(y1, cl(w2), b2.to(DEV), cl(x), (0, 0), (1, 1), 3)       # residual from outside the chain
+        y3 = ops.conv_fused(y2, cl(w2[:, :64]), b2.to(DEV), y2, (0, 0), (1, 1), 1)   # residual from inside
+    finally:
+        ops.chain_end()
+    assert ops.last_status() == 0
+    r1 = R.conv_fused_ref(x, w1, b1, None, (1, 1), (1, 1), 1)
+    close(y1, r1)
+    r2 = R.conv_fused_ref(y1.float().cpu(), w2, b2, x, (0, 0), (1, 1), 3)
+    close(y2, r2)
+    r3 = R.conv_fused_ref(y2.float().cpu(), w2[:, :64], b2, y2.float().cpu(), (0, 0), (1, 1), 1)
+    close(y3, r3)
+
+
+def test_conv_chain_with_aliased_buffers_falls_back_to_stream_order():
+    # the second layer writes into the first layer's input buffer: not expressible as a chain, so the recorded layers
+    # go out one by one and the result is that of stream order
+    ops.init(DEV)
+    if ops.query(4) <= 0:
+        pytest.skip("this device cannot launch CTA pairs")
+    x = cl(gen((4, 64, 16, 16), 61))
+    w1, w2 = cl(gen((64, 64, 1, 1), 62, 0.1)), cl(gen((64, 64, 1, 1), 63, 0.1))
+    y1_ref = ops.conv_fused(x, w1, None, None, (0, 0), (1, 1), 1)
+    y2_ref = ops.conv_fused(y1_ref, w2, None, None, (0, 0), (1, 1), 1)
+    xin = x.clone(memory_format=torch.channels_last)
+    before = ops.launches()
+    assert ops.chain_begin()
+    try:
+        y1 = ops.conv_fused(xin, w1, None, None, (0, 0), (1, 1), 1)
+        ops.conv_fused_into(y1, w2, None, None, (0, 0), (1, 1), 1, xin)
+    finally:
+        ops.chain_end()
+    assert ops.last_status() == 0
+    assert ops.launches() - before == 2
+    assert torch.equal(y1, y1_ref) and torch.equal(xin, y2_ref)
+
+
 HALO_CASES = [
     # N, H, W, C, K, dil, res, tile, weight-resident (0 choose / 1 on / 2 off)
     (2, 16, 8, 64, 64, 1, False, 0, 2),        # exactly one patch per image
