@@ -32,7 +32,11 @@ from .. import fold, ops
 from ..layers import GATE_IN_WEIGHTS, DepthwiseConv, FusedConv, LayerNormCL, SqueezeExcite, act_code
 from ..runtime import GraphRunner
 
-CHAIN_RESNET = os.environ.get("FVM_B200_CHAIN_RESNET", "1") != "0"
+# Bottleneck stages as chain launches (ops.chain_begin): measured on B200 at batch 64, one launch per layer is as fast
+# (stage 4 only: 1.127 against 1.129 ms per forward) or faster (from stage 3: 1.16 ms, from stage 2: 1.17-1.19 ms),
+# because a layer of these stages has about as many tiles as there are CTA pairs and the next layer's tiles wait for
+# them just as a next launch would. Off unless asked for.
+CHAIN_RESNET = os.environ.get("FVM_B200_CHAIN_RESNET", "0") == "1"
 
 
 # ------------------------------------------------------------------------------------------------ ResNet
@@ -63,9 +67,10 @@ class ResNetTrunk(nn.Module):
             self.stage_ends.append(len(blocks))
         self.blocks = nn.ModuleList(blocks)
         self.out_channels = self.blocks[-1]["convs"][-1].out_channels
-        # first block whose convolutions run as chain launches: the second stage (the first stage's 3x3 layers over 64
-        # channels are faster on staged input patches, a mode the chain kernel does not have)
-        self.chain_from = self.stage_ends[int(os.environ.get('FVM_B200_CHAIN_STAGE', '1')) - 1] if CHAIN_RESNET else len(blocks)
+        # first block whose convolutions run as chain launches (FVM_B200_CHAIN_STAGE = 2, 3 or 4: from that stage on; the
+        # first stage's 3x3 layers over 64 channels are faster on staged input patches, which the chain kernel lacks)
+        stage = min(4, max(2, int(os.environ.get("FVM_B200_CHAIN_STAGE", "2"))))
+        self.chain_from = self.stage_ends[stage - 2] if CHAIN_RESNET else len(blocks)
 
     def forward(self, x: torch.Tensor, want_stage3: bool = False):
         # fp32 / fp16 NCHW image batch (fewer than 8 channels), or an fp16 NHWC8 tensor (clf::input_nhwc8's output)

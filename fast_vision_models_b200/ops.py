@@ -96,7 +96,6 @@ def _stream() -> int:
 # ------------------------------------------------------------------------------------------------ layer chains
 CHAIN_MAX_LAYERS = 48
 CHAINS = os.environ.get("FVM_B200_CHAIN", "1") != "0"
-_CHAIN_BN = int(os.environ.get("FVM_B200_CHAIN_BN", "0"))
 
 
 class _Chain:
@@ -123,8 +122,6 @@ class _Chain:
                 (c.x, c.w, c.bias, c.res, c.scale, c.y, c.N, c.H, c.W, c.C, c.K, c.R, c.S, c.ph, c.pw, c.sh, c.sw, c.dh,
                  c.dw, c.ldx, c.ldy, c.ldr, c.act) = a
                 c.tile_n = (tile_n & 0xffff) if (tile_n >> 30) & 1 else 0     # a width that was chosen for CTA pairs
-                if _CHAIN_BN and c.K > 128:
-                    c.tile_n = 256 if (_CHAIN_BN == 256 and c.K == 256) else (_CHAIN_BN if _CHAIN_BN != 256 else 128)
             rc = L.fvm_conv_chain_f16(arr, len(layers), stream)
             if rc == 0:
                 return
