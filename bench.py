@@ -391,10 +391,12 @@ def main():
         pk = peaks()
         ms_step = med / steps
         roof = roofline_of(MODEL, BATCH, ms_step, pk)
-        roof["kernel"] = "whole forward graph; conv_tcgen05_kernel is the dominant kernel (about 96 % of the device time)"
-        roof["traffic"] = 2486.9e6 if (MODEL, BATCH) == ("resnet50", 64) else None
-        roof["traffic_source"] = ("ncu capture of an earlier build's forward (dram__bytes_read.sum + dram__bytes_write.sum "
-                                  "over its 59 launches, serialised, cold caches); not a property of this run")
+        roof["kernel"] = ("whole forward graph; the two convolution kernels carry 95 % of the device time "
+                          "(conv_pair_kernel 67 % over 43 launches, conv_tcgen05_kernel 29 % over 11)")
+        roof["traffic"] = 2486.0e6 if (MODEL, BATCH) == ("resnet50", 64) else None
+        roof["traffic_source"] = ("ncu capture of this forward (dram__bytes_read.sum + dram__bytes_write.sum over its 58 "
+                                  "launches, serialised, cold caches: profiles/resnet50_b64_forward_launches.md); "
+                                  "not measured in this run")
         line = {"metric": "ResNet-50 fp16 b64 images/s", "value": round(value, 1),
                 "value_min": round(images_per_window / (max(win_dev) / 1e3), 1),
                 "value_max": round(images_per_window / (min(win_dev) / 1e3), 1), "unit": "images/s", "n_gpus": world,

@@ -23,7 +23,7 @@
 //   per 64 channels and the nine taps are MMA operands that start at different rows of that patch.
 //   Stem mode (stride 2, 8-channel input stored as two column-parity planes per image row): the same idea without
 //   swizzle; one MMA covers two vertically adjacent taps.
-// No cluster launch and no multicast: every CTA issues its own loads.
+// conv_tcgen05_kernel and conv_streamk_kernel launch no clusters; in every kernel each CTA issues its own loads.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -1268,7 +1268,7 @@ conv_streamk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // neighbouring SMs (a cluster of two) compute one tile of 256 pixels x BN channels with tcgen05.mma.cta_group::2. Each
 // CTA loads its own 128 rows of A and HALF of the B tile (BN/2 output channels), the MMA reads both halves across the
 // pair, and each CTA finishes its own 128 rows from its own TMEM (bias, residual, activation, store) as in the plain
-// kernel. Per k-block a CTA fetches 16 KB + BN x 64 B instead of 16 KB + BN x 128 B. No multicast anywhere: every load
+// kernel. Per k-block a CTA fetches 16 KB + BN x 64 B instead of 16 KB + BN x 128 B. Every load
 // lands in the shared memory of the CTA that issued it.
 // Protocol (even CTA = leader): `full` barriers live in the leader and count one arrive.expect_tx from each CTA's
 // producer plus the bytes of both CTAs' loads; `empty` and `tfull` barriers are per CTA and are signalled by the

@@ -524,7 +524,7 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t by
                  : "memory");
 }
 // Bulk tensor loads whose completion is counted on an mbarrier of either CTA of the pair (`bar`: a shared::cluster
-// address); the destination is this CTA's shared memory. No multicast: each CTA fetches its own boxes.
+// address); the destination is this CTA's shared memory: each CTA fetches its own boxes.
 __device__ __forceinline__ void tma_pair_load_2d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
