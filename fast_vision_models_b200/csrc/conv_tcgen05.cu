@@ -101,6 +101,7 @@ struct ConvParams {
     int wb, wb_tpi;
     FastDiv div_tpi;
     int sk;
+    int rev;       // walk the m-tiles from the last to the first (see fvm_conv2d_f16_tile)
     int pair;      // conv_pair_kernel: two CTAs per tile of 256 pixels x BN channels (m_tiles counts 256-pixel tiles)
     uint32_t sk_units;
     FastDiv div_kb;
@@ -247,12 +248,15 @@ __device__ __forceinline__ bool tile_at(const ConvParams& p, int it, int& m_tile
         const int q = static_cast<int>(fastdiv(blockIdx.x, p.div_ntiles));
         n_tile = static_cast<int>(blockIdx.x) - q * p.n_tiles;
         m_tile = q + it * static_cast<int>(fastdiv(gridDim.x, p.div_ntiles));
-        return m_tile < p.m_tiles;
+        if (m_tile >= p.m_tiles) return false;
+        if (p.rev) m_tile = p.m_tiles - 1 - m_tile;
+        return true;
     }
     const int tile = static_cast<int>(blockIdx.x) + it * static_cast<int>(gridDim.x);
     if (tile >= p.m_tiles * p.n_tiles) return false;
     m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
     n_tile = tile - m_tile * p.n_tiles;
+    if (p.rev) m_tile = p.m_tiles - 1 - m_tile;
     return true;
 }
 
@@ -1307,8 +1311,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     auto tile_at2 = [&](int it, int& m0, int& n0) {
         const int tile = pair + it * npairs;
         if (tile >= total_tiles) return false;
-        const int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
+        int m_tile = static_cast<int>(fastdiv(static_cast<uint32_t>(tile), p.div_ntiles));
         n0 = (tile - m_tile * p.n_tiles) * p.BN;
+        if (p.rev) m_tile = p.m_tiles - 1 - m_tile;
         m0 = (2 * m_tile + static_cast<int>(rank)) * BM;
         return true;
     };
@@ -2426,6 +2431,16 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     if (p.n_tiles > 1 && (p.BN & 63)) return FVM_ERR_ARG;   // split K only in whole 64-channel store boxes
     p.im2col = !(R == 1 && S == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && ph_hi == 0 && pw_hi == 0);
     p.act = act;
+    // Tile order: a 1x1 stride-1 layer without residual whose input is larger than half of the L2 and at least four
+    // times wider than its output (the first convolution of a bottleneck block, reading the previous block's output)
+    // walks its m-tiles from the last to the first: the kernel before it wrote that tensor front to back, so the tail
+    // is what the L2 still holds (measured inside a ResNet-50 forward at batch 64: 27.6 -> 21.8 us for 256 -> 64 at 56x56).
+    {
+        static const int rev_rule = [] { const char* v = getenv("FVM_B200_REVERSE"); return (v && v[0] == '0') ? 0 : 1; }();
+        if (rev_rule && R == 1 && S == 1 && sh == 1 && sw == 1 && !res && C >= 4 * K &&
+            static_cast<long long>(p.M) * ldx * 2 > 64ll * 1024 * 1024)
+            p.rev = 1;
+    }
     p.has_res = res != nullptr;
     p.bias = static_cast<const __half*>(bias);
     p.scale = scale;
