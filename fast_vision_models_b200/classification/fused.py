@@ -4,6 +4,7 @@ Counterpart of the reference's `fuse_graph` / `fuse_dw` / `replace_bn_act` / `re
 (classification/fast/fused.py:163-312): the traced graph is rewritten so that
 
   Conv2d(groups=1, zero padding, C % 8 == 0, K % 8 == 0) [-> BatchNorm2d] [-> add(other)] [-> activation]
+  Conv2d(1 < groups < C, C % 8 == 0, K % 8 == 0) [-> BatchNorm2d] [-> activation]          -> clfr3.gconv2
                                                   ==> torch.ops.clf.conv_fused(x, w, b, res, padding, stride, act)
   (dilated)                                       ==> torch.ops.segx.conv_fused_d(..., dilation, act)
   depthwise Conv2d [-> BatchNorm2d] [-> activation] ==> torch.ops.clf.dwconv(x, w_rsc, b, stride, padding, act)
@@ -124,7 +125,10 @@ class Rewriter:
         depthwise = conv.groups == C == K and C % 8 == 0 and conv.groups > 1
         image_stem = node.args[0].op == "placeholder" and conv.groups == 1 and C < 8 and K % 8 == 0
         dense = conv.groups == 1 and C % 8 == 0 and K % 8 == 0
-        if not (depthwise or dense or image_stem):
+        # grouped (not depthwise): clfr3.gconv2, the reference's rewrite of RegNet / ResNeXt convolutions (r3.py:166-214)
+        grouped = (1 < conv.groups and not depthwise and C % conv.groups == 0 and K % conv.groups == 0 and C % 8 == 0
+                   and K % 8 == 0 and conv.dilation == (1, 1))
+        if not (depthwise or dense or image_stem or grouped):
             return False
         last, bn = node, None
         u = _single_user(last)
@@ -132,7 +136,7 @@ class Rewriter:
             bn, last = self.mods[u.target], u
         res = None
         u = _single_user(last)
-        if not depthwise and u is not None and u.op == "call_function" and u.target in _ADDS and len(u.args) == 2 and not u.kwargs:
+        if not depthwise and not grouped and u is not None and u.op == "call_function" and u.target in _ADDS and len(u.args) == 2 and not u.kwargs:
             other = u.args[1] if u.args[0] is last else u.args[0]
             if isinstance(other, fx.Node) and other is not last:
                 res, last = other, u
@@ -158,6 +162,12 @@ class Rewriter:
                 else:
                     new = self.g.call_function(torch.ops.clf.dwconv, (x, wn, bn_, list(conv.stride), list(conv.padding), act))
                 self.stats["dwconv"] += 1
+            elif grouped:
+                wn = self._buffer("gw", fold.to_krsc_half(w))        # [K, C/groups, R, S], the reference's layout
+                bn_ = self._buffer("gb", b.half().contiguous())
+                new = self.g.call_function(torch.ops.clfr3.gconv2, (x, wn, bn_, list(conv.stride), list(conv.padding),
+                                                                    conv.groups, act))
+                self.stats["gconv"] = self.stats.get("gconv", 0) + 1
             else:
                 if image_stem:
                     w = fold.pad_in_channels(w, 8)

@@ -153,6 +153,15 @@ extern "C" int fvm_conv2d_f16_pad(const void* x, const void* w, const void* bias
                          tile_n, ph_hi, pw_hi, static_cast<cudaStream_t>(stream));
 }
 
+// Grouped convolution on the dense kernel: see fvm_gconv2d_f16 in the header.
+extern "C" int fvm_gconv2d_f16(const void* x, const void* w_sg, const void* bias, const void* res, void* y, int N, int H,
+                               int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
+                               long long ldx, long long ldy, long long ldr, int act, int gsg, int gsk, void* stream) {
+    if (gsg <= 0) return FVM_ERR_ARG;
+    return conv2d_launch(x, w_sg, bias, res, nullptr, y, N, H, W, C, K, R, S, ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, act, 0,
+                         -1, -1, static_cast<cudaStream_t>(stream), 0, gsg, gsk);
+}
+
 // 1x1 stride-1 convolution whose weights differ per image: w_n is [N][K][C]. Used for the project conv of a
 // squeeze-excite block with the gate folded into the weights (see fvm_gate_weights_f16).
 extern "C" int fvm_conv1x1_wbatch_f16(const void* x, const void* w_n, const void* bias, const void* res, void* y, int N,

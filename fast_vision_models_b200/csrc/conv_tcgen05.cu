@@ -101,6 +101,8 @@ struct ConvParams {
     int wb, wb_tpi;
     FastDiv div_tpi;
     int sk;
+    int gsg, gsk;  // grouped convolution: input / output channels per super-group (0: dense), see conv2d_launch
+    FastDiv div_gsk;
     int rev;       // walk the m-tiles from the last to the first (see fvm_conv2d_f16_tile)
     int pair;      // conv_pair_kernel: two CTAs per tile of 256 pixels x BN channels (m_tiles counts 256-pixel tiles)
     uint32_t sk_units;
@@ -495,6 +497,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     h0 = pp * p.sh - p.ph;
                     w0 = qq * p.sw - p.pw;
                 }
+                // grouped convolution: the input channels of this n-tile's super-group start at goff
+                const int goff = p.gsg ? static_cast<int>(fastdiv(static_cast<uint32_t>(n0), p.div_gsk)) * p.gsg : 0;
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
                     const bool armed = issued < pre;      // this stage's barrier and B tile were set up before the wait
@@ -522,14 +526,14 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     if (!p.bres && !armed) load_w(b_dst, full_bar(stage), cc * BK, tap, n0 + wb_img * p.K);
                     if (p.im2col) {
-                        tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), cc * BK, w0, h0, img,
+                        tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), goff + cc * BK, w0, h0, img,
                                            static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
                     } else if (p.wb) {
                         tma_load_3d(a_dst, &tmap_a, full_bar(stage), cc * BK, wb_row0, wb_img);
                     } else {
                         for (int l = 0; l < p.a_loads; ++l)
-                            tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage), cc * BK,
-                                        m0 + l * p.a_rows);
+                            tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage),
+                                        goff + cc * BK, m0 + l * p.a_rows);
                     }
                     if (++cc == p.cchunks) {
                         cc = 0;
@@ -2325,7 +2329,7 @@ int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int 
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
-                  cudaStream_t stream, int w_per_image) {
+                  cudaStream_t stream, int w_per_image, int gsg, int gsk) {
     // ph / pw pad the top / left; ph_hi / pw_hi the bottom / right (negative: same as top / left)
     if (ph_hi < 0) ph_hi = ph;
     if (pw_hi < 0) pw_hi = pw;
@@ -2363,6 +2367,22 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     p.K = K; p.C = C; p.R = R; p.S = S; p.P = P; p.Q = Q;
     p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
     p.cchunks = (C + BK - 1) / BK;
+    if (gsg > 0) {
+        // Grouped convolution as block-diagonal dense convolutions over "super-groups": the channels are cut into runs
+        // of gsg input / gsk output channels (whole groups; gsk a multiple of 64 so that output tiles and their
+        // 64-channel store boxes never straddle a run, the last run may be short), and w is [K][R*S][gsg] with zeros
+        // outside each output channel's own group. An n-tile then reads only the input channels of its run.
+        if (w_per_image || (gsg & 7) || gsk <= 0 || (gsk < K && (gsk & 63)) || gsg > C || force_halo == 1 ||
+            force_bres == 1 || force_sk == 1 || force_pair || force_mt > 1)
+            return FVM_ERR_ARG;
+        if ((static_cast<long long>(C) + gsg - 1) / gsg != (static_cast<long long>(K) + gsk - 1) / gsk) return FVM_ERR_ARG;
+        p.gsg = gsg;
+        p.gsk = gsk;
+        p.div_gsk = fastdiv_init(static_cast<uint32_t>(gsk));
+        p.cchunks = (gsg + BK - 1) / BK;
+        if (force_bn <= 0) force_bn = gsk >= K ? 0 : (gsk % 256 == 0 ? 256 : (gsk % 128 == 0 ? 128 : 64));
+        if (force_bn > 0 && gsk < K && gsk % force_bn) return FVM_ERR_ARG;
+    }
     p.kblocks = R * S * p.cchunks;
     p.m_tiles = (p.M + BM - 1) / BM;
     p.taps = R * S;
@@ -2382,7 +2402,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         const int Kp16 = (K + 31) / 32 * 32;   // tiles are multiples of 32 channels
         SmemPlan tp;
         const int tpk = (C == 8 || C == 16) ? BK / C : 1;      // taps per k-block in tap-packed mode
-        p.tapk = ((C == 8 || C == 16) && R * S > 1 && Kp16 <= 256 && (force_bn <= 0 || force_bn >= Kp16) &&
+        p.tapk = (!gsg && (C == 8 || C == 16) && R * S > 1 && Kp16 <= 256 && (force_bn <= 0 || force_bn >= Kp16) &&
                   plan_smem(Kp16, 1, (R * S + tpk - 1) / tpk, K, true, false, &tp)) ? C : 0;
         if (p.tapk) {
             p.kblocks = (R * S + tpk - 1) / tpk;
@@ -2392,7 +2412,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // Halo mode for 3x3 stride-1 convolutions (dilation up to 4): an m-tile is a 16 x 8 patch of output pixels of one
     // image. Chosen when few patch pixels fall outside the image (they are computed and clipped by the store).
     uint32_t halo_bytes = 0;
-    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1 && !force_pair) {
+    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1 && !force_pair && !gsg) {
         const int ty = (P + HALO_TH - 1) / HALO_TH, tx = (Q + HALO_TW - 1) / HALO_TW;
         const double eff = static_cast<double>(P) * Q / (static_cast<double>(ty) * tx * BM);
         // by default only for inputs of one 64-channel chunk: there the taps are accumulated in the same order as in
@@ -2415,7 +2435,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // 28x28 and smaller maps of a ResNet at batch 64; measured there: 10-25 % faster than the best single-CTA tile).
     // Tile width from the same measurements: all of K (up to 256) for deep reductions without a residual, else 128.
     static const int auto_pairs = [] { const char* v = getenv("FVM_B200_PAIR"); return (v && v[0] == '0') ? 0 : 1; }();
-    if (free_choice && auto_pairs && !p.tapk && !p.halo && !p.wb && st->pair_clusters > 0 && C >= 24 && K >= 64 &&
+    if (free_choice && auto_pairs && !gsg && !p.tapk && !p.halo && !p.wb && st->pair_clusters > 0 && C >= 24 && K >= 64 &&
         p.m_tiles <= 4 * st->sms) {
         const int bn = (K <= 128 || (K <= 256 && !res && p.kblocks >= 8)) ? (K + 31) / 32 * 32 : 128;
         SmemPlan tp;
@@ -2482,7 +2502,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     {
         const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
         const long long units = tiles * p.kblocks;
-        const bool can = !p.tapk && !p.halo && !p.wb && !p.pair && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
+        const bool can = !p.tapk && !p.halo && !p.wb && !p.pair && !gsg && p.mt == 1 && force_bres != 1 && st->sk_part != nullptr && p.kblocks >= 2 &&
                          units >= st->sms && units < 0x7fffffffll &&
                          static_cast<size_t>(st->sms) * BM * p.BN <= st->sk_floats;
         if (force_sk == 1 && !can) return FVM_ERR_ARG;
@@ -2496,7 +2516,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     }
     SmemPlan sp;
     p.bres = 0;
-    if (!p.sk && !p.wb && !p.tapk && !p.pair && force_bres != 2 && p.n_tiles <= st->sms) {
+    if (!p.sk && !p.wb && !p.tapk && !p.pair && !gsg && force_bres != 2 && p.n_tiles <= st->sms) {
         const long long wbytes = static_cast<long long>(p.kblocks) * p.BN * BK * 2;
         const int cta_per_n = st->sms / p.n_tiles;
         const bool worth = p.m_tiles >= 2 * cta_per_n;
@@ -2578,9 +2598,10 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     }
     {
         // weights [K][R*S][C] (per-image weights: [N * K][1][C], image n's rows start at n * K)
-        cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(R * S),
+        const int Cw = gsg > 0 ? gsg : C;      // input channels per weight row
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(Cw), static_cast<cuuint64_t>(R * S),
                               static_cast<cuuint64_t>(K) * (p.wb ? N : 1)};
-        cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 2, static_cast<cuuint64_t>(R) * S * C * 2};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(Cw) * 2, static_cast<cuuint64_t>(R) * S * Cw * 2};
         cuuint32_t box[3] = {static_cast<cuuint32_t>(p.tapk ? p.tapk : BK), 1, static_cast<cuuint32_t>(p.pair ? p.BN / 2 : p.BN)};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = g_encode_tiled(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(w), dims, strides,

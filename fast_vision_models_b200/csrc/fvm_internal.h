@@ -40,7 +40,7 @@ int stem_s2_launch(const void* x, const void* w, const void* bias, void* y, int 
 int conv2d_launch(const void* x, const void* w, const void* bias, const void* res, const float* scale, void* y, int N,
                   int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
-                  cudaStream_t stream, int w_per_image = 0);
+                  cudaStream_t stream, int w_per_image = 0, int gsg = 0, int gsk = 0);
 int conv_chain_launch(const fvm_chain_layer* layers, int n, cudaStream_t stream);
 
 }  // namespace fvm

@@ -68,6 +68,36 @@ def to_krsc_half(w: torch.Tensor) -> torch.Tensor:
     return w.half().contiguous(memory_format=torch.channels_last)
 
 
+def grouped_runs(C: int, K: int, groups: int):
+    """Super-group shape for fvm_gconv2d_f16: the fewest whole groups per run such that a run's input channels are a
+    multiple of 8 and its output channels a multiple of 64 (or one run covers everything). Returns (gsg, gsk)."""
+    if groups <= 0 or C % groups or K % groups:
+        raise ValueError(f"grouped conv: {C} -> {K} channels do not divide into {groups} groups")
+    gw, kg = C // groups, K // groups
+    for r in range(1, groups + 1):
+        if r == groups or ((r * gw) % 8 == 0 and (r * kg) % 64 == 0):
+            return r * gw, r * kg
+    return C, K
+
+
+def pack_grouped(w: torch.Tensor, groups: int):
+    """Grouped-conv weight [K, GW, R, S] (the reference's clfr3.gconv2 layout, r3.cu:230-232) -> ([K, gsg, R, S] fp16
+    stored KRSC, gsg, gsk): every output channel's GW weights sit at its group's place inside its run of gsg input
+    channels, zeros elsewhere, so that a run is a dense gsg -> gsk convolution."""
+    K, GW, R, S = w.shape
+    C = GW * groups
+    gsg, gsk = grouped_runs(C, K, groups)
+    kg = K // groups
+    per_run = gsg // GW
+    out = torch.zeros((K, gsg, R, S), dtype=torch.float16, device=w.device)
+    wh = w.to(torch.float16)
+    for j in range(per_run):                       # position of the group inside its run
+        ks = torch.arange(K, device=w.device)
+        sel = ((ks // kg) % per_run) == j
+        out[sel, j * GW:(j + 1) * GW] = wh[sel]
+    return out.contiguous(memory_format=torch.channels_last), gsg, gsk
+
+
 def dw_to_rsc_half(w: torch.Tensor) -> torch.Tensor:
     """Depthwise weight [C,1,R,S] fp32 -> [R,S,C] fp16 contiguous (reference: fused.py:221)."""
     return w[:, 0].permute(1, 2, 0).contiguous().half()

@@ -297,6 +297,96 @@ def pw_into(x, w, bias, res, act: int, out: torch.Tensor, force: int = 0) -> Non
     conv_fused_into(x, w, bias, res, (0, 0), (1, 1), act, out)
 
 
+_PACKED_GROUPED = {}      # (data_ptr, version, shape, groups) -> (packed weights, gsg, gsk, the source tensor kept alive)
+
+
+def _packed_grouped(w: torch.Tensor, groups: int):
+    from . import fold
+    key = (w.data_ptr(), w._version, tuple(w.shape), int(groups))
+    hit = _PACKED_GROUPED.get(key)
+    if hit is None:
+        if len(_PACKED_GROUPED) >= 512:
+            _PACKED_GROUPED.clear()
+        wp, gsg, gsk = fold.pack_grouped(w, groups)
+        hit = _PACKED_GROUPED[key] = (wp, gsg, gsk, w)
+    return hit[:3]
+
+
+def gconv2_packed_into(x, w_sg, bias, res, stride, pad, act: int, gsg: int, gsk: int, out: torch.Tensor, dilation=(1, 1)) -> None:
+    """Grouped convolution with weights already in the super-group layout of fold.pack_grouped (fvm_gconv2d_f16)."""
+    init(x.device)
+    x, N, C, H, W, ldx = nhwc_view(x, "x")
+    w_sg = _krsc(w_sg)
+    K, Cw, R, S = w_sg.shape
+    if Cw != gsg:
+        raise FvmError(f"gconv2: packed weight has {Cw} input channels per run, expected {gsg}")
+    ph, pw = _pair(pad)
+    sh, sw = _pair(stride)
+    dh, dw = _pair(dilation)
+    P = (H + 2 * ph - dh * (R - 1) - 1) // sh + 1
+    Q = (W + 2 * pw - dw * (S - 1) - 1) // sw + 1
+    out_v, No, Ko, Po, Qo, ldy = nhwc_view(out, "out")
+    if out_v is not out or (No, Ko, Po, Qo) != (N, K, P, Q):
+        raise FvmError(f"gconv2: out must be a channels-last [N,K,P,Q]={N, K, P, Q} tensor or channel slice")
+    ldr = 0
+    if res is not None:
+        res, Nr, Kr, Pr, Qr, ldr = nhwc_view(res, "res")
+        if (Nr, Kr, Pr, Qr) != (N, K, P, Q):
+            raise FvmError("gconv2: residual shape does not match the output")
+    if bias is not None:
+        _require_cuda_half(bias, "bias")
+        bias = bias.contiguous()
+    _check(lib().fvm_gconv2d_f16(x.data_ptr(), w_sg.data_ptr(), _ptr(bias), _ptr(res), out.data_ptr(), N, H, W, C, K, R, S,
+                                 ph, pw, sh, sw, dh, dw, ldx, ldy, ldr, int(act), int(gsg), int(gsk), _stream()), "gconv2d_f16")
+
+
+def gconv2(x, w, bias=None, stride=(1, 1), pad=(0, 0), groups: int = 1, act: int = 0, cfg: int = -1) -> torch.Tensor:
+    """clfr3::gconv2(x, w, bias?, stride, pad, groups, act, cfg=-1) -> Tensor (r3.cu:276-279, schema :800): grouped
+    convolution, w [K, C/groups, R, S] channels-last. Runs on the dense tcgen05 kernel over block-diagonal runs of groups
+    (the packed weights are built once per weight tensor and kept); `cfg` is accepted and ignored."""
+    N, C, H, W = x.shape
+    K, GW, R, S = w.shape
+    if GW * groups != C:
+        raise FvmError(f"gconv2: weight has {GW} channels per group, {groups} groups, input has {C} channels")
+    w_sg, gsg, gsk = _packed_grouped(w, groups)
+    ph, pw = _pair(pad)
+    sh, sw = _pair(stride)
+    out = empty_nhwc(N, K, (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1, x.device)
+    gconv2_packed_into(x, w_sg, bias, None, stride, pad, act, gsg, gsk, out)
+    return out
+
+
+def gconv2_pool(x, w, bias, stride, pad, groups: int, act: int):
+    """clfr3::gconv2_pool -> (y, mean [N, K, 1, 1]) (r3.cu:289-299): the grouped convolution and the global average of its
+    output (the squeeze of a squeeze-excite block that follows). Two launches here: gconv2, then the pooling kernel."""
+    y = gconv2(x, w, bias, stride, pad, groups, act)
+    return y, global_avgpool(y)
+
+
+def dwmult(x, w_rsk, bias=None, stride=(1, 1), pad=(0, 0), act: int = 0) -> torch.Tensor:
+    """clfmb::dwmult(x, w_rsk, bias?, stride, pad, act) (mbconv.cu:776-788, schema :1248): depthwise convolution with a
+    channel multiplier, w_rsk [R, S, K] with K = m * C (output channel k reads input channel k // m). A grouped
+    convolution with groups = C and one input channel per group."""
+    R, S, K = w_rsk.shape
+    C = x.shape[1]
+    if K % C:
+        raise FvmError("dwmult: K must be a multiple of C")
+    w = w_rsk.permute(2, 0, 1).reshape(K, 1, R, S)
+    key_src = w_rsk
+    hit = _PACKED_GROUPED.get((key_src.data_ptr(), key_src._version, tuple(key_src.shape), -C))
+    if hit is None:
+        from . import fold
+        wp, gsg, gsk = fold.pack_grouped(w, C)
+        hit = _PACKED_GROUPED[(key_src.data_ptr(), key_src._version, tuple(key_src.shape), -C)] = (wp, gsg, gsk, key_src)
+    w_sg, gsg, gsk = hit[:3]
+    N, _, H, W = x.shape
+    ph, pw = _pair(pad)
+    sh, sw = _pair(stride)
+    out = empty_nhwc(N, K, (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1, x.device)
+    gconv2_packed_into(x, w_sg, bias, None, stride, pad, act, gsg, gsk, out)
+    return out
+
+
 def conv_tc(x, w, bias=None, stride=(1, 1), pad=(0, 0), act: int = 0, cfg: int = -1) -> torch.Tensor:
     """clfr3::conv_tc(x, w, bias?, stride, pad, act, cfg=-1) (r3.cu:801): dense KxK conv over few input channels
     (C <= 48, C % 16 == 0 in the reference, which runs it on its grouped-conv kernel). Note the argument order: stride

@@ -42,9 +42,12 @@ SCHEMAS = {
         "dwconv2(Tensor x, Tensor w_rsc, Tensor? bias, int[] stride, int[] padding, int act) -> Tensor",
         "se_scale(Tensor x, Tensor s) -> Tensor",
         "stem_pool(Tensor x, Tensor w_t, Tensor? bias, int[] stride, int[] pad, int act, int pk, int ps, int pp, bool ceil) -> Tensor",
+        "gconv2(Tensor x, Tensor w, Tensor? bias, int[] stride, int[] pad, int groups, int act, int cfg=-1) -> Tensor",
+        "gconv2_pool(Tensor x, Tensor w, Tensor? bias, int[] stride, int[] pad, int groups, int act) -> (Tensor, Tensor)",
     ],
     "clfmb": [
         "stem_direct(Tensor x, Tensor w_t, Tensor? bias, int[] stride, int[] pad, int act) -> Tensor",
+        "dwmult(Tensor x, Tensor w_rsk, Tensor? bias, int[] stride, int[] pad, int act) -> Tensor",
     ],
     "segx": [
         "input_nhwc8(Tensor x) -> Tensor",
@@ -141,6 +144,18 @@ def _cuda_impls():
         y = stem_meta(x, w_t, bias, stride, pad, act)
         return _empty_cl(x, (y.shape[0], y.shape[1], ops._pool_out(y.shape[2], pk, ps, pp, ceil), ops._pool_out(y.shape[3], pk, ps, pp, ceil)))
 
+    def gconv2_meta(x, w, bias, stride, pad, groups, act, cfg=-1):
+        return _empty_cl(x, _conv_out(x, w, pad, stride))
+
+    def gconv2_pool_meta(x, w, bias, stride, pad, groups, act):
+        y = gconv2_meta(x, w, bias, stride, pad, groups, act)
+        return y, _empty_cl(x, (y.shape[0], y.shape[1], 1, 1))
+
+    def dwmult_meta(x, w_rsk, bias, stride, pad, act):
+        N, _, H, W = x.shape
+        R, S, K = w_rsk.shape
+        return _empty_cl(x, (N, K, (H + 2 * pad[0] - R) // stride[0] + 1, (W + 2 * pad[1] - S) // stride[1] + 1))
+
     def up_argmax(s, H, W, align):
         # the reference passes the scores as an NHWC-shaped tensor [B, h, w, C] (segx_ops.cu:172-175)
         return ops.up_argmax(s.permute(0, 3, 1, 2), H, W, align)
@@ -164,6 +179,11 @@ def _cuda_impls():
         "pw_into": (lambda x, w, bias, res, act, out, force=0: ops.pw_into(x, w, bias, res, act, out, force), nothing),
         "conv_tc": (lambda x, w, bias, stride, pad, act, cfg=-1: ops.conv_tc(x, w, bias, stride, pad, act, cfg), conv_tc_meta),
         "conv_tc_into": (lambda x, w, bias, stride, pad, act, out: ops.conv_tc_into(x, w, bias, stride, pad, act, out), nothing),
+        "gconv2": (lambda x, w, bias, stride, pad, groups, act, cfg=-1: ops.gconv2(x, w, bias, stride, pad, groups, act, cfg),
+                   gconv2_meta),
+        "gconv2_pool": (lambda x, w, bias, stride, pad, groups, act: ops.gconv2_pool(x, w, bias, stride, pad, groups, act),
+                        gconv2_pool_meta),
+        "dwmult": (lambda x, w_rsk, bias, stride, pad, act: ops.dwmult(x, w_rsk, bias, stride, pad, act), dwmult_meta),
         "se_scale": (ops.se_scale, same_meta),
         "stem_direct": (ops.stem_direct, stem_meta),
         "stem_pool": (ops.stem_pool, stem_pool_meta),

@@ -84,6 +84,18 @@ int fvm_conv2d_f16_tile(const void* x, const void* w, const void* bias, const vo
                         int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw,
                         long long ldx, long long ldy, long long ldr, int act, int tile_n, void* stream);
 
+/* Grouped convolution -- replaces clfr3::gconv2 (classification/fast/csrc/r3.cu:49-299; a hand-written grouped
+ * implicit GEMM there) and, with a group width of one, clfmb::dwmult (depthwise with channel multiplier). It runs on the
+ * dense tcgen05 kernel as block-diagonal convolutions over "super-groups": the channels are cut into runs of gsg input
+ * and gsk output channels that hold whole groups (gsg a multiple of the group width and of 8, gsk = gsg * K / C a
+ * multiple of 64 unless one run covers everything; the last run may be short), and w_sg is [K][R][S][gsg] with each
+ * output channel's own group's weights in place and zeros elsewhere (fast_vision_models_b200.fold.pack_grouped builds it
+ * from the reference's [K][GW][R][S] weights). An output tile reads only its run's input channels, so the work grows
+ * with gsg / GW, not with the number of groups. Same epilogue as fvm_conv2d_f16 (bias, residual, activation). */
+int fvm_gconv2d_f16(const void* x, const void* w_sg, const void* bias, const void* res, void* y, int N, int H, int W, int C,
+                    int K, int R, int S, int ph, int pw, int sh, int sw, int dh, int dw, long long ldx, long long ldy,
+                    long long ldr, int act, int gsg, int gsk, void* stream);
+
 /* A run of dense convolutions as ONE launch -- no counterpart in the reference, which launches one kernel per layer
  * (classification/fast/csrc/fused_conv.cu:231-306): the bottleneck blocks of a ResNet stage, say. Each entry is one
  * fvm_conv2d_f16 call (same operands, same arithmetic, same bits as the CTA-pair kernel of fvm_conv2d_f16_tile); layer

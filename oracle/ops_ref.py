@@ -31,6 +31,15 @@ def act_ref(v: torch.Tensor, act: int) -> torch.Tensor:
     raise ValueError(act)
 
 
+def gconv2_ref(x, w, bias=None, stride=(1, 1), padding=(0, 0), groups=1, act=0):
+    """Grouped convolution + bias + activation -- clfr3::gconv2 (classification/fast/csrc/r3.cu:49-299; w [K, C/groups, R, S]).
+    The reference kernel accumulates in fp16, its portable tier (aten) in fp32 as here; one rounding to fp16 at the end."""
+    v = F.conv2d(x.float(), w.float(), None, stride, padding, 1, groups)
+    if bias is not None:
+        v = v + bias.float().view(1, -1, 1, 1)
+    return act_ref(v, act).half()
+
+
 def conv_fused_ref(x, w, bias=None, res=None, padding=(0, 0), stride=(1, 1), act=0, dilation=(1, 1), scale=None):
     """y = half(act(conv(x,w) + bias + res)) -- epilogue order of Visitor::visit, fused_conv.cu:81-99 (fp32 epilogue,
     single rounding); accumulation in fp32 (the reference kernel accumulates in fp16, its portable tier in fp32).

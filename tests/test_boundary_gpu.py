@@ -135,7 +135,7 @@ def test_fx_graph_of_registered_ops_replays_under_cuda_graph_capture():
     assert (captured.cpu() == R.up_argmax_ref(s, 48, 64, False)).float().mean() >= 0.995
 
 
-@pytest.mark.parametrize("name", ["resnet18", "mobilenet_v2", "densenet121", "regnet_y_400mf", "squeezenet1_1"])
+@pytest.mark.parametrize("name", ["resnet18", "mobilenet_v2", "densenet121", "regnet_y_400mf", "squeezenet1_1", "resnext50_32x4d"])
 def test_generic_graph_pass_matches_upstream_fp32(name):
     # architectures without a hand-built compiler go through the pattern pass (conv -> [add] -> [act] chains,
     # depthwise, pools, unfoldable BatchNorm, squeeze-excite scale); what it cannot place stays on aten in fp16
@@ -149,6 +149,8 @@ def test_generic_graph_pass_matches_upstream_fp32(name):
     net = Fast(fuse_graph(model)).to(DEV)          # what optimize() builds for a family without a hand-built compiler
     stats = net.net.gm.fvm_stats
     assert stats["conv_fused"] >= 10 and stats["stem_pad"] == 1
+    if name in ("regnet_y_400mf", "resnext50_32x4d"):
+        assert stats.get("gconv", 0) >= 10          # grouped convolutions go to clfr3.gconv2, not to aten
     x = seeded_input((4, 3, 96, 96), seed=0).to(DEV)
     y = net(x)
     with torch.inference_mode():

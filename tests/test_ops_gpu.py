@@ -339,6 +339,41 @@ def test_conv_chain_with_aliased_buffers_falls_back_to_stream_order():
     assert torch.equal(y1, y1_ref) and torch.equal(xin, y2_ref)
 
 
+GCONV_CASES = [
+    # N, H, W, C, K, groups, R, pad, stride, act
+    (4, 28, 28, 128, 128, 32, 3, 1, 1, 1),      # ResNeXt-50 32x4d stage 1: 4 channels per group, 16 groups per run
+    (4, 14, 14, 256, 256, 16, 3, 1, 2, 1),      # 16 per group, stride 2
+    (3, 20, 20, 96, 96, 2, 3, 1, 1, 3),         # RegNet-like 48 per group: one run over everything
+    (2, 17, 13, 432, 432, 9, 3, 1, 1, 1),       # 48 per group, 9 groups: runs of 192 with a short last run
+    (2, 12, 12, 448, 448, 4, 3, 1, 2, 1),       # 112 per group: one run of 448
+    (5, 9, 9, 64, 128, 8, 1, 0, 1, 0),          # 1x1, more output than input channels per group (8 -> 16)
+    (2, 16, 16, 224, 224, 28, 3, 1, 1, 1),      # 8 per group: runs of 64, 3.5 runs
+]
+
+
+@pytest.mark.parametrize("case", GCONV_CASES)
+def test_gconv2_matches_oracle(case):
+    N, H, W, C, K, G, Rr, pad, stride, act = case
+    x, w, b = gen((N, C, H, W), 71), gen((K, C // G, Rr, Rr), 72, 0.08), gen((K,), 73, 0.1)
+    y = ops.gconv2(cl(x), cl(w), b.to(DEV), (stride, stride), (pad, pad), G, act)
+    assert ops.last_status() == 0
+    close(y, R.gconv2_ref(x, w, b, (stride, stride), (pad, pad), G, act))
+    y2, mean = ops.gconv2_pool(cl(x), cl(w), b.to(DEV), (stride, stride), (pad, pad), G, act)
+    assert torch.equal(y2, y)
+    close(mean, y.float().mean((2, 3), keepdim=True).half().cpu(), 2e-3)
+
+
+def test_dwmult_matches_oracle():
+    # depthwise with channel multiplier 2 and 4: output channel k reads input channel k // m
+    for C, m, Rr in ((32, 2, 3), (16, 4, 5)):
+        K = C * m
+        x, w, b = gen((3, C, 15, 11), 81), gen((K, 1, Rr, Rr), 82, 0.2), gen((K,), 83, 0.1)
+        w_rsk = w[:, 0].permute(1, 2, 0).contiguous().half().to(DEV)
+        y = ops.dwmult(cl(x), w_rsk, b.to(DEV), (1, 1), (Rr // 2, Rr // 2), 3)
+        assert ops.last_status() == 0
+        close(y, R.gconv2_ref(x, w, b, (1, 1), (Rr // 2, Rr // 2), C, 3))
+
+
 HALO_CASES = [
     # N, H, W, C, K, dil, res, tile, weight-resident (0 choose / 1 on / 2 off)
     (2, 16, 8, 64, 64, 1, False, 0, 2),        # exactly one patch per image
