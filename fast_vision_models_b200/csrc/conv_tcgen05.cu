@@ -427,6 +427,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     wb_img = static_cast<int>(fastdiv(static_cast<uint32_t>(m_tile), p.div_tpi));
                     wb_row0 = (m_tile - wb_img * p.wb_tpi) * BM * p.mt;
                 }
+                // grouped convolution: the input channels of this n-tile's super-group start at goff
+                const int goff = p.gsg ? static_cast<int>(fastdiv(static_cast<uint32_t>(n0), p.div_gsk)) * p.gsg : 0;
                 // halo mode: m_tile = (image, patch row, patch column)
                 int himg = 0, hy0 = 0, hx0 = 0;
                 if (p.halo) {
@@ -470,7 +472,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             tma_load_5d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), 0,
                                         hx0 + p.stem_xlo, 0, 2 * hy0 - p.ph, himg);
                         else
-                            tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), hc * BK,
+                            tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), goff + hc * BK,
                                         hx0 - p.pw, hy0 - p.ph, himg);
                         if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
                         if (p.bres) continue;
@@ -497,8 +499,6 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     h0 = pp * p.sh - p.ph;
                     w0 = qq * p.sw - p.pw;
                 }
-                // grouped convolution: the input channels of this n-tile's super-group start at goff
-                const int goff = p.gsg ? static_cast<int>(fastdiv(static_cast<uint32_t>(n0), p.div_gsk)) * p.gsg : 0;
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int kb = 0; kb < p.kblocks; ++kb) {
                     const bool armed = issued < pre;      // this stage's barrier and B tile were set up before the wait
@@ -2372,8 +2372,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         // of gsg input / gsk output channels (whole groups; gsk a multiple of 64 so that output tiles and their
         // 64-channel store boxes never straddle a run, the last run may be short), and w is [K][R*S][gsg] with zeros
         // outside each output channel's own group. An n-tile then reads only the input channels of its run.
-        if (w_per_image || (gsg & 7) || gsk <= 0 || (gsk < K && (gsk & 63)) || gsg > C || force_halo == 1 ||
-            force_bres == 1 || force_sk == 1 || force_pair || force_mt > 1)
+        if (w_per_image || (gsg & 7) || gsk <= 0 || (gsk < K && (gsk & 63)) || gsg > C || force_sk == 1 || force_pair ||
+            force_mt > 1)
             return FVM_ERR_ARG;
         if ((static_cast<long long>(C) + gsg - 1) / gsg != (static_cast<long long>(K) + gsk - 1) / gsk) return FVM_ERR_ARG;
         p.gsg = gsg;
@@ -2412,12 +2412,13 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     // Halo mode for 3x3 stride-1 convolutions (dilation up to 4): an m-tile is a 16 x 8 patch of output pixels of one
     // image. Chosen when few patch pixels fall outside the image (they are computed and clipped by the store).
     uint32_t halo_bytes = 0;
-    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1 && !force_pair && !gsg) {
+    if (!p.tapk && R == 3 && S == 3 && sh == 1 && sw == 1 && dh == dw && dh <= 4 && force_halo != 2 && force_mt <= 1 && !force_pair) {
         const int ty = (P + HALO_TH - 1) / HALO_TH, tx = (Q + HALO_TW - 1) / HALO_TW;
         const double eff = static_cast<double>(P) * Q / (static_cast<double>(ty) * tx * BM);
         // by default only for inputs of one 64-channel chunk: there the taps are accumulated in the same order as in
-        // im2col mode (bit-identical results), and the measured gain is largest
-        if (force_halo == 1 || (eff >= 0.95 && p.cchunks == 1)) {
+        // im2col mode (bit-identical results), and the measured gain is largest (at 56 x 56, where an eighth of the
+        // patch rows fall outside the image: 23.7 us against 32.6 us for 64 -> 64 at batch 64)
+        if (force_halo == 1 || (eff >= 0.85 && p.cchunks == 1)) {
             p.halo = 1;
             p.halo_rows = HALO_TH + (R - 1) * dh;
             p.nh = 2;
@@ -2516,7 +2517,7 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     }
     SmemPlan sp;
     p.bres = 0;
-    if (!p.sk && !p.wb && !p.tapk && !p.pair && !gsg && force_bres != 2 && p.n_tiles <= st->sms) {
+    if (!p.sk && !p.wb && !p.tapk && !p.pair && force_bres != 2 && p.n_tiles <= st->sms) {
         const long long wbytes = static_cast<long long>(p.kblocks) * p.BN * BK * 2;
         const int cta_per_n = st->sms / p.n_tiles;
         const bool worth = p.m_tiles >= 2 * cta_per_n;

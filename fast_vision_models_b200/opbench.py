@@ -25,6 +25,7 @@ def _cl(t):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--groups", type=int, default=1, help="conv: groups (> 1: clfr3.gconv2 path)")
     ap.add_argument("op", choices=["conv", "stem", "dwconv", "layernorm", "gap", "se_scale", "maxpool", "up_argmax", "wbatch"])
     ap.add_argument("--n", type=int, default=64)
     ap.add_argument("--hw", type=int, nargs="+", default=[56], help="height [width]")
@@ -59,9 +60,19 @@ def main():
         nbytes = 2 * (N * H * W * C + K * C * R * R + K + N * P * Q * K * (2 if a.res else 1))
         flops = 2 * N * P * Q * K * C * R * R
 
-        def launch(i):
-            ops.conv_fused_into(xs[i], w, b, rs[i], (a.pad, a.pad), (a.stride, a.stride), a.act, ys[i],
-                                dilation=(a.dil, a.dil), tile_n=a.tile)
+        if a.groups > 1:
+            from . import fold
+            wg = _cl(rnd(K, C // a.groups, R, R, scale=0.05))
+            w_sg, gsg, gsk = fold.pack_grouped(wg, a.groups)
+            nbytes = 2 * (N * H * W * C + K * (C // a.groups) * R * R + K + N * P * Q * K)
+            flops = 2 * N * P * Q * K * (C // a.groups) * R * R
+
+            def launch(i):
+                ops.gconv2_packed_into(xs[i], w_sg, b, None, (a.stride, a.stride), (a.pad, a.pad), a.act, gsg, gsk, ys[i])
+        else:
+            def launch(i):
+                ops.conv_fused_into(xs[i], w, b, rs[i], (a.pad, a.pad), (a.stride, a.stride), a.act, ys[i],
+                                    dilation=(a.dil, a.dil), tile_n=a.tile)
     elif a.op == "stem":
         P, Q = (H + 2 * a.pad - R) // 2 + 1, (W + 2 * a.pad - R) // 2 + 1
         xs = [ops.input_nhwc8_split(torch.randn((N, 3, H, W), generator=g).to(dev)) for _ in range(nbuf)]
