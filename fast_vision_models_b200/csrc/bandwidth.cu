@@ -257,35 +257,59 @@ __global__ void se_gate_kernel(const void* __restrict__ g_in, const __half* __re
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int cv = C >> 3;
-    for (int j = warp; j < Cs; j += nwarps) {
-        const __half* row = w1 + static_cast<long long>(j) * C;
-        float acc = 0.f;
+    // FC1: a warp takes two rows of W1 at a time (eight 16-byte loads in flight per lane: the rows come from L2 and the
+    // loop is bound by that latency, not by arithmetic); each row's products are added in the same order as one by one
+    for (int j = 2 * warp; j < Cs; j += 2 * nwarps) {
+        const bool two = j + 1 < Cs;
+        const __half* row0 = w1 + static_cast<long long>(j) * C;
+        const __half* row1 = row0 + (two ? C : 0);
+        float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll 4
-        for (int v = lane; v < cv; v += 32) {     // unrolled: several 16-byte weight loads in flight per lane
-            float f[8];
-            to_f8(ldg16(row + v * 8), f);
+        for (int v = lane; v < cv; v += 32) {
+            float f0[8], f1[8];
+            to_f8(ldg16(row0 + v * 8), f0);
+            to_f8(ldg16(row1 + v * 8), f1);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc = fmaf(f[k], g[v * 8 + k], acc);
+            for (int k = 0; k < 8; ++k) {
+                acc0 = fmaf(f0[k], g[v * 8 + k], acc0);
+                acc1 = fmaf(f1[k], g[v * 8 + k], acc1);
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        for (int o = 16; o > 0; o >>= 1) {
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+        }
         if (lane == 0) {
-            if (b1) acc += __half2float(b1[j]);
-            h[j] = __half2float(__float2half_rn(act_f(acc, act)));
+            if (b1) acc0 += __half2float(b1[j]);
+            h[j] = __half2float(__float2half_rn(act_f(acc0, act)));
+            if (two) {
+                if (b1) acc1 += __half2float(b1[j + 1]);
+                h[j + 1] = __half2float(__float2half_rn(act_f(acc1, act)));
+            }
         }
     }
     __syncthreads();
+    // FC2: one output per thread and pass; the row of W2 (Cs halves) is fetched with all its loads in flight
     const int sv = Cs >> 3;
     const int per = (C + gridDim.y - 1) / gridDim.y, c_end = min(C, static_cast<int>(blockIdx.y + 1) * per);
     for (int c = blockIdx.y * per + threadIdx.x; c < c_end; c += blockDim.x) {
         const __half* row = w2 + static_cast<long long>(c) * Cs;
         float acc = 0.f;
-#pragma unroll 4
-        for (int v = 0; v < sv; ++v) {
-            float f[8];
-            to_f8(ldg16(row + v * 8), f);
+        for (int v0 = 0; v0 < sv; v0 += 8) {
+            uint4 q[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc = fmaf(f[k], h[v * 8 + k], acc);
+            for (int u = 0; u < 8; ++u)
+                if (v0 + u < sv) q[u] = ldg16(row + (v0 + u) * 8);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (v0 + u < sv) {
+                    float f[8];
+                    to_f8(q[u], f);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc = fmaf(f[k], h[(v0 + u) * 8 + k], acc);
+                }
+            }
         }
         if (b2) acc += __half2float(b2[c]);
         s_out[n * C + c] = __float2half_rn(acc);
@@ -726,7 +750,9 @@ static int se_gate_launch(const void* g, int slots, const void* w1, const void* 
     const int sms = st ? st->sms : 148;
     int split = 1;                       // blocks per image: fill the GPU when the batch alone does not
     while (split < 4 && N * split * 2 <= 2 * sms && C / (split * 2) >= 256) split *= 2;
-    se_gate_kernel<<<dim3(N, split), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+    // large layers: 1024 threads (the loops are latency-bound: more rows / outputs in flight per SM)
+    const int threads = static_cast<long long>(C) * Cs >= 16 * 1024 ? 1024 : 256;
+    se_gate_kernel<<<dim3(N, split), threads, smem, static_cast<cudaStream_t>(stream)>>>(
         g, static_cast<const __half*>(w1), static_cast<const __half*>(b1), static_cast<const __half*>(w2),
         static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale, slots, sgroups);
     FVM_LAUNCH_CHECK();

@@ -26,7 +26,7 @@ def _cl(t):
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--groups", type=int, default=1, help="conv: groups (> 1: clfr3.gconv2 path)")
-    ap.add_argument("op", choices=["conv", "stem", "dwconv", "layernorm", "gap", "se_scale", "maxpool", "up_argmax", "wbatch"])
+    ap.add_argument("op", choices=["conv", "stem", "dwconv", "layernorm", "gap", "se_scale", "se_gate", "maxpool", "up_argmax", "wbatch"])
     ap.add_argument("--n", type=int, default=64)
     ap.add_argument("--hw", type=int, nargs="+", default=[56], help="height [width]")
     ap.add_argument("--c", type=int, default=64)
@@ -119,6 +119,15 @@ def main():
 
             def launch(i):
                 ops.global_avgpool(xs[i])
+        elif a.op == "se_gate":
+            # the two small FCs of a squeeze-excite block fed by the fused squeeze: --k = squeeze channels, --hw = slots
+            Cs = a.k
+            parts = [torch.randn((N, H, C), generator=g).to(dev) for _ in range(nbuf)]
+            w1, b1, w2, b2 = rnd(Cs, C, scale=0.05), rnd(Cs, scale=0.1), rnd(C, Cs, scale=0.05), rnd(C, scale=0.1)
+            nbytes = 4 * N * H * C + 2 * (2 * C * Cs + C + Cs) + 2 * N * C
+
+            def launch(i):
+                ops.se_gate_pooled(parts[i], 100, w1, b1, w2, b2, 3)
         elif a.op == "se_scale":
             s_ = rnd(N, C, 1, 1)
             nbytes = 4 * N * H * W * C
