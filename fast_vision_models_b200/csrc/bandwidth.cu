@@ -748,10 +748,11 @@ static int se_gate_launch(const void* g, int slots, const void* w1, const void* 
     if (smem > 48 * 1024) return FVM_ERR_ARG;
     DeviceState* st = device_state();
     const int sms = st ? st->sms : 148;
-    int split = 1;                       // blocks per image: fill the GPU when the batch alone does not
-    while (split < 4 && N * split * 2 <= 2 * sms && C / (split * 2) >= 256) split *= 2;
-    // large layers: 1024 threads (the loops are latency-bound: more rows / outputs in flight per SM)
+    // large layers: 1024 threads (the loops are latency-bound: more rows / outputs in flight per SM), one block per SM
     const int threads = static_cast<long long>(C) * Cs >= 16 * 1024 ? 1024 : 256;
+    const int resident = threads == 1024 ? sms : 2 * sms;
+    int split = 1;                       // blocks per image: fill the GPU when the batch alone does not, in one wave
+    while (split < 4 && N * split * 2 <= resident && C / (split * 2) >= 256) split *= 2;
     se_gate_kernel<<<dim3(N, split), threads, smem, static_cast<cudaStream_t>(stream)>>>(
         g, static_cast<const __half*>(w1), static_cast<const __half*>(b1), static_cast<const __half*>(w2),
         static_cast<const __half*>(b2), static_cast<__half*>(s), C, Cs, act, mean_scale, slots, sgroups);
