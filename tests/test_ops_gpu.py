@@ -339,6 +339,25 @@ def test_conv_chain_with_aliased_buffers_falls_back_to_stream_order():
     assert torch.equal(y1, y1_ref) and torch.equal(xin, y2_ref)
 
 
+@pytest.mark.parametrize("M,C,K,act,res,scale", [(197 * 4, 384, 1536, 5, False, False), (197 * 4, 1536, 384, 0, True, True),
+                                                  (64, 2048, 1000, 0, False, False), (1000, 96, 40, 3, True, False)])
+def test_linear_gemm_matches_oracle(M, C, K, act, res, scale):
+    # ops.linear: the row-major GEMM view the reference's transformer blocks use (`_lin`, classification/fast/vit.py:56-64):
+    # y[M,K] = act((x[M,C] @ w[K,C]^T + bias) * scale + res), on the convolution kernel as a 1x1 convolution over M pixels
+    x, w, b = gen((M, C), 91), gen((K, C), 92, 0.05), gen((K,), 93, 0.1)
+    r = gen((M, K), 94) if res else None
+    sc = (torch.rand(K, generator=torch.Generator().manual_seed(95)) + 0.5) if scale else None
+    y = ops.linear(x.to(DEV), w.to(DEV), b.to(DEV), None if r is None else r.to(DEV), act,
+                   None if sc is None else sc.to(DEV))
+    assert ops.last_status() == 0
+    v = x.float() @ w.float().t() + b.float()
+    if sc is not None:
+        v = v * sc
+    if r is not None:
+        v = v + r.float()
+    close(y, R.act_ref(v, act).half())
+
+
 GCONV_CASES = [
     # N, H, W, C, K, groups, R, pad, stride, act
     (4, 28, 28, 128, 128, 32, 3, 1, 1, 1),      # ResNeXt-50 32x4d stage 1: 4 channels per group, 16 groups per run
