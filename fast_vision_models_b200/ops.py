@@ -43,8 +43,13 @@ def init(device: Optional[torch.device] = None) -> None:
     """Per-device set-up; must run before the first launch on a device and before any CUDA-graph capture."""
     if not torch.cuda.is_available():
         raise FvmError("fvm_b200 needs a CUDA device (sm_100a); there is no CPU path")
-    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    cur = torch.cuda.current_device()
+    dev = torch.device("cuda", cur) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else cur
+    if idx != cur:
+        # the library launches on the current device's stream: a tensor of another device would be a wild pointer there
+        raise FvmError(f"fvm_b200: tensor on cuda:{idx} but the current device is cuda:{cur}; "
+                       f"wrap the call in torch.cuda.device({idx})")
     if idx in _initialised_devices:
         return
     with torch.cuda.device(idx):

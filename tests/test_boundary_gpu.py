@@ -215,3 +215,32 @@ def test_bounded_wait_runs_out_reports_and_leaves_the_device_usable():
     with pytest.raises(ops.FvmError):
         runner(t)
     assert ops.last_status() == 0
+
+
+def test_two_devices_in_one_process():
+    # per-device set-up (kernel attributes, status word, scratch, cluster capacity) and launches on a second GPU of the
+    # same process; a tensor of a device that is not current is refused before anything is launched
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    x, w, b = gen((4, 64, 28, 28), 1), gen((128, 64, 3, 3), 2, 0.05), gen((128,), 3, 0.1)
+    wd, bd = gen((64, 1, 3, 3), 4, 0.2), gen((64,), 5, 0.1)
+    ref = R.conv_fused_ref(x, w, b, None, (1, 1), (1, 1), 1)
+    ref_dw = R.dwconv_ref(x, wd[:, 0].permute(1, 2, 0).contiguous(), bd, (1, 1), (1, 1), 3)
+    for _round in range(2):
+        for d in (0, 1):
+            dev = f"cuda:{d}"
+            with torch.cuda.device(d):
+                xd = x.to(dev).contiguous(memory_format=torch.channels_last)
+                wdev = w.to(dev).contiguous(memory_format=torch.channels_last)
+                y = ops.conv_fused(xd, wdev, b.to(dev), None, (1, 1), (1, 1), 1)
+                close(y, ref)
+                if ops.query(4) > 0:
+                    yp = ops.conv_fused(xd, wdev, b.to(dev), None, (1, 1), (1, 1), 1, tile_n=(1 << 30) | 128)
+                    assert torch.equal(yp, y)
+                ydw = ops.dwconv(xd, wd[:, 0].permute(1, 2, 0).contiguous().to(dev), bd.to(dev), (1, 1), (1, 1), 3)
+                close(ydw, ref_dw)
+                assert ops.last_status() == 0
+    with torch.cuda.device(0):
+        with pytest.raises(ops.FvmError):
+            ops.conv_fused(x.to("cuda:1").contiguous(memory_format=torch.channels_last),
+                           w.to("cuda:1").contiguous(memory_format=torch.channels_last), None, None, (1, 1), (1, 1), 1)
