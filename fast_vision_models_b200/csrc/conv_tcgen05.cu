@@ -103,6 +103,7 @@ struct ConvParams {
     int sk;
     int gsg, gsk;  // grouped convolution: input / output channels per super-group (0: dense), see conv2d_launch
     FastDiv div_gsk;
+    int hints;     // L2 eviction hints: bit 0 input is dead after this layer, bit 1 residual is, bit 2 keep the output
     int rev;       // walk the m-tiles from the last to the first (see fvm_conv2d_f16_tile)
     int pair;      // conv_pair_kernel: two CTAs per tile of 256 pixels x BN channels (m_tiles counts 256-pixel tiles)
     uint32_t sk_units;
@@ -380,6 +381,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             auto load_w = [&](uint32_t dst, uint32_t bar, int c0, int c1, int c2) {
                 tma_load_3d(dst, &tmap_b, bar, c0, c1, c2);
             };
+            const unsigned long long pol_a = (p.hints & 1) ? l2_policy_evict_first() : 0ull;
+            const unsigned long long pol_r = (p.hints & 2) ? l2_policy_evict_first() : 0ull;
             if (p.tapk) {
                 // weights of every tap (taps past R*S are out of bounds of the weight tensor: zero-filled)
                 mbar_expect_tx(bres_full_bar, bres_bytes);
@@ -452,9 +455,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         for (int sub = 0; sub < nsub; ++sub) {
                             const uint32_t dst = epi_base + static_cast<uint32_t>(e) * epi_bytes +
                                                  static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES;
-                            if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg);
+                            if (p.halo) tma_load_4d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, hx0, hy0, himg, pol_r);
                             else if (p.wb) tma_load_3d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, wb_row0 + mt * BM, wb_img);
-                            else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM);
+                            else tma_load_2d(dst, &tmap_r, res_full_bar(e), n0 + sub * 64, m0 + mt * BM, pol_r);
                         }
                     if (++e == p.nepi) e = 0;
                 }
@@ -473,7 +476,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                         hx0 + p.stem_xlo, 0, 2 * hy0 - p.ph, himg);
                         else
                             tma_load_4d(halo_base + static_cast<uint32_t>(hs) * halo_bytes, &tmap_a, hfull_bar(hs), goff + hc * BK,
-                                        hx0 - p.pw, hy0 - p.ph, himg);
+                                        hx0 - p.pw, hy0 - p.ph, himg, pol_a);
                         if (++hs == p.nh) { hs = 0; hphase ^= 1u; }
                         if (p.bres) continue;
                         for (int tp = 0; tp < p.taps; ++tp) {
@@ -527,13 +530,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (!p.bres && !armed) load_w(b_dst, full_bar(stage), cc * BK, tap, n0 + wb_img * p.K);
                     if (p.im2col) {
                         tma_load_im2col_4d(a_dst, &tmap_a, full_bar(stage), goff + cc * BK, w0, h0, img,
-                                           static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                                           static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh), pol_a);
                     } else if (p.wb) {
                         tma_load_3d(a_dst, &tmap_a, full_bar(stage), cc * BK, wb_row0, wb_img);
                     } else {
                         for (int l = 0; l < p.a_loads; ++l)
                             tma_load_2d(a_dst + static_cast<uint32_t>(l * p.a_rows) * 128u, &tmap_a, full_bar(stage),
-                                        goff + cc * BK, m0 + l * p.a_rows);
+                                        goff + cc * BK, m0 + l * p.a_rows, pol_a);
                     }
                     if (++cc == p.cchunks) {
                         cc = 0;
@@ -820,6 +823,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (elect_one()) {
             uint32_t e_phase = 0;   // one parity bit per staging buffer
             int e = 0;
+            const unsigned long long pol_y = (p.hints & 4) ? l2_policy_evict_last() : 0ull;
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int m_tile, n_tile;
@@ -856,7 +860,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         tma_store_2d(&tmap_y,
                                      epi_base + static_cast<uint32_t>(e) * epi_bytes +
                                          static_cast<uint32_t>(mt * p.nsub + sub) * SUB_BYTES,
-                                     n0 + sub * 64, m0 + mt * BM);
+                                     n0 + sub * 64, m0 + mt * BM, pol_y);
                 tma_store_commit();
                 tma_store_wait_read();          // the staging buffer has been read out: it may be refilled
                 mbar_arrive(epi_free_bar(e));
@@ -1365,6 +1369,8 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int PQ = p.P * p.Q;
             const uint32_t lead_full0 = mapa_shared(full_bar(0), 0);    // the leader's `full` barriers, 8 bytes apart
             const int b_row0 = static_cast<int>(rank) * (p.BN / 2);     // this CTA's half of the n-tile
+            const unsigned long long pol_a = (p.hints & 1) ? l2_policy_evict_first() : 0ull;
+            const unsigned long long pol_r = (p.hints & 2) ? l2_policy_evict_first() : 0ull;
             int m0, n0;
             // Weights are constants: the B halves of the first k-blocks (one per pipeline stage) are requested before the
             // wait for the preceding kernel, their barriers armed for the whole stage; the A tiles follow after the wait.
@@ -1393,7 +1399,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     mbar_expect_tx(res_full_bar(e), static_cast<uint32_t>(nsub) * SUB_BYTES);
                     for (int sub = 0; sub < nsub; ++sub)      // rows past M: zero fill
                         tma_load_2d(epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
-                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0);
+                                    &tmap_r, res_full_bar(e), n0 + sub * 64, m0, pol_r);
                     if (++e == p.nepi) e = 0;
                 }
                 // a peer whose 128 rows lie past the last pixel loads the leader's rows instead (its results are dropped)
@@ -1424,9 +1430,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     if (p.im2col)
                         tma_pair_load_im2col_4d(a_dst, &tmap_a, bar, cc * BK, w0, h0, img,
-                                                static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh));
+                                                static_cast<uint16_t>(s * p.dw), static_cast<uint16_t>(r * p.dh), pol_a);
                     else
-                        tma_pair_load_2d(a_dst, &tmap_a, bar, cc * BK, ml);
+                        tma_pair_load_2d(a_dst, &tmap_a, bar, cc * BK, ml, pol_a);
                     if (++cc == p.cchunks) {
                         cc = 0;
                         ++tap;
@@ -1550,6 +1556,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (elect_one()) {
             uint32_t e_phase = 0;
             int e = 0;
+            const unsigned long long pol_y = (p.hints & 4) ? l2_policy_evict_last() : 0ull;
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             int m0, n0;
@@ -1564,7 +1571,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (m0 < p.M) {
                     for (int sub = 0; sub < nsub; ++sub)
                         tma_store_2d(&tmap_y, epi_base + static_cast<uint32_t>(e) * epi_bytes + static_cast<uint32_t>(sub) * SUB_BYTES,
-                                     n0 + sub * 64, m0);
+                                     n0 + sub * 64, m0, pol_y);
                     tma_store_commit();
                     tma_store_wait_read();
                 }
@@ -2461,6 +2468,18 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
         if (rev_rule && R == 1 && S == 1 && sh == 1 && sw == 1 && !res && C >= 4 * K &&
             static_cast<long long>(p.M) * ldx * 2 > 64ll * 1024 * 1024)
             p.rev = 1;
+    }
+    // L2 eviction hints (performance only). A convolution with a fused residual closes a block: its residual operand
+    // and its input are dead after it (evict first), its output is read twice soon (by the next block's first layer
+    // and as that block's residual: evict last); the input of a 3x3 layer has a single reader in the networks this
+    // serves. Measured inside a ResNet-50 forward at batch 64: stage 1 (103 MB tensors against a 126 MB L2) ends
+    // 5-10 us earlier, 1.100 -> 1.079 ms per forward; FVM_B200_L2_HINTS=0 switches the hints off.
+    {
+        static const int l2_hints = [] { const char* v = getenv("FVM_B200_L2_HINTS"); return (v && v[0] == '0') ? 0 : 1; }();
+        if (l2_hints) {
+            if (res) p.hints |= 2 | 4 | 1;
+            if (R == 3 && S == 3) p.hints |= 1;
+        }
     }
     p.has_res = res != nullptr;
     p.bias = static_cast<const __half*>(bias);

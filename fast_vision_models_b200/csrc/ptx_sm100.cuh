@@ -112,7 +112,27 @@ __device__ __forceinline__ uint32_t fastdiv(uint32_t n, const FastDiv& f) {
 __device__ __forceinline__ void tma_prefetch_desc(const void* desc) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(desc)) : "memory");
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1) {
+// L2 eviction priorities for bulk loads (0 = none): evict_first for data that is dead after this read, so that it does
+// not push out lines a later kernel will want; evict_last for the opposite.
+__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ unsigned long long l2_policy_evict_last() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1,
+                                            unsigned long long policy = 0) {
+    if (policy) {
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
+            : "memory");
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
@@ -124,7 +144,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* desc, uint
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2, int c3) {
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1, int c2, int c3,
+                                            unsigned long long policy = 0) {
+    if (policy) {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+            : "memory");
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
@@ -139,7 +167,16 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* desc, uint
 // im2col-mode load of NHWC activations: coordinates (c, w, h, n) of the first pixel's filter-window origin, plus the
 // filter tap offset (off_w, off_h) in input pixels (tap index times dilation).
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* desc, uint32_t bar, int c, int w, int h,
-                                                   int n, uint16_t off_w, uint16_t off_h) {
+                                                   int n, uint16_t off_w, uint16_t off_h, unsigned long long policy = 0) {
+    if (policy) {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8}, %9;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+            "h"(off_h), "l"(policy)
+            : "memory");
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
@@ -149,7 +186,13 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* des
 }
 
 // Bulk tensor store shared -> global (clipped at the tensor bounds), tracked by the issuing thread's bulk groups.
-__device__ __forceinline__ void tma_store_2d(const void* desc, uint32_t src, int c0, int c1) {
+__device__ __forceinline__ void tma_store_2d(const void* desc, uint32_t src, int c0, int c1, unsigned long long policy = 0) {
+    if (policy) {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+                     ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(src), "r"(c0), "r"(c1), "l"(policy)
+                     : "memory");
+        return;
+    }
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(src), "r"(c0), "r"(c1)
                  : "memory");
@@ -532,7 +575,15 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t by
 }
 // Bulk tensor loads whose completion is counted on an mbarrier of either CTA of the pair (`bar`: a shared::cluster
 // address); the destination is this CTA's shared memory: each CTA fetches its own boxes.
-__device__ __forceinline__ void tma_pair_load_2d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1) {
+__device__ __forceinline__ void tma_pair_load_2d(uint32_t dst, const void* desc, uint32_t bar, int c0, int c1,
+                                                 unsigned long long policy = 0) {
+    if (policy) {
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "l"(policy)
+            : "memory");
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
@@ -545,7 +596,16 @@ __device__ __forceinline__ void tma_pair_load_3d(uint32_t dst, const void* desc,
         : "memory");
 }
 __device__ __forceinline__ void tma_pair_load_im2col_4d(uint32_t dst, const void* desc, uint32_t bar, int c, int w, int h,
-                                                        int n, uint16_t off_w, uint16_t off_h) {
+                                                        int n, uint16_t off_w, uint16_t off_h, unsigned long long policy = 0) {
+    if (policy) {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8}, %9;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+            "h"(off_h), "l"(policy)
+            : "memory");
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
