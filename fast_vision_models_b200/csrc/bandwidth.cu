@@ -677,9 +677,10 @@ extern "C" int fvm_input_nhwc8_split_f16(const void* x, void* y, int N, int C, i
 // 3x3 window with the loops unrolled: the (up to) nine 16-byte loads of a thread are independent and all in flight
 // together; the general kernel above issues them one by one behind its bounds checks. Same mapping, same bits.
 __global__ void maxpool3x3_kernel(const __half* __restrict__ x, __half* __restrict__ y, int H, int W, int C, int sh, int sw,
-                                  int ph, int pw, int P, int Q, long long total) {
-    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+                                  int ph, int pw, int P, int Q, long long total, int rev) {
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= total) return;
+    if (rev) i = total - 1 - i;      // last outputs first: see fvm_maxpool_f16
     const int cv = C >> 3;
     const int v = static_cast<int>(i % cv);
     long long t = i / cv;
@@ -716,8 +717,12 @@ extern "C" int fvm_maxpool_f16(const void* x, void* y, int N, int H, int W, int 
         return FVM_ERR_ARG;
     if (kh == 3 && kw == 3) {
         const long long total3 = static_cast<long long>(N) * P * Q * (C >> 3);
+        // An input larger than half of the L2 was written front to back by the kernel before: its tail is what the
+        // L2 still holds, so the pool walks from the last output to the first (FVM_B200_REVERSE=0: never).
+        static const int rev_rule = [] { const char* v = getenv("FVM_B200_REVERSE"); return (v && v[0] == '0') ? 0 : 1; }();
+        const int rev = rev_rule && static_cast<long long>(N) * H * W * C * 2 > 64ll * 1024 * 1024;
         maxpool3x3_kernel<<<blocks_for(total3, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-            static_cast<const __half*>(x), static_cast<__half*>(y), H, W, C, sh, sw, ph, pw, P, Q, total3);
+            static_cast<const __half*>(x), static_cast<__half*>(y), H, W, C, sh, sw, ph, pw, P, Q, total3, rev);
         FVM_LAUNCH_CHECK();
     }
     const long long total = static_cast<long long>(N) * P * Q * (C >> 3);
