@@ -2469,18 +2469,6 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
             static_cast<long long>(p.M) * ldx * 2 > 64ll * 1024 * 1024)
             p.rev = 1;
     }
-    // L2 eviction hints (performance only). A convolution with a fused residual closes a block: its residual operand
-    // and its input are dead after it (evict first), its output is read twice soon (by the next block's first layer
-    // and as that block's residual: evict last); the input of a 3x3 layer has a single reader in the networks this
-    // serves. Measured inside a ResNet-50 forward at batch 64: stage 1 (103 MB tensors against a 126 MB L2) ends
-    // 5-10 us earlier, 1.100 -> 1.079 ms per forward; FVM_B200_L2_HINTS=0 switches the hints off.
-    {
-        static const int l2_hints = [] { const char* v = getenv("FVM_B200_L2_HINTS"); return (v && v[0] == '0') ? 0 : 1; }();
-        if (l2_hints) {
-            if (res) p.hints |= 2 | 4 | 1;
-            if (R == 3 && S == 3) p.hints |= 1;
-        }
-    }
     p.has_res = res != nullptr;
     p.bias = static_cast<const __half*>(bias);
     p.scale = scale;
@@ -2560,6 +2548,24 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
     size_t smem = sp.bytes;
     if (smem < 120 * 1024) smem = 120 * 1024;
 
+    // L2 eviction hints (performance only). A convolution with a fused residual closes a block: its residual operand is
+    // dead after it (evict first) and its output is read twice soon, by the next block's first layer and as that block's
+    // residual (evict last, if it can stay: at most 112 MB against the 126 MB L2). The input is fetched evict-first only
+    // where the kernel reads each element once or in one burst (staged patches; a 1x1 layer with a single n-tile that
+    // closes a block): im2col loads and several n-tiles come back to the same lines and must find them in the L2
+    // (measured: hints on im2col inputs cost DeepLabV3 5 %). Inside a ResNet-50 forward at batch 64 stage 1 (103 MB
+    // tensors) ends 5-10 us earlier, 1.100 -> 1.08 ms per forward; ConvNeXt-T 1.93 -> 1.89 ms. FVM_B200_L2_HINTS=0: off.
+    {
+        static const int l2_hints = [] { const char* v = getenv("FVM_B200_L2_HINTS"); return (v && v[0] == '0') ? 0 : 1; }();
+        if (l2_hints) {
+            if (res) {
+                p.hints |= 2;
+                if (static_cast<long long>(p.M) * ldy * 2 <= 112ll * 1024 * 1024) p.hints |= 4;
+                if (R == 1 && S == 1 && p.n_tiles == 1) p.hints |= 1;
+            }
+            if (p.halo == 1) p.hints |= 1;
+        }
+    }
     CUtensorMap tmap_a, tmap_b, tmap_r, tmap_y;
     if (p.halo) {
         // output / residual as (K, Q, P, N): 64-channel x 8-column x 16-row boxes (clipped at the image border)
