@@ -161,9 +161,11 @@ def reference_arm(args, rank):
 
 
 def timed_windows(step_fn, steps: int, barrier, target_s: float = TARGET_TIMED_SECONDS, min_windows: int = 10,
-                  max_windows: int = 200):
+                  max_windows: int = 200, agree=lambda v: v):
     """R windows of exactly `steps` calls of step_fn(i), each bracketed by barrier() and timed with CUDA events.
-    Returns the list of window times in ms (this rank)."""
+    Returns the list of window times in ms (this rank). R follows from the first window's time; `agree` maps that time
+    to a value all ranks share (its maximum over ranks), so that every rank runs the same number of windows and
+    barriers."""
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -172,7 +174,7 @@ def timed_windows(step_fn, steps: int, barrier, target_s: float = TARGET_TIMED_S
     e1.record()
     barrier()
     first = e0.elapsed_time(e1)
-    windows = int(min(max_windows, max(min_windows, target_s * 1e3 / max(first, 1e-3))))
+    windows = int(min(max_windows, max(min_windows, target_s * 1e3 / max(agree(first), 1e-3))))
     times = [first]
     for _ in range(windows - 1):
         barrier()
@@ -319,7 +321,10 @@ def main():
     def step_dev(i):
         out[0] = m.model(xs[i % NBUF])
 
-    win_dev = timed_windows(step_dev, steps, barrier)
+    def agree(v):        # the same number on every rank
+        return parallel.max_over_ranks([float(v)], device=dev)[0]
+
+    win_dev = timed_windows(step_dev, steps, barrier, agree=agree)
     clocks = sampler.stop()
     y = out[0]
     status = ops.last_status()
@@ -360,7 +365,7 @@ def main():
         torch.cuda.synchronize()
         wins = []
         barrier()
-        n_win = max(10, min(200, int(TARGET_TIMED_SECONDS * 1e3 / max(statistics.median(win_dev), 1e-3))))
+        n_win = max(10, min(200, int(TARGET_TIMED_SECONDS * 1e3 / max(agree(statistics.median(win_dev)), 1e-3))))
         for _ in range(n_win):
             barrier()
             t0 = time.perf_counter()
