@@ -160,6 +160,12 @@ def reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def window_count(first_ms: float, target_s: float, min_windows: int, max_windows: int, agree=lambda v: v) -> int:
+    """How many windows fill `target_s` seconds, from the time of the first one. `agree` turns this rank's time into a
+    value all ranks share, so that all of them get the same count (each window is bracketed by collective barriers)."""
+    return int(min(max_windows, max(min_windows, target_s * 1e3 / max(agree(first_ms), 1e-3))))
+
+
 def timed_windows(step_fn, steps: int, barrier, target_s: float = TARGET_TIMED_SECONDS, min_windows: int = 10,
                   max_windows: int = 200, agree=lambda v: v):
     """R windows of exactly `steps` calls of step_fn(i), each bracketed by barrier() and timed with CUDA events.
@@ -174,7 +180,7 @@ def timed_windows(step_fn, steps: int, barrier, target_s: float = TARGET_TIMED_S
     e1.record()
     barrier()
     first = e0.elapsed_time(e1)
-    windows = int(min(max_windows, max(min_windows, target_s * 1e3 / max(agree(first), 1e-3))))
+    windows = window_count(first, target_s, min_windows, max_windows, agree)
     times = [first]
     for _ in range(windows - 1):
         barrier()
@@ -365,7 +371,7 @@ def main():
         torch.cuda.synchronize()
         wins = []
         barrier()
-        n_win = max(10, min(200, int(TARGET_TIMED_SECONDS * 1e3 / max(agree(statistics.median(win_dev)), 1e-3))))
+        n_win = window_count(statistics.median(win_dev), TARGET_TIMED_SECONDS, 10, 200, agree)
         for _ in range(n_win):
             barrier()
             t0 = time.perf_counter()

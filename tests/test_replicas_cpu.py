@@ -40,6 +40,31 @@ def test_two_rank_shard_gather_and_max():
     assert out[0] and out[1]
 
 
+def _window_worker(rank, world_size, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world_size)
+    try:
+        import bench
+        first = 20.0 + 7.0 * rank                # the ranks time their first window differently
+        alone = bench.window_count(first, 2.0, 10, 200)
+        shared = bench.window_count(first, 2.0, 10, 200, agree=lambda v: parallel.max_over_ranks([float(v)])[0])
+        out[rank] = (alone, shared)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_all_ranks_run_the_same_number_of_timed_windows():
+    # bench.py brackets every timed window with a barrier: a window count taken from each rank's own first window would
+    # differ between ranks (100 against 74 here) and leave them in different collectives
+    port = _free_port()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_window_worker, args=(2, port, out), nprocs=2, join=True)
+    assert out[0][0] != out[1][0]
+    assert out[0][1] == out[1][1] == 74
+
+
 def test_shard_ranges_cover_everything_once():
     for n in (0, 1, 7, 64, 65):
         for ws in (1, 2, 3, 8):
