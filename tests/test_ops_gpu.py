@@ -213,6 +213,29 @@ def test_conv_cta_pairs_match_oracle_and_single_cta_kernel(case):
     assert torch.equal(y_pair, y_one)
 
 
+@pytest.mark.parametrize("case", [
+    # N, H, W, C, K, R, pad, stride, res, act: shapes whose default tile is a CTA pair of an unusual width
+    (8, 14, 14, 64, 72, 1, 0, 1, False, 1),        # one 96-wide tile, 24 columns of padding
+    (8, 14, 14, 512, 200, 1, 0, 1, False, 3),      # 224-wide tile, SiLU
+    (8, 14, 14, 128, 136, 3, 1, 1, True, 1),       # two 128-wide tiles, the second 8 channels wide, residual
+    (4, 28, 28, 96, 80, 3, 1, 2, False, 5),        # stride 2, GELU, 96-wide tile
+    (2, 7, 7, 2048, 1000, 1, 0, 1, False, 0),      # eight tiles, ragged last one
+    (1, 5, 5, 24, 64, 3, 1, 1, True, 1),           # fewer rows than one CTA's 128: the peer CTA has none
+])
+def test_conv_default_tiles_with_odd_channel_counts(case):
+    N, H, W, C, K, Rr, pad, stride, res, act = case
+    x, w, b = gen((N, C, H, W), 41), gen((K, C, Rr, Rr), 42, 0.03), gen((K,), 43, 0.1)
+    P = (H + 2 * pad - Rr) // stride + 1
+    Q = (W + 2 * pad - Rr) // stride + 1
+    r = gen((N, K, P, Q), 44) if res else None
+    y = ops.conv_fused(cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (stride, stride), act)
+    assert ops.last_status() == 0
+    close(y, R.conv_fused_ref(x, w, b, r, (pad, pad), (stride, stride), act))
+    y1 = ops.conv_fused(cl(x), cl(w), b.to(DEV), None if r is None else cl(r), (pad, pad), (stride, stride), act,
+                        tile_n=(2 << 28) | (2 << 26) | (2 << 24) | 64)            # single-CTA kernel, 64-wide tiles
+    assert torch.equal(y, y1)
+
+
 def test_conv_cta_pairs_are_refused_where_they_do_not_apply():
     x8, w8 = cl(gen((2, 8, 32, 32), 1)), cl(gen((64, 8, 7, 7), 2, 0.05))
     with pytest.raises(ops.FvmError):
