@@ -14,8 +14,8 @@ Counterpart of the reference's `fuse_graph` / `fuse_dw` / `replace_bn_act` / `re
   AdaptiveAvgPool2d(1), Linear                    ==> this library's global average pool and GEMM modules
   first conv on an image with fewer than 8 channels: weights zero-padded to 8, input through torch.ops.clf.input_nhwc8
 
-BatchNorm and the weights are folded in fp32 and rounded once (fold.py). Everything the patterns do not cover (grouped
-convolutions, channel counts that are not multiples of 8, concatenations, ...) stays an aten op on fp16 channels-last
+BatchNorm and the weights are folded in fp32 and rounded once (fold.py). Everything the patterns do not cover
+(channel counts that are not multiples of 8, concatenations, ...) stays an aten op on fp16 channels-last
 tensors, as in the reference. `classification/fast.py` keeps hand-built compilers for ResNet, EfficientNet and ConvNeXt
 (per-layer tile tuning, fused squeeze); this pass is what every other architecture gets.
 """
