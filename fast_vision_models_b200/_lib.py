@@ -171,6 +171,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "fvm_conv2d_f16_tile": ([_P] * 6 + [_I] * 13 + [_L] * 3 + [_I, _I, _P], _I),
         "fvm_conv2d_f16_pad": ([_P] * 6 + [_I] * 13 + [_L] * 3 + [_I, _I, _I, _I, _P], _I),
         "fvm_conv_chain_f16": ([ctypes.POINTER(ChainLayer), _I, _P], _I),
+        "fvm_conv_dual_f16": ([_P] * 8 + [_L] + [_I] * 3 + [_L] * 4 + [_I, _I, _P], _I),
         "fvm_gconv2d_f16": ([_P] * 5 + [_I] * 13 + [_L] * 3 + [_I, _I, _I, _P], _I),
         "fvm_dwconv_f16": ([_P] * 5 + [_I] * 12 + [_L] * 2 + [_I, _P], _I),
         "fvm_dwconv_pool_slots": ([_I] * 12, _I),
@@ -210,7 +211,7 @@ def _declare(lib: ctypes.CDLL) -> None:
 
 OPTIONAL_SIGNATURES: dict = {}
 
-EXPORTED = ["fvm_init", "fvm_query", "fvm_last_status", "fvm_selftest_wait_expiry", "fvm_conv2d_f16", "fvm_conv2d_f16_tile", "fvm_conv2d_f16_pad", "fvm_conv_chain_f16", "fvm_gconv2d_f16", "fvm_dwconv_f16", "fvm_dwconv_pool_slots", "fvm_se_gate_pooled_f16", "fvm_maxpool_f16",
+EXPORTED = ["fvm_init", "fvm_query", "fvm_last_status", "fvm_selftest_wait_expiry", "fvm_conv2d_f16", "fvm_conv2d_f16_tile", "fvm_conv2d_f16_pad", "fvm_conv_chain_f16", "fvm_conv_dual_f16", "fvm_gconv2d_f16", "fvm_dwconv_f16", "fvm_dwconv_pool_slots", "fvm_se_gate_pooled_f16", "fvm_maxpool_f16",
             "fvm_avgpool_f16", "fvm_gap_scratch_floats", "fvm_global_avgpool_f16", "fvm_global_avgpool_f16_noalloc",
             "fvm_global_avgpool_f16_noalloc_max_floats", "fvm_se_gate_f16",
             "fvm_se_scale_f16", "fvm_gate_weights_f16", "fvm_conv1x1_wbatch_f16", "fvm_layernorm_cl_f16", "fvm_input_nhwc8_f32", "fvm_input_nhwc8_split_f32",

@@ -37,6 +37,9 @@ from ..runtime import GraphRunner
 # because a layer of these stages has about as many tiles as there are CTA pairs and the next layer's tiles wait for
 # them just as a next launch would. Off unless asked for.
 CHAIN_RESNET = os.environ.get("FVM_B200_CHAIN_RESNET", "0") == "1"
+# The last convolution of a bottleneck block and the first of the next block as one launch (ops.pw_dual) where the
+# shapes allow it (64 -> 256 -> 64 channels: the first stage of a ResNet-50/101/152). FVM_B200_DUAL=0: one launch each.
+DUAL_RESNET = os.environ.get("FVM_B200_DUAL", "1") != "0"
 
 
 # ------------------------------------------------------------------------------------------------ ResNet
@@ -71,6 +74,15 @@ class ResNetTrunk(nn.Module):
         # first stage's 3x3 layers over 64 channels are faster on staged input patches, which the chain kernel lacks)
         stage = min(4, max(2, int(os.environ.get("FVM_B200_CHAIN_STAGE", "2"))))
         self.chain_from = self.stage_ends[stage - 2] if CHAIN_RESNET else len(blocks)
+        # blocks whose last convolution runs together with the next block's first one
+        self.dual_after = set()
+        for i in range(len(blocks) - 1):
+            last, nxt = blocks[i]["convs"][-1], blocks[i + 1]["convs"][0]
+            plain = all(c.stride == (1, 1) and c.padding == (0, 0) and c.scale is None and tuple(c.w.shape[2:]) == (1, 1)
+                        for c in (last, nxt))
+            if DUAL_RESNET and plain and len(blocks[i]["convs"]) == 3 and len(blocks[i + 1]["convs"]) == 3 \
+                    and nxt.w.shape[1] == last.w.shape[0] and ops.pw_dual_ok(last.w.shape[1], last.w.shape[0], nxt.w.shape[0]):
+                self.dual_after.add(i)
 
     def forward(self, x: torch.Tensor, want_stage3: bool = False):
         # fp32 / fp16 NCHW image batch (fewer than 8 channels), or an fp16 NHWC8 tensor (clf::input_nhwc8's output)
@@ -79,6 +91,7 @@ class ResNetTrunk(nn.Module):
         x = ops.maxpool(x, k, s, p, ceil)
         aux = None
         chained = False
+        head = None
         try:
             for i, blk in enumerate(self.blocks):
                 if i == self.chain_from:
@@ -86,11 +99,20 @@ class ResNetTrunk(nn.Module):
                     # to 48 layers, tiles ordered by their data dependencies) instead of one launch per layer
                     chained = ops.chain_begin()
                 identity = blk["ds"](x) if "ds" in blk else x
-                y = x
                 convs = blk["convs"]
-                for c in convs[:-1]:
+                if head is not None:
+                    y, first = head, 1       # this block's first convolution already ran with the previous block's last
+                    head = None
+                else:
+                    y, first = x, 0
+                for c in convs[first:-1]:
                     y = c(y)
-                x = convs[-1](y, res=identity)
+                nxt = self.blocks[i + 1]["convs"][0] if i in self.dual_after and not chained else None
+                if nxt is not None:
+                    last = convs[-1]
+                    x, head = ops.pw_dual(y, last.w, last.b, identity, last.act, nxt.w, nxt.b, nxt.act)
+                else:
+                    x = convs[-1](y, res=identity)
                 if want_stage3 and i + 1 == self.stage_ends[2]:
                     aux = x
         finally:

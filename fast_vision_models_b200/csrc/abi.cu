@@ -125,6 +125,13 @@ extern "C" int fvm_conv_chain_f16(const fvm_chain_layer* layers, int n_layers, v
     return conv_chain_launch(layers, n_layers, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int fvm_conv_dual_f16(const void* x, const void* w1, const void* b1, const void* res, void* y, const void* w2,
+                                 const void* b2, void* z, long long M, int C1, int K1, int K2, long long ldx, long long ldr,
+                                 long long ldy, long long ldz, int act1, int act2, void* stream) {
+    return conv_dual_launch(x, w1, b1, res, y, w2, b2, z, M, C1, K1, K2, ldx, ldr, ldy, ldz, act1, act2,
+                            static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int fvm_conv2d_f16(const void* x, const void* w, const void* bias, const void* res, const float* scale,
                               void* y, int N, int H, int W, int C, int K, int R, int S, int ph, int pw, int sh, int sw,
                               int dh, int dw, long long ldx, long long ldy, long long ldr, int act, void* stream) {

@@ -2052,6 +2052,351 @@ conv_chain_kernel(const __grid_constant__ ChainParams cp) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------ two layers, one launch
+// z = act2(conv1x1(y, w2) + b2) with y = act1(conv1x1(x, w1) + b1 [+ res]): the last convolution of a bottleneck block
+// (64 -> 256 channels, + identity, ReLU) and the first of the next block (256 -> 64), where the 256-channel map is by
+// far the largest tensor of either layer. Each CTA walks 128-pixel tiles; a tile's y is produced in two halves of 128
+// channels (a half = two 64-channel panels in the 128-byte-swizzled layout that TMA and the MMA unit share):
+//   GEMM 1 (A = x tile by TMA, B = w1 resident)  -> TMEM half accumulator (ring of three)
+//   epilogue 1: + bias (+ residual, which TMA put into the y slot) -> act1 -> fp16, in place in the y slot
+//   the finished y slot is (a) stored to global memory by TMA and (b) read as the A operand of GEMM 2 (B = w2 resident),
+//   two k-blocks per half -> second accumulator (two buffers of N2 columns); the slot is free when both are done
+//   epilogue 2: + bias -> act2 -> fp16 -> z staging panel -> TMA store.
+// y is written once and never read back: the second layer costs its weights and its (small) output only. Results are
+// those of two separate launches bit for bit: same fp16 y values, same order of the fp32 accumulation over K.
+// Roles as in conv_tcgen05_kernel (producer lane, MMA lane, 16 epilogue warps, store lane); every wait is bounded.
+static constexpr int DUAL_YSLOTS = 3;                 // y half-tile slots (2 panels each) and half accumulators
+static constexpr int DUAL_MAX_SA = 4;                 // x-tile stages
+static constexpr int DUAL_LAG = 2;                    // GEMM 2 of a half is issued this many halves behind GEMM 1
+static constexpr int DUAL_ACC2_COL = DUAL_YSLOTS * 128;      // TMEM column of the second accumulator's first buffer
+static constexpr int DUAL_NUM_BARRIERS = 1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + 4 + 2;
+static constexpr int DUAL_MISC_BYTES = 16 + (DUAL_NUM_BARRIERS & 1) * 8;
+static constexpr int STATUS_WAIT_DUAL = 0x109;
+
+struct DualParams {
+    int M, m_tiles;
+    int kb1;            // input channels of the first layer / 64 (1 or 2)
+    int K1, H;          // channels of y (128 or 256) and halves per tile (K1 / 128)
+    int N2;             // channels of z (multiple of 16, at most 64)
+    int act1, act2, has_res;
+    int hints;          // bit 0: x is dead after this launch, bit 1: the residual is, bit 2: keep y in L2
+    int sa;             // x-tile stages
+    const __half* bias1;
+    const __half* bias2;
+    int* status;
+};
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w1,
+                 const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_y,
+                 const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_z,
+                 const DualParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t w1_kb_bytes = static_cast<uint32_t>(p.K1) * 128u;            // [K1][64] of one k-block
+    const uint32_t w1_bytes = static_cast<uint32_t>(p.kb1) * w1_kb_bytes;
+    const uint32_t w2_kb_bytes = static_cast<uint32_t>(p.N2) * 128u;            // [N2][64] of one k-block of GEMM 2
+    const int kb2 = p.K1 >> 6;
+    const uint32_t w2_bytes = static_cast<uint32_t>(kb2) * w2_kb_bytes;
+    const uint32_t a_stage_bytes = static_cast<uint32_t>(p.kb1) * A_STAGE_BYTES;
+    const uint32_t w1_base = smem_base;
+    const uint32_t w2_base = w1_base + w1_bytes;
+    const uint32_t a_base = w2_base + w2_bytes;
+    const uint32_t y_base = a_base + static_cast<uint32_t>(p.sa) * a_stage_bytes;
+    const uint32_t y_slot_bytes = 2u * SUB_BYTES;
+    const uint32_t z_base = y_base + DUAL_YSLOTS * y_slot_bytes;
+    const uint32_t bar_base = z_base + SUB_BYTES;
+    const uint32_t w_full_bar = bar_base;
+    auto a_full_bar = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto a_empty_bar = [&](int s) { return bar_base + 8u * (1 + DUAL_MAX_SA + s); };
+    auto res_full_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + s); };
+    auto acc1_full_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + DUAL_YSLOTS + s); };
+    auto acc1_empty_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 2 * DUAL_YSLOTS + s); };
+    auto y_done_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 3 * DUAL_YSLOTS + s); };
+    auto y_free_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 4 * DUAL_YSLOTS + s); };
+    auto acc2_full_bar = [&](int b) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + b); };
+    auto acc2_empty_bar = [&](int b) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + 2 + b); };
+    const uint32_t z_done_bar = bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + 4);
+    const uint32_t z_free_bar = z_done_bar + 8u;
+    const uint32_t misc_off = (bar_base - smem_u32(smem_raw)) + 8u * DUAL_NUM_BARRIERS;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + misc_off + 4);
+    static_assert((8 * DUAL_NUM_BARRIERS + DUAL_MISC_BYTES) % 16 == 0, "bias copies must be 16-byte aligned");
+    const uint32_t bias_off = misc_off + DUAL_MISC_BYTES;
+    const uint32_t bias1_s = smem_u32(smem_raw) + bias_off;                    // fp32 [K1], then fp32 [N2]
+    const uint32_t bias2_s = bias1_s + 4u * static_cast<uint32_t>(p.K1);
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int T = static_cast<int>(blockIdx.x) < p.m_tiles
+                      ? (p.m_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;   // tiles of this CTA
+    const int U = T * p.H;                                                                                       // halves
+    auto tile_row0 = [&](int it) { return (static_cast<int>(blockIdx.x) + it * static_cast<int>(gridDim.x)) * BM; };
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full_bar, 1);
+        for (int s = 0; s < p.sa; ++s) {
+            mbar_init(a_full_bar(s), 1);
+            mbar_init(a_empty_bar(s), 1);
+        }
+        for (int s = 0; s < DUAL_YSLOTS; ++s) {
+            mbar_init(res_full_bar(s), 1);
+            mbar_init(acc1_full_bar(s), 1);
+            mbar_init(acc1_empty_bar(s), EPI_WARPS);
+            mbar_init(y_done_bar(s), EPI_WARPS);
+            mbar_init(y_free_bar(s), 2);            // the store has read the slot out + GEMM 2 has read it
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc2_full_bar(b), 1);
+            mbar_init(acc2_empty_bar(b), EPI_WARPS);
+        }
+        mbar_init(z_done_bar, EPI_WARPS);
+        mbar_init(z_free_bar, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_w1);
+        tma_prefetch_desc(&tmap_w2);
+        tma_prefetch_desc(&tmap_y);
+        tma_prefetch_desc(&tmap_z);
+        if (p.has_res) tma_prefetch_desc(&tmap_r);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512u);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            const unsigned long long pol_a = (p.hints & 1) ? l2_policy_evict_first() : 0ull;
+            const unsigned long long pol_r = (p.hints & 2) ? l2_policy_evict_first() : 0ull;
+            if (T > 0) {      // both weight tensors, once (constants: fetched before the dependency wait)
+                mbar_expect_tx(w_full_bar, w1_bytes + w2_bytes);
+                for (int kb = 0; kb < p.kb1; ++kb)
+                    for (int h = 0; h < p.H; ++h)
+                        tma_load_3d(w1_base + static_cast<uint32_t>(kb) * w1_kb_bytes + static_cast<uint32_t>(h) * (128u * 128u),
+                                    &tmap_w1, w_full_bar, kb * BK, 0, h * 128);
+                for (int kb = 0; kb < kb2; ++kb)
+                    tma_load_3d(w2_base + static_cast<uint32_t>(kb) * w2_kb_bytes, &tmap_w2, w_full_bar, kb * BK, 0, 0);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            bool ok = true;
+            int u = 0;
+            for (int it = 0; ok && it < T; ++it) {
+                const int m0 = tile_row0(it);
+                const int sa = it % p.sa;
+                if (!mbar_wait(a_empty_bar(sa), (static_cast<uint32_t>(it / p.sa) & 1u) ^ 1u, abort_flag)) {
+                    atomicExch(p.status, STATUS_WAIT_DUAL);
+                    break;
+                }
+                mbar_expect_tx(a_full_bar(sa), a_stage_bytes);
+                for (int kb = 0; kb < p.kb1; ++kb)
+                    tma_load_2d(a_base + static_cast<uint32_t>(sa) * a_stage_bytes + static_cast<uint32_t>(kb) * A_STAGE_BYTES, &tmap_a,
+                                a_full_bar(sa), kb * BK, m0, pol_a);
+                if (!p.has_res) continue;
+                for (int h = 0; h < p.H; ++h, ++u) {
+                    const int s = u % DUAL_YSLOTS;
+                    if (!mbar_wait(y_free_bar(s), (static_cast<uint32_t>(u / DUAL_YSLOTS) & 1u) ^ 1u, abort_flag)) {
+                        atomicExch(p.status, STATUS_WAIT_DUAL);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(res_full_bar(s), y_slot_bytes);
+                    for (int j = 0; j < 2; ++j)
+                        tma_load_2d(y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(j) * SUB_BYTES, &tmap_r,
+                                    res_full_bar(s), h * 128 + j * 64, m0, pol_r);
+                }
+            }
+            // no bulk load of this CTA may be in flight when it exits: x tiles are consumed by GEMM 1 and residual
+            // halves by epilogue 1, both of which the closing barrier waits for
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            const uint32_t idesc1 = umma_idesc_f16_f32(BM, 128);
+            const uint32_t idesc2 = umma_idesc_f16_f32(BM, p.N2);
+            const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
+            auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
+            bool failed = false;
+            if (T > 0) failed |= !mbar_wait(w_full_bar, 0u, abort_flag);
+            for (int step = 0; step < U + DUAL_LAG; ++step) {
+                if (step < U) {
+                    // GEMM 1 of half `step`: 128 pixels x 128 channels of y
+                    const int it = step / p.H, h = step - it * p.H;
+                    const int s = step % DUAL_YSLOTS, sa = it % p.sa;
+                    if (h == 0) failed |= !mbar_wait(a_full_bar(sa), static_cast<uint32_t>(it / p.sa) & 1u, abort_flag);
+                    failed |= !mbar_wait(acc1_empty_bar(s), (static_cast<uint32_t>(step / DUAL_YSLOTS) & 1u) ^ 1u, abort_flag);
+                    tc_fence_after();
+                    for (int kb = 0; kb < p.kb1; ++kb)
+                        umma_f16_kblock(tmem_base + static_cast<uint32_t>(s * 128),
+                                        lo_of(a_base + static_cast<uint32_t>(sa) * a_stage_bytes + static_cast<uint32_t>(kb) * A_STAGE_BYTES), hi128,
+                                        lo_of(w1_base + static_cast<uint32_t>(kb) * w1_kb_bytes + static_cast<uint32_t>(h) * (128u * 128u)), hi128,
+                                        idesc1, static_cast<uint32_t>(kb != 0));
+                    umma_commit(acc1_full_bar(s));
+                    if (h == p.H - 1) umma_commit(a_empty_bar(sa));       // the x tile is free once these MMAs have read it
+                }
+                if (step >= DUAL_LAG) {
+                    // GEMM 2, the two k-blocks that half `v` of y contributes: A = the finished y slot
+                    const int v = step - DUAL_LAG;
+                    const int jt = v / p.H, hh = v - jt * p.H;
+                    const int s = v % DUAL_YSLOTS, b = jt & 1;
+                    if (hh == 0) failed |= !mbar_wait(acc2_empty_bar(b), (static_cast<uint32_t>(jt >> 1) & 1u) ^ 1u, abort_flag);
+                    failed |= !mbar_wait(y_done_bar(s), static_cast<uint32_t>(v / DUAL_YSLOTS) & 1u, abort_flag);
+                    tc_fence_after();
+                    for (int j = 0; j < 2; ++j)
+                        umma_f16_kblock(tmem_base + static_cast<uint32_t>(DUAL_ACC2_COL + b * 64),
+                                        lo_of(y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(j) * SUB_BYTES), hi128,
+                                        lo_of(w2_base + static_cast<uint32_t>(2 * hh + j) * w2_kb_bytes), hi128, idesc2,
+                                        static_cast<uint32_t>((hh | j) != 0));
+                    umma_commit(y_free_bar(s));
+                    if (hh == p.H - 1) umma_commit(acc2_full_bar(b));
+                }
+            }
+            if (failed) atomicExch(p.status, STATUS_WAIT_DUAL);
+        }
+        __syncwarp();
+    } else if (warp < STORE_WARP) {
+        // ------------------------------------------------------------------ epilogue (both layers)
+        const int lane_group = warp & 3;
+        const int group = (warp - 2) >> 2;
+        const int row = lane_group * 32 + lane;
+        const uint32_t row_xor = static_cast<uint32_t>(row & 7);
+        {
+            float* bias_f = reinterpret_cast<float*>(smem_raw + bias_off);
+            for (int i = threadIdx.x - 64; i < p.K1 + p.N2; i += EPI_WARPS * 32) {
+                const __half* src = i < p.K1 ? p.bias1 : p.bias2;
+                bias_f[i] = src != nullptr ? __half2float(src[i < p.K1 ? i : i - p.K1]) : 0.f;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        }
+        ConvParams q1, q2;          // what the shared epilogue code reads of its parameter block
+        q1.scale = nullptr; q1.act = p.act1;
+        q2.scale = nullptr; q2.act = p.act2;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
+        // activation as a template argument for the common ones, as in the single-layer kernels (same code, same bits)
+        const int act1_t = (p.act1 == 0 || p.act1 == 1 || p.act1 == 3 || p.act1 == 5) ? p.act1 : 2;
+        const int act2_t = (p.act2 == 0 || p.act2 == 1 || p.act2 == 3 || p.act2 == 5) ? p.act2 : 2;
+        bool ok = true;
+        auto second = [&](int j) {       // epilogue of the second layer for tile j of this CTA
+            const int b = j & 1;
+            if (!mbar_wait<EPI_BACKOFF_NS>(z_free_bar, (static_cast<uint32_t>(j) & 1u) ^ 1u, abort_flag) ||
+                !mbar_wait<EPI_BACKOFF_NS>(acc2_full_bar(b), static_cast<uint32_t>(j >> 1) & 1u, abort_flag)) {
+                if (lane == 0) atomicExch(p.status, STATUS_WAIT_DUAL);
+                ok = false;
+                return;
+            }
+            tc_fence_after();
+            const uint32_t t = t_lane + static_cast<uint32_t>(DUAL_ACC2_COL + b * 64);
+            const uint32_t srow = z_base + static_cast<uint32_t>(row) * 128u;
+            if (act2_t == 0) epilogue_rows<0, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
+            else if (act2_t == 1) epilogue_rows<1, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
+            else if (act2_t == 3) epilogue_rows<3, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
+            else if (act2_t == 5) epilogue_rows<5, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
+            else epilogue_rows<2, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(acc2_empty_bar(b));
+                mbar_arrive(z_done_bar);
+            }
+        };
+        int u = 0;
+        for (int it = 0; ok && it < T; ++it) {
+            for (int h = 0; ok && h < p.H; ++h, ++u) {
+                const int s = u % DUAL_YSLOTS;
+                const uint32_t par = static_cast<uint32_t>(u / DUAL_YSLOTS) & 1u;
+                const bool got = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(s), par, abort_flag)
+                                           : mbar_wait<EPI_BACKOFF_NS>(y_free_bar(s), par ^ 1u, abort_flag);
+                if (!got || !mbar_wait<EPI_BACKOFF_NS>(acc1_full_bar(s), par, abort_flag)) {
+                    if (lane == 0) atomicExch(p.status, STATUS_WAIT_DUAL);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t t = t_lane + static_cast<uint32_t>(s * 128);
+                const uint32_t srow = y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(row) * 128u;
+                const int variant = act1_t * 2 + (p.has_res ? 1 : 0);
+                switch (variant) {
+                    case 0: epilogue_rows<0, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 1: epilogue_rows<0, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 2: epilogue_rows<1, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 3: epilogue_rows<1, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 4: epilogue_rows<2, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 5: epilogue_rows<2, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 6: epilogue_rows<3, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 7: epilogue_rows<3, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 10: epilogue_rows<5, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    default: epilogue_rows<5, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                }
+                tc_fence_before();
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(acc1_empty_bar(s));
+                    mbar_arrive(y_done_bar(s));
+                }
+            }
+            if (ok && it >= 1) second(it - 1);
+        }
+        if (ok && T > 0) second(T - 1);
+    } else {
+        // ------------------------------------------------------------------ store warp
+        if (elect_one()) {
+            const unsigned long long pol_y = (p.hints & 4) ? l2_policy_evict_last() : 0ull;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            bool ok = true;
+            auto store_z = [&](int j) {
+                if (!mbar_wait<EPI_BACKOFF_NS>(z_done_bar, static_cast<uint32_t>(j) & 1u, abort_flag)) {
+                    atomicExch(p.status, STATUS_WAIT_DUAL);
+                    ok = false;
+                    return;
+                }
+                tma_store_2d(&tmap_z, z_base, 0, tile_row0(j));
+                tma_store_commit();
+                tma_store_wait_read();
+                mbar_arrive(z_free_bar);
+            };
+            int u = 0;
+            for (int it = 0; ok && it < T; ++it) {
+                const int m0 = tile_row0(it);
+                for (int h = 0; ok && h < p.H; ++h, ++u) {
+                    const int s = u % DUAL_YSLOTS;
+                    if (!mbar_wait<EPI_BACKOFF_NS>(y_done_bar(s), static_cast<uint32_t>(u / DUAL_YSLOTS) & 1u, abort_flag)) {
+                        atomicExch(p.status, STATUS_WAIT_DUAL);
+                        ok = false;
+                        break;
+                    }
+                    for (int j = 0; j < 2; ++j)
+                        tma_store_2d(&tmap_y, y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(j) * SUB_BYTES,
+                                     h * 128 + j * 64, m0, pol_y);
+                    tma_store_commit();
+                    tma_store_wait_read();
+                    mbar_arrive(y_free_bar(s));
+                }
+                if (ok && it >= 1) store_z(it - 1);
+            }
+            if (ok && T > 0) store_z(T - 1);
+            tma_store_wait_read();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512u);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- host side
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -2090,7 +2435,8 @@ int conv_host_init() {
         cudaFuncSetAttribute(conv_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
             cudaSuccess ||
         cudaFuncSetAttribute(conv_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(conv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+        cudaFuncSetAttribute(conv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(conv_dual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
         return FVM_ERR_SETUP;
     return FVM_OK;
 }
@@ -2943,6 +3289,123 @@ int conv_chain_launch(const fvm_chain_layer* layers, int n, cudaStream_t stream)
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, conv_chain_kernel, cp) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return FVM_ERR_LAUNCH;
+    }
+    count_launch();
+    return FVM_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------------ two layers, one launch
+// y = act1(x * w1^T + b1 [+ res]) ([M, K1], row stride ldy) and z = act2(y * w2^T + b2) ([M, K2], row stride ldz) as one
+// launch of conv_dual_kernel. x [M, C1] (row stride ldx), w1 [K1][C1], w2 [K2][K1]; (C1, K1) is (64, 128), (64, 256) or
+// (128, 128), K2 a multiple of 16 up to 64; activations 0 (none) or 1 (ReLU) run specialised, the others through the generic code.
+// Refused (FVM_ERR_ARG, nothing launched): other shapes, misaligned pointers, outputs that overlap an input or each other.
+int conv_dual_launch(const void* x, const void* w1, const void* b1, const void* res, void* y, const void* w2, const void* b2,
+                     void* z, long long M, int C1, int K1, int K2, long long ldx, long long ldr, long long ldy, long long ldz,
+                     int act1, int act2, cudaStream_t stream) {
+    DeviceState* st = device_state();
+    if (!st) return FVM_ERR_SETUP;
+    if (!x || !w1 || !y || !w2 || !z) return FVM_ERR_ARG;
+    if (M <= 0 || M > 0x7fffff00ll) return FVM_ERR_ARG;
+    if ((C1 != 64 && C1 != 128) || (K1 != 128 && K1 != 256) || C1 * K1 > 64 * 256 || K2 < 16 || K2 > 64 || (K2 & 15)) return FVM_ERR_ARG;
+    if (act1 < 0 || act1 > 6 || act2 < 0 || act2 > 6) return FVM_ERR_ARG;
+    if ((ldx & 7) || ldx < C1 || (ldy & 7) || ldy < K1 || (ldz & 7) || ldz < K2 || (res && ((ldr & 7) || ldr < K1))) return FVM_ERR_ARG;
+    const void* ptrs[8] = {x, w1, b1, res, y, w2, b2, z};
+    for (int i = 0; i < 8; ++i)
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) return FVM_ERR_ARG;
+    {
+        const size_t nx = static_cast<size_t>((M - 1) * ldx + C1) * 2, ny = static_cast<size_t>((M - 1) * ldy + K1) * 2;
+        const size_t nz = static_cast<size_t>((M - 1) * ldz + K2) * 2, nr = res ? static_cast<size_t>((M - 1) * ldr + K1) * 2 : 0;
+        if (ranges_overlap(y, ny, x, nx) || ranges_overlap(z, nz, x, nx) || ranges_overlap(y, ny, z, nz)) return FVM_ERR_ARG;
+        if (res && (ranges_overlap(y, ny, res, nr) || ranges_overlap(z, nz, res, nr))) return FVM_ERR_ARG;
+    }
+    DualParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = static_cast<int>(M);
+    p.m_tiles = static_cast<int>((M + BM - 1) / BM);
+    p.kb1 = C1 / 64;
+    p.K1 = K1;
+    p.H = K1 / 128;
+    p.N2 = K2;
+    p.act1 = act1;
+    p.act2 = act2;
+    p.has_res = res != nullptr;
+    p.bias1 = static_cast<const __half*>(b1);
+    p.bias2 = static_cast<const __half*>(b2);
+    p.status = st->status_dev;
+    {
+        // same rule as a single layer with a residual (conv2d_launch): x and the identity are dead after this launch
+        // in a bottleneck block, y is read again (as the next identity) if it fits the L2
+        static const int use_hints = [] { const char* v = getenv("FVM_B200_L2_HINTS"); return (v && v[0] == '0') ? 0 : 1; }();
+        if (use_hints && res) {
+            p.hints = 1 | 2;
+            if (static_cast<unsigned long long>(M) * K1 * 2 <= 112ull * 1024 * 1024) p.hints |= 4;
+        }
+    }
+    const uint32_t fixed = 1024 + static_cast<uint32_t>(p.kb1 * K1) * 128u + static_cast<uint32_t>((K1 / 64) * K2) * 128u +
+                           DUAL_YSLOTS * 2 * SUB_BYTES + SUB_BYTES + 8 * DUAL_NUM_BARRIERS + DUAL_MISC_BYTES +
+                           ((static_cast<uint32_t>(K1 + K2) * 4 + 15u) & ~15u);
+    const uint32_t a_stage = static_cast<uint32_t>(p.kb1) * A_STAGE_BYTES;
+    if (fixed + 2 * a_stage > 227u * 1024) return FVM_ERR_ARG;
+    p.sa = static_cast<int>((227u * 1024 - fixed) / a_stage);
+    if (p.sa > DUAL_MAX_SA) p.sa = DUAL_MAX_SA;
+    size_t smem = fixed + static_cast<size_t>(p.sa) * a_stage;
+    if (smem < 120 * 1024) smem = 120 * 1024;          // one CTA per SM: it owns all 512 TMEM columns
+
+    CUtensorMap tmap_a, tmap_w1, tmap_r, tmap_y, tmap_w2, tmap_z;
+    const unsigned long long Mu = static_cast<unsigned long long>(M);
+    {
+        const unsigned long long dims[2] = {static_cast<unsigned long long>(C1), Mu};
+        const unsigned long long strides[1] = {static_cast<unsigned long long>(ldx) * 2};
+        const unsigned box[2] = {BK, BM};
+        if (encode_tiled_f16(&tmap_a, x, 2, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+    }
+    {
+        const unsigned long long dims[2] = {static_cast<unsigned long long>(K1), Mu};
+        const unsigned long long ystr[1] = {static_cast<unsigned long long>(ldy) * 2};
+        const unsigned box[2] = {64, BM};
+        if (encode_tiled_f16(&tmap_y, y, 2, dims, ystr, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        if (res) {
+            const unsigned long long rstr[1] = {static_cast<unsigned long long>(ldr) * 2};
+            if (encode_tiled_f16(&tmap_r, res, 2, dims, rstr, box, true) != FVM_OK) return FVM_ERR_TMAP;
+        } else {
+            tmap_r = tmap_y;
+        }
+    }
+    {
+        const unsigned long long dims[2] = {static_cast<unsigned long long>(K2), Mu};
+        const unsigned long long zstr[1] = {static_cast<unsigned long long>(ldz) * 2};
+        const unsigned box[2] = {64, BM};
+        if (encode_tiled_f16(&tmap_z, z, 2, dims, zstr, box, true) != FVM_OK) return FVM_ERR_TMAP;
+    }
+    {
+        const unsigned long long dims[3] = {static_cast<unsigned long long>(C1), 1ull, static_cast<unsigned long long>(K1)};
+        const unsigned long long strides[2] = {static_cast<unsigned long long>(C1) * 2, static_cast<unsigned long long>(C1) * 2};
+        const unsigned box[3] = {BK, 1, 128};
+        if (encode_tiled_f16(&tmap_w1, w1, 3, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+    }
+    {
+        const unsigned long long dims[3] = {static_cast<unsigned long long>(K1), 1ull, static_cast<unsigned long long>(K2)};
+        const unsigned long long strides[2] = {static_cast<unsigned long long>(K1) * 2, static_cast<unsigned long long>(K1) * 2};
+        const unsigned box[3] = {BK, 1, static_cast<unsigned>(K2)};
+        if (encode_tiled_f16(&tmap_w2, w2, 3, dims, strides, box, true) != FVM_OK) return FVM_ERR_TMAP;
+    }
+    const int grid = p.m_tiles < st->sms ? p.m_tiles : st->sms;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(CONV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    static const int use_pdl = [] { const char* v = getenv("FVM_B200_PDL"); return (v && v[0] == '0') ? 0 : 1; }();
+    cfg.attrs = attrs;
+    cfg.numAttrs = use_pdl ? 1u : 0u;
+    if (cudaLaunchKernelEx(&cfg, conv_dual_kernel, tmap_a, tmap_w1, tmap_r, tmap_y, tmap_w2, tmap_z, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return FVM_ERR_LAUNCH;
     }

@@ -42,5 +42,8 @@ int conv2d_launch(const void* x, const void* w, const void* bias, const void* re
                   long long ldx, long long ldy, long long ldr, int act, int force_bn, int ph_hi, int pw_hi,
                   cudaStream_t stream, int w_per_image = 0, int gsg = 0, int gsk = 0);
 int conv_chain_launch(const fvm_chain_layer* layers, int n, cudaStream_t stream);
+int conv_dual_launch(const void* x, const void* w1, const void* b1, const void* res, void* y, const void* w2, const void* b2,
+                     void* z, long long M, int C1, int K1, int K2, long long ldx, long long ldr, long long ldy, long long ldz,
+                     int act1, int act2, cudaStream_t stream);
 
 }  // namespace fvm

@@ -302,6 +302,44 @@ def pw_into(x, w, bias, res, act: int, out: torch.Tensor, force: int = 0) -> Non
     conv_fused_into(x, w, bias, res, (0, 0), (1, 1), act, out)
 
 
+def pw_dual_ok(C1: int, K1: int, K2: int) -> bool:
+    """Shapes fvm_conv_dual_f16 takes: (C1, K1) one of (64, 128), (64, 256), (128, 128) -- both weight tensors stay in
+    shared memory -- and K2 a multiple of 16 up to 64."""
+    return (C1, K1) in ((64, 128), (64, 256), (128, 128)) and 16 <= K2 <= 64 and K2 % 16 == 0
+
+
+def pw_dual(x, w1, b1, res, act1: int, w2, b2, act2: int):
+    """Two 1x1 stride-1 convolutions as one launch: y = act1(x . w1^T + b1 + res), z = act2(y . w2^T + b2); returns (y, z).
+    The last convolution of a bottleneck block with the first of the next one (torchvision Bottleneck.conv3 + identity
+    + ReLU -> conv1 + ReLU); the reference runs them as two clf::conv_fused launches (fused_conv.cu:231-306). y is
+    written once and the second layer reads it from shared memory; same bits as `pw` twice. Raises FvmError for shapes
+    outside pw_dual_ok."""
+    init(x.device)
+    x, N, C1, H, W, ldx = nhwc_view(x, "x")
+    w1, w2 = _krsc(w1), _krsc(w2)
+    K1, K2 = w1.shape[0], w2.shape[0]
+    if tuple(w1.shape[1:]) != (C1, 1, 1) or tuple(w2.shape[1:]) != (K1, 1, 1):
+        raise FvmError("pw_dual: expected 1x1 weights [K1,C1,1,1] and [K2,K1,1,1]")
+    if not pw_dual_ok(C1, K1, K2):
+        raise FvmError(f"pw_dual: unsupported channel counts {C1} -> {K1} -> {K2}")
+    ldr = 0
+    if res is not None:
+        res, Nr, Kr, Hr, Wr, ldr = nhwc_view(res, "res")
+        if (Nr, Kr, Hr, Wr) != (N, K1, H, W):
+            raise FvmError("pw_dual: residual shape does not match the first layer's output")
+    for b, name in ((b1, "b1"), (b2, "b2")):
+        if b is not None:
+            _require_cuda_half(b, name)
+    b1 = None if b1 is None else b1.contiguous()
+    b2 = None if b2 is None else b2.contiguous()
+    y = empty_nhwc(N, K1, H, W, x.device)
+    z = empty_nhwc(N, K2, H, W, x.device)
+    rc = lib().fvm_conv_dual_f16(x.data_ptr(), w1.data_ptr(), _ptr(b1), _ptr(res), y.data_ptr(), w2.data_ptr(), _ptr(b2),
+                                 z.data_ptr(), N * H * W, C1, K1, K2, ldx, ldr, K1, K2, int(act1), int(act2), _stream())
+    _check(rc, "conv_dual_f16")
+    return y, z
+
+
 _PACKED_GROUPED = {}      # (data_ptr, version, shape, groups) -> (packed weights, gsg, gsk, the source tensor kept alive)
 
 

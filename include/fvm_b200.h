@@ -120,6 +120,19 @@ typedef struct fvm_chain_layer {
 } fvm_chain_layer;
 int fvm_conv_chain_f16(const fvm_chain_layer* layers, int n_layers, void* stream);
 
+/* Two 1x1 convolutions as ONE launch, the first layer's output handed to the second on chip -- no counterpart in the
+ * reference (one kernel per layer, classification/fast/csrc/fused_conv.cu:231-306); it takes the last convolution of a
+ * bottleneck block and the first of the next (torchvision Bottleneck.conv3 -> add -> ReLU -> next Bottleneck.conv1):
+ *   y = act1(x * w1^T + b1 [+ res])   x [M, C1] (row stride ldx), w1 [K1][C1], res / y [M, K1] (row strides ldr / ldy)
+ *   z = act2(y * w2^T + b2)           w2 [K2][K1], z [M, K2] (row stride ldz)
+ * y is written to global memory once and read by the second layer from the shared-memory tile it was stored from, so
+ * the second layer costs its weights and its output only. Same bits as two fvm_conv2d_f16 calls. (C1, K1) is (64, 128),
+ * (64, 256) or (128, 128) (both weight tensors stay in shared memory), K2 a multiple of 16 up to 64; returns 1 with
+ * nothing launched for other shapes, for misaligned pointers (16 bytes) or when y or z overlaps another operand. */
+int fvm_conv_dual_f16(const void* x, const void* w1, const void* b1, const void* res, void* y, const void* w2,
+                      const void* b2, void* z, long long M, int C1, int K1, int K2, long long ldx, long long ldr,
+                      long long ldy, long long ldz, int act1, int act2, void* stream);
+
 /* fvm_conv2d_f16_tile with separate bottom / right padding (ph_hi, pw_hi; negative = same as top / left). The host
  * uses it to run a stride-2 RGB stem (reference: the zero-padded 8-channel stem, fused.py:90-105) over column pairs:
  * the NHWC8 input viewed as [N, H, W/2, 16] with re-packed weights, which halves the rows the TMA unit gathers. */

@@ -281,6 +281,64 @@ def _resnet_stage(N, H, W, cin, mid, blocks, stride, seed):
     return run
 
 
+DUAL_CASES = [
+    # N, H, W, C1, K1, K2, act1, act2, residual
+    (64, 56, 56, 64, 256, 64, 1, 1, True),     # ResNet-50 stage 1: conv3 + identity + ReLU, then the next block's conv1
+    (8, 128, 256, 64, 256, 64, 1, 1, True),    # the same pair inside DeepLabV3 at 512 x 1024, batch 8
+    (3, 19, 23, 64, 256, 64, 1, 1, True),      # 1311 pixels: ragged last tile
+    (2, 9, 7, 128, 128, 48, 1, 0, True),       # two k-blocks in the first layer, 48 output channels
+    (5, 12, 12, 64, 128, 16, 0, 1, True),      # y of one half only, narrowest z
+    (4, 30, 30, 128, 128, 32, 3, 5, False),    # no residual, SiLU / GELU through the generic activation code
+    (1, 1, 1, 64, 256, 64, 1, 1, False),       # a single pixel
+    (64, 28, 28, 128, 128, 64, 1, 1, True),    # more tiles than one wave, fewer than three
+]
+
+
+@pytest.mark.parametrize("case", DUAL_CASES)
+def test_pw_dual_matches_two_launches_bit_for_bit(case):
+    # y = act1(conv1x1(x) + b1 + res), z = act2(conv1x1(y) + b2) as one launch (the second layer reads y from the shared
+    # memory tile it is stored from) against two launches of the single-layer kernel: same bits for y and for z
+    N, H, W, C1, K1, K2, act1, act2, has_res = case
+    ops.init(DEV)
+    x = cl(gen((N, C1, H, W), 70))
+    w1, b1 = cl(gen((K1, C1, 1, 1), 71, 0.08)), gen((K1,), 72, 0.1).to(DEV)
+    w2, b2 = cl(gen((K2, K1, 1, 1), 73, 0.05)), gen((K2,), 74, 0.1).to(DEV)
+    res = cl(gen((N, K1, H, W), 75)) if has_res else None
+    y_ref = ops.conv_fused(x, w1, b1, res, (0, 0), (1, 1), act1)
+    z_ref = ops.conv_fused(y_ref, w2, b2, None, (0, 0), (1, 1), act2)
+    for _ in range(2):
+        before = ops.launches()
+        y, z = ops.pw_dual(x, w1, b1, res, act1, w2, b2, act2)
+        assert ops.launches() - before == 1
+        assert ops.last_status() == 0
+        assert torch.equal(y, y_ref), (y.float() - y_ref.float()).abs().max().item()
+        assert torch.equal(z, z_ref), (z.float() - z_ref.float()).abs().max().item()
+
+
+def test_pw_dual_against_the_oracle_and_refusals():
+    ops.init(DEV)
+    N, H, W = 2, 11, 13
+    x, w1, b1 = gen((N, 64, H, W), 80), gen((256, 64, 1, 1), 81, 0.08), gen((256,), 82, 0.1)
+    w2, b2, res = gen((64, 256, 1, 1), 83, 0.05), gen((64,), 84, 0.1), gen((N, 256, H, W), 85)
+    y, z = ops.pw_dual(cl(x), cl(w1), b1.to(DEV), cl(res), 1, cl(w2), b2.to(DEV), 1)
+    assert ops.last_status() == 0
+    close(y, R.conv_fused_ref(x, w1, b1, res, (0, 0), (1, 1), 1))
+    close(z, R.conv_fused_ref(y.float().cpu(), w2, b2, None, (0, 0), (1, 1), 1))
+    # shapes outside the kernel's range are refused by the host layer and by the C entry point (status 1, no launch)
+    with pytest.raises(ops.FvmError):
+        ops.pw_dual(cl(gen((1, 96, 4, 4), 86)), cl(gen((256, 96, 1, 1), 87)), None, None, 1, cl(w2), None, 1)
+    L = ops.lib()
+    xd, w1d, w2d = cl(x), cl(w1), cl(w2)
+    yd, zd = ops.empty_nhwc(N, 256, H, W, DEV), ops.empty_nhwc(N, 64, H, W, DEV)
+    before = ops.launches()
+    args = lambda y_ptr, K2: (xd.data_ptr(), w1d.data_ptr(), None, None, y_ptr, w2d.data_ptr(), None, zd.data_ptr(),
+                              N * H * W, 64, 256, K2, 64, 0, 256, 64, 1, 1, None)
+    assert L.fvm_conv_dual_f16(*args(yd.data_ptr(), 40)) == 1           # K2 not a multiple of 16
+    assert L.fvm_conv_dual_f16(*args(xd.data_ptr(), 64)) == 1           # y overlaps x
+    assert L.fvm_conv_dual_f16(*args(yd.data_ptr() + 8, 64)) == 1       # misaligned y
+    assert ops.launches() == before
+
+
 CHAIN_CASES = [
     # N, H, W, input channels, bottleneck width, blocks, stride of the first block
     (64, 28, 28, 512, 256, 3, 2),      # ResNet-50 stage 3 (first three blocks): 28x28 -> 14x14
