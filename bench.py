@@ -402,12 +402,12 @@ def main():
         pk = peaks()
         ms_step = med / steps
         roof = roofline_of(MODEL, BATCH, ms_step, pk)
-        roof["kernel"] = ("whole forward graph; the two convolution kernels carry 95 % of the device time "
-                          "(conv_pair_kernel 67 % over 43 launches, conv_tcgen05_kernel 29 % over 11)")
-        roof["traffic"] = 2486.0e6 if (MODEL, BATCH) == ("resnet50", 64) else None
-        roof["traffic_source"] = ("ncu capture of this forward (dram__bytes_read.sum + dram__bytes_write.sum over its 58 "
-                                  "launches, serialised, cold caches: profiles/resnet50_b64_forward_launches.md); "
-                                  "not measured in this run")
+        roof["kernel"] = ("whole forward graph; the three convolution kernels carry 96 % of the device time "
+                          "(conv_pair_kernel 68 % over 43 launches, conv_tcgen05_kernel 20 % over 7, "
+                          "conv_dual_kernel 7 % over 2)")
+        roof["traffic"] = 2212.4e6 if (MODEL, BATCH) == ("resnet50", 64) else None
+        roof["traffic_source"] = ("ncu capture of this forward (dram__bytes_read.sum + dram__bytes_write.sum over its 56 "
+                                  "launches, serialised, cold caches); not measured in this run")
         line = {"metric": "ResNet-50 fp16 b64 images/s", "value": round(value, 1),
                 "value_min": round(images_per_window / (max(win_dev) / 1e3), 1),
                 "value_max": round(images_per_window / (min(win_dev) / 1e3), 1), "unit": "images/s", "n_gpus": world,

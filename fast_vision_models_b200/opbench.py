@@ -6,6 +6,7 @@
     python -m fast_vision_models_b200.opbench dwconv --n 64 --hw 95 --c 192 --r 3 --pad 1 --act 3
     python -m fast_vision_models_b200.opbench layernorm --n 64 --hw 56 --c 96
     python -m fast_vision_models_b200.opbench gap --n 64 --hw 7 --c 2048        (also: se_scale, maxpool, up_argmax, wbatch)
+    python -m fast_vision_models_b200.opbench dual --n 64 --hw 56 --c 64 --k 256 --k2 64 --res     (two 1x1 layers, one launch)
 
 Default: the op is captured 20 times into a CUDA graph over 4 rotating buffer sets (so that inputs do not stay in
 L2), the graph is replayed and timed with CUDA events; prints microseconds per launch and the algorithmic GB/s
@@ -26,11 +27,12 @@ def _cl(t):
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--groups", type=int, default=1, help="conv: groups (> 1: clfr3.gconv2 path)")
-    ap.add_argument("op", choices=["conv", "stem", "dwconv", "layernorm", "gap", "se_scale", "se_gate", "maxpool", "up_argmax", "wbatch"])
+    ap.add_argument("op", choices=["conv", "dual", "stem", "dwconv", "layernorm", "gap", "se_scale", "se_gate", "maxpool", "up_argmax", "wbatch"])
     ap.add_argument("--n", type=int, default=64)
     ap.add_argument("--hw", type=int, nargs="+", default=[56], help="height [width]")
     ap.add_argument("--c", type=int, default=64)
     ap.add_argument("--k", type=int, default=64)
+    ap.add_argument("--k2", type=int, default=64, help="dual: output channels of the second layer")
     ap.add_argument("--r", type=int, default=1, help="filter size (square)")
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--pad", type=int, default=0)
@@ -73,6 +75,18 @@ def main():
             def launch(i):
                 ops.conv_fused_into(xs[i], w, b, rs[i], (a.pad, a.pad), (a.stride, a.stride), a.act, ys[i],
                                     dilation=(a.dil, a.dil), tile_n=a.tile)
+    elif a.op == "dual":
+        # y = act(x . w1^T + b1 + res), z = act(y . w2^T + b2) as one launch (ops.pw_dual)
+        K2 = a.k2
+        xs = [_cl(rnd(N, C, H, W)) for _ in range(nbuf)]
+        w1, b1 = _cl(rnd(K, C, 1, 1, scale=0.08)), rnd(K, scale=0.1)
+        w2, b2 = _cl(rnd(K2, K, 1, 1, scale=0.05)), rnd(K2, scale=0.1)
+        rs = [_cl(rnd(N, K, H, W)) if a.res else None for _ in range(nbuf)]
+        nbytes = 2 * (N * H * W * (C + K * (2 if a.res else 1) + K2) + K * C + K2 * K + K + K2)
+        flops = 2 * N * H * W * K * (C + K2)
+
+        def launch(i):
+            ops.pw_dual(xs[i], w1, b1, rs[i], a.act, w2, b2, a.act)
     elif a.op == "stem":
         P, Q = (H + 2 * a.pad - R) // 2 + 1, (W + 2 * a.pad - R) // 2 + 1
         xs = [ops.input_nhwc8_split(torch.randn((N, 3, H, W), generator=g).to(dev)) for _ in range(nbuf)]
