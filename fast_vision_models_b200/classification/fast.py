@@ -40,6 +40,10 @@ CHAIN_RESNET = os.environ.get("FVM_B200_CHAIN_RESNET", "0") == "1"
 # The last convolution of a bottleneck block and the first of the next block as one launch (ops.pw_dual) where the
 # shapes allow it (64 -> 256 -> 64 channels: the first stage of a ResNet-50/101/152). FVM_B200_DUAL=0: one launch each.
 DUAL_RESNET = os.environ.get("FVM_B200_DUAL", "1") != "0"
+# Also where the second layer has more than 64 channels (the first block of stage 2: 64 -> 256 -> 128): 62 against 78 us
+# when the pair is timed alone, but 0.4 % slower inside a ResNet-50 forward at batch 64 (59.55 against 59.81 k img/s on
+# one B200: as its own launch that layer reads most of y from L2, back to front). Off unless asked for.
+DUAL_WIDE = os.environ.get("FVM_B200_DUAL_WIDE", "0") == "1"
 
 
 # ------------------------------------------------------------------------------------------------ ResNet
@@ -81,7 +85,8 @@ class ResNetTrunk(nn.Module):
             plain = all(c.stride == (1, 1) and c.padding == (0, 0) and c.scale is None and tuple(c.w.shape[2:]) == (1, 1)
                         for c in (last, nxt))
             if DUAL_RESNET and plain and len(blocks[i]["convs"]) == 3 and len(blocks[i + 1]["convs"]) == 3 \
-                    and nxt.w.shape[1] == last.w.shape[0] and ops.pw_dual_ok(last.w.shape[1], last.w.shape[0], nxt.w.shape[0]):
+                    and nxt.w.shape[1] == last.w.shape[0] and ops.pw_dual_ok(last.w.shape[1], last.w.shape[0], nxt.w.shape[0]) \
+                    and (DUAL_WIDE or nxt.w.shape[0] <= 64):
                 self.dual_after.add(i)
 
     def forward(self, x: torch.Tensor, want_stage3: bool = False):

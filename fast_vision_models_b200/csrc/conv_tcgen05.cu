@@ -2055,29 +2055,32 @@ conv_chain_kernel(const __grid_constant__ ChainParams cp) {
 // ------------------------------------------------------------------------------------------------ two layers, one launch
 // z = act2(conv1x1(y, w2) + b2) with y = act1(conv1x1(x, w1) + b1 [+ res]): the last convolution of a bottleneck block
 // (64 -> 256 channels, + identity, ReLU) and the first of the next block (256 -> 64), where the 256-channel map is by
-// far the largest tensor of either layer. Each CTA walks 128-pixel tiles; a tile's y is produced in two halves of 128
-// channels (a half = two 64-channel panels in the 128-byte-swizzled layout that TMA and the MMA unit share):
-//   GEMM 1 (A = x tile by TMA, B = w1 resident)  -> TMEM half accumulator (ring of three)
+// far the largest tensor of either layer. Each CTA walks 128-pixel tiles; a tile's y is produced in units of 128
+// channels (z up to 64 channels wide; a unit = two 64-channel panels in the 128-byte-swizzled layout that TMA and the
+// MMA unit share, ring of three slots) or of 64 channels (z up to 128 wide: one panel, ring of four):
+//   GEMM 1 (A = x tile by TMA, B = w1 resident)  -> TMEM unit accumulator (one per slot)
 //   epilogue 1: + bias (+ residual, which TMA put into the y slot) -> act1 -> fp16, in place in the y slot
 //   the finished y slot is (a) stored to global memory by TMA and (b) read as the A operand of GEMM 2 (B = w2 resident),
-//   two k-blocks per half -> second accumulator (two buffers of N2 columns); the slot is free when both are done
-//   epilogue 2: + bias -> act2 -> fp16 -> z staging panel -> TMA store.
+//   one k-block per panel -> second accumulator (two buffers of 64 or 128 columns); the slot is free when both are done
+//   epilogue 2: + bias -> act2 -> fp16 -> z staging panels -> TMA store.
 // y is written once and never read back: the second layer costs its weights and its (small) output only. Results are
 // those of two separate launches bit for bit: same fp16 y values, same order of the fp32 accumulation over K.
 // Roles as in conv_tcgen05_kernel (producer lane, MMA lane, 16 epilogue warps, store lane); every wait is bounded.
-static constexpr int DUAL_YSLOTS = 3;                 // y half-tile slots (2 panels each) and half accumulators
+static constexpr int DUAL_MAX_YSLOTS = 4;             // y unit slots = unit accumulators in TMEM (3 or 4 are used)
 static constexpr int DUAL_MAX_SA = 4;                 // x-tile stages
-static constexpr int DUAL_LAG = 2;                    // GEMM 2 of a half is issued this many halves behind GEMM 1
-static constexpr int DUAL_ACC2_COL = DUAL_YSLOTS * 128;      // TMEM column of the second accumulator's first buffer
-static constexpr int DUAL_NUM_BARRIERS = 1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + 4 + 2;
+static constexpr int DUAL_LAG = 2;                    // GEMM 2 of a unit is issued this many units behind GEMM 1
+static constexpr int DUAL_NUM_BARRIERS = 1 + 2 * DUAL_MAX_SA + 5 * DUAL_MAX_YSLOTS + 4 + 2;
 static constexpr int DUAL_MISC_BYTES = 16 + (DUAL_NUM_BARRIERS & 1) * 8;
 static constexpr int STATUS_WAIT_DUAL = 0x109;
 
 struct DualParams {
     int M, m_tiles;
     int kb1;            // input channels of the first layer / 64 (1 or 2)
-    int K1, H;          // channels of y (128 or 256) and halves per tile (K1 / 128)
-    int N2;             // channels of z (multiple of 16, at most 64)
+    int K1, H;          // channels of y (128 or 256) and units per tile (K1 / UW)
+    int UW, UP, ys;     // channels per unit (128 or 64), panels per unit (UW / 64), y slots (3 or 4; ys * UW <= 384)
+    int N2;             // channels of z (multiple of 16, at most 128)
+    int acc2_col, acc2_stride;   // TMEM column of the second accumulator's first buffer, columns between its two buffers
+    int zp;             // 64-channel panels of the z staging tile (1 or 2)
     int act1, act2, has_res;
     int hints;          // bit 0: x is dead after this launch, bit 1: the residual is, bit 2: keep y in L2
     int sa;             // x-tile stages
@@ -2103,20 +2106,20 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t w2_base = w1_base + w1_bytes;
     const uint32_t a_base = w2_base + w2_bytes;
     const uint32_t y_base = a_base + static_cast<uint32_t>(p.sa) * a_stage_bytes;
-    const uint32_t y_slot_bytes = 2u * SUB_BYTES;
-    const uint32_t z_base = y_base + DUAL_YSLOTS * y_slot_bytes;
-    const uint32_t bar_base = z_base + SUB_BYTES;
+    const uint32_t y_slot_bytes = static_cast<uint32_t>(p.UP) * SUB_BYTES;
+    const uint32_t z_base = y_base + static_cast<uint32_t>(p.ys) * y_slot_bytes;
+    const uint32_t bar_base = z_base + static_cast<uint32_t>(p.zp) * SUB_BYTES;
     const uint32_t w_full_bar = bar_base;
     auto a_full_bar = [&](int s) { return bar_base + 8u * (1 + s); };
     auto a_empty_bar = [&](int s) { return bar_base + 8u * (1 + DUAL_MAX_SA + s); };
     auto res_full_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + s); };
-    auto acc1_full_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + DUAL_YSLOTS + s); };
-    auto acc1_empty_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 2 * DUAL_YSLOTS + s); };
-    auto y_done_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 3 * DUAL_YSLOTS + s); };
-    auto y_free_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 4 * DUAL_YSLOTS + s); };
-    auto acc2_full_bar = [&](int b) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + b); };
-    auto acc2_empty_bar = [&](int b) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + 2 + b); };
-    const uint32_t z_done_bar = bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_YSLOTS + 4);
+    auto acc1_full_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + DUAL_MAX_YSLOTS + s); };
+    auto acc1_empty_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 2 * DUAL_MAX_YSLOTS + s); };
+    auto y_done_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 3 * DUAL_MAX_YSLOTS + s); };
+    auto y_free_bar = [&](int s) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 4 * DUAL_MAX_YSLOTS + s); };
+    auto acc2_full_bar = [&](int b) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_MAX_YSLOTS + b); };
+    auto acc2_empty_bar = [&](int b) { return bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_MAX_YSLOTS + 2 + b); };
+    const uint32_t z_done_bar = bar_base + 8u * (1 + 2 * DUAL_MAX_SA + 5 * DUAL_MAX_YSLOTS + 4);
     const uint32_t z_free_bar = z_done_bar + 8u;
     const uint32_t misc_off = (bar_base - smem_u32(smem_raw)) + 8u * DUAL_NUM_BARRIERS;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + misc_off);
@@ -2139,7 +2142,7 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(a_full_bar(s), 1);
             mbar_init(a_empty_bar(s), 1);
         }
-        for (int s = 0; s < DUAL_YSLOTS; ++s) {
+        for (int s = 0; s < p.ys; ++s) {
             mbar_init(res_full_bar(s), 1);
             mbar_init(acc1_full_bar(s), 1);
             mbar_init(acc1_empty_bar(s), EPI_WARPS);
@@ -2179,9 +2182,9 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (T > 0) {      // both weight tensors, once (constants: fetched before the dependency wait)
                 mbar_expect_tx(w_full_bar, w1_bytes + w2_bytes);
                 for (int kb = 0; kb < p.kb1; ++kb)
-                    for (int h = 0; h < p.H; ++h)
-                        tma_load_3d(w1_base + static_cast<uint32_t>(kb) * w1_kb_bytes + static_cast<uint32_t>(h) * (128u * 128u),
-                                    &tmap_w1, w_full_bar, kb * BK, 0, h * 128);
+                    for (int r = 0; r < p.K1; r += 128)      // boxes of 128 rows, row r of a k-block at r * 128 bytes
+                        tma_load_3d(w1_base + static_cast<uint32_t>(kb) * w1_kb_bytes + static_cast<uint32_t>(r) * 128u,
+                                    &tmap_w1, w_full_bar, kb * BK, 0, r);
                 for (int kb = 0; kb < kb2; ++kb)
                     tma_load_3d(w2_base + static_cast<uint32_t>(kb) * w2_kb_bytes, &tmap_w2, w_full_bar, kb * BK, 0, 0);
             }
@@ -2201,16 +2204,16 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                 a_full_bar(sa), kb * BK, m0, pol_a);
                 if (!p.has_res) continue;
                 for (int h = 0; h < p.H; ++h, ++u) {
-                    const int s = u % DUAL_YSLOTS;
-                    if (!mbar_wait(y_free_bar(s), (static_cast<uint32_t>(u / DUAL_YSLOTS) & 1u) ^ 1u, abort_flag)) {
+                    const int s = u % p.ys;
+                    if (!mbar_wait(y_free_bar(s), (static_cast<uint32_t>(u / p.ys) & 1u) ^ 1u, abort_flag)) {
                         atomicExch(p.status, STATUS_WAIT_DUAL);
                         ok = false;
                         break;
                     }
                     mbar_expect_tx(res_full_bar(s), y_slot_bytes);
-                    for (int j = 0; j < 2; ++j)
+                    for (int j = 0; j < p.UP; ++j)
                         tma_load_2d(y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(j) * SUB_BYTES, &tmap_r,
-                                    res_full_bar(s), h * 128 + j * 64, m0, pol_r);
+                                    res_full_bar(s), h * p.UW + j * 64, m0, pol_r);
                 }
             }
             // no bulk load of this CTA may be in flight when it exits: x tiles are consumed by GEMM 1 and residual
@@ -2220,7 +2223,7 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
-            const uint32_t idesc1 = umma_idesc_f16_f32(BM, 128);
+            const uint32_t idesc1 = umma_idesc_f16_f32(BM, p.UW);
             const uint32_t idesc2 = umma_idesc_f16_f32(BM, p.N2);
             const uint32_t hi128 = static_cast<uint32_t>(umma_desc_sw128(0) >> 32);
             auto lo_of = [](uint32_t addr) { return ((addr & 0x3ffffu) >> 4) | 0x10000u; };
@@ -2228,32 +2231,32 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (T > 0) failed |= !mbar_wait(w_full_bar, 0u, abort_flag);
             for (int step = 0; step < U + DUAL_LAG; ++step) {
                 if (step < U) {
-                    // GEMM 1 of half `step`: 128 pixels x 128 channels of y
+                    // GEMM 1 of unit `step`: 128 pixels x UW channels of y
                     const int it = step / p.H, h = step - it * p.H;
-                    const int s = step % DUAL_YSLOTS, sa = it % p.sa;
+                    const int s = step % p.ys, sa = it % p.sa;
                     if (h == 0) failed |= !mbar_wait(a_full_bar(sa), static_cast<uint32_t>(it / p.sa) & 1u, abort_flag);
-                    failed |= !mbar_wait(acc1_empty_bar(s), (static_cast<uint32_t>(step / DUAL_YSLOTS) & 1u) ^ 1u, abort_flag);
+                    failed |= !mbar_wait(acc1_empty_bar(s), (static_cast<uint32_t>(step / p.ys) & 1u) ^ 1u, abort_flag);
                     tc_fence_after();
                     for (int kb = 0; kb < p.kb1; ++kb)
-                        umma_f16_kblock(tmem_base + static_cast<uint32_t>(s * 128),
+                        umma_f16_kblock(tmem_base + static_cast<uint32_t>(s * p.UW),
                                         lo_of(a_base + static_cast<uint32_t>(sa) * a_stage_bytes + static_cast<uint32_t>(kb) * A_STAGE_BYTES), hi128,
-                                        lo_of(w1_base + static_cast<uint32_t>(kb) * w1_kb_bytes + static_cast<uint32_t>(h) * (128u * 128u)), hi128,
+                                        lo_of(w1_base + static_cast<uint32_t>(kb) * w1_kb_bytes + static_cast<uint32_t>(h * p.UW) * 128u), hi128,
                                         idesc1, static_cast<uint32_t>(kb != 0));
                     umma_commit(acc1_full_bar(s));
                     if (h == p.H - 1) umma_commit(a_empty_bar(sa));       // the x tile is free once these MMAs have read it
                 }
                 if (step >= DUAL_LAG) {
-                    // GEMM 2, the two k-blocks that half `v` of y contributes: A = the finished y slot
+                    // GEMM 2, the k-blocks (one per panel) that unit `v` of y contributes: A = the finished y slot
                     const int v = step - DUAL_LAG;
                     const int jt = v / p.H, hh = v - jt * p.H;
-                    const int s = v % DUAL_YSLOTS, b = jt & 1;
+                    const int s = v % p.ys, b = jt & 1;
                     if (hh == 0) failed |= !mbar_wait(acc2_empty_bar(b), (static_cast<uint32_t>(jt >> 1) & 1u) ^ 1u, abort_flag);
-                    failed |= !mbar_wait(y_done_bar(s), static_cast<uint32_t>(v / DUAL_YSLOTS) & 1u, abort_flag);
+                    failed |= !mbar_wait(y_done_bar(s), static_cast<uint32_t>(v / p.ys) & 1u, abort_flag);
                     tc_fence_after();
-                    for (int j = 0; j < 2; ++j)
-                        umma_f16_kblock(tmem_base + static_cast<uint32_t>(DUAL_ACC2_COL + b * 64),
+                    for (int j = 0; j < p.UP; ++j)
+                        umma_f16_kblock(tmem_base + static_cast<uint32_t>(p.acc2_col + b * p.acc2_stride),
                                         lo_of(y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(j) * SUB_BYTES), hi128,
-                                        lo_of(w2_base + static_cast<uint32_t>(2 * hh + j) * w2_kb_bytes), hi128, idesc2,
+                                        lo_of(w2_base + static_cast<uint32_t>(hh * p.UP + j) * w2_kb_bytes), hi128, idesc2,
                                         static_cast<uint32_t>((hh | j) != 0));
                     umma_commit(y_free_bar(s));
                     if (hh == p.H - 1) umma_commit(acc2_full_bar(b));
@@ -2293,7 +2296,7 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 return;
             }
             tc_fence_after();
-            const uint32_t t = t_lane + static_cast<uint32_t>(DUAL_ACC2_COL + b * 64);
+            const uint32_t t = t_lane + static_cast<uint32_t>(p.acc2_col + b * p.acc2_stride);
             const uint32_t srow = z_base + static_cast<uint32_t>(row) * 128u;
             if (act2_t == 0) epilogue_rows<0, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
             else if (act2_t == 1) epilogue_rows<1, false>(q2, t, srow, row_xor, bias2_s, 0, p.N2, group);
@@ -2311,8 +2314,8 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int u = 0;
         for (int it = 0; ok && it < T; ++it) {
             for (int h = 0; ok && h < p.H; ++h, ++u) {
-                const int s = u % DUAL_YSLOTS;
-                const uint32_t par = static_cast<uint32_t>(u / DUAL_YSLOTS) & 1u;
+                const int s = u % p.ys;
+                const uint32_t par = static_cast<uint32_t>(u / p.ys) & 1u;
                 const bool got = p.has_res ? mbar_wait<EPI_BACKOFF_NS>(res_full_bar(s), par, abort_flag)
                                            : mbar_wait<EPI_BACKOFF_NS>(y_free_bar(s), par ^ 1u, abort_flag);
                 if (!got || !mbar_wait<EPI_BACKOFF_NS>(acc1_full_bar(s), par, abort_flag)) {
@@ -2321,20 +2324,20 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     break;
                 }
                 tc_fence_after();
-                const uint32_t t = t_lane + static_cast<uint32_t>(s * 128);
+                const uint32_t t = t_lane + static_cast<uint32_t>(s * p.UW);
                 const uint32_t srow = y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(row) * 128u;
                 const int variant = act1_t * 2 + (p.has_res ? 1 : 0);
                 switch (variant) {
-                    case 0: epilogue_rows<0, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 1: epilogue_rows<0, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 2: epilogue_rows<1, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 3: epilogue_rows<1, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 4: epilogue_rows<2, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 5: epilogue_rows<2, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 6: epilogue_rows<3, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 7: epilogue_rows<3, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    case 10: epilogue_rows<5, false>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
-                    default: epilogue_rows<5, true>(q1, t, srow, row_xor, bias1_s, h * 128, 128, group); break;
+                    case 0: epilogue_rows<0, false>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 1: epilogue_rows<0, true>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 2: epilogue_rows<1, false>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 3: epilogue_rows<1, true>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 4: epilogue_rows<2, false>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 5: epilogue_rows<2, true>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 6: epilogue_rows<3, false>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 7: epilogue_rows<3, true>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    case 10: epilogue_rows<5, false>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
+                    default: epilogue_rows<5, true>(q1, t, srow, row_xor, bias1_s, h * p.UW, p.UW, group); break;
                 }
                 tc_fence_before();
                 fence_proxy_async_smem();
@@ -2359,7 +2362,7 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     ok = false;
                     return;
                 }
-                tma_store_2d(&tmap_z, z_base, 0, tile_row0(j));
+                for (int c = 0; c < p.zp; ++c) tma_store_2d(&tmap_z, z_base + static_cast<uint32_t>(c) * SUB_BYTES, c * 64, tile_row0(j));
                 tma_store_commit();
                 tma_store_wait_read();
                 mbar_arrive(z_free_bar);
@@ -2368,15 +2371,15 @@ conv_dual_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int it = 0; ok && it < T; ++it) {
                 const int m0 = tile_row0(it);
                 for (int h = 0; ok && h < p.H; ++h, ++u) {
-                    const int s = u % DUAL_YSLOTS;
-                    if (!mbar_wait<EPI_BACKOFF_NS>(y_done_bar(s), static_cast<uint32_t>(u / DUAL_YSLOTS) & 1u, abort_flag)) {
+                    const int s = u % p.ys;
+                    if (!mbar_wait<EPI_BACKOFF_NS>(y_done_bar(s), static_cast<uint32_t>(u / p.ys) & 1u, abort_flag)) {
                         atomicExch(p.status, STATUS_WAIT_DUAL);
                         ok = false;
                         break;
                     }
-                    for (int j = 0; j < 2; ++j)
+                    for (int j = 0; j < p.UP; ++j)
                         tma_store_2d(&tmap_y, y_base + static_cast<uint32_t>(s) * y_slot_bytes + static_cast<uint32_t>(j) * SUB_BYTES,
-                                     h * 128 + j * 64, m0, pol_y);
+                                     h * p.UW + j * 64, m0, pol_y);
                     tma_store_commit();
                     tma_store_wait_read();
                     mbar_arrive(y_free_bar(s));
@@ -3300,7 +3303,7 @@ int conv_chain_launch(const fvm_chain_layer* layers, int n, cudaStream_t stream)
 // ------------------------------------------------------------------------------------------------ two layers, one launch
 // y = act1(x * w1^T + b1 [+ res]) ([M, K1], row stride ldy) and z = act2(y * w2^T + b2) ([M, K2], row stride ldz) as one
 // launch of conv_dual_kernel. x [M, C1] (row stride ldx), w1 [K1][C1], w2 [K2][K1]; (C1, K1) is (64, 128), (64, 256) or
-// (128, 128), K2 a multiple of 16 up to 64; activations 0 (none) or 1 (ReLU) run specialised, the others through the generic code.
+// (128, 128), K2 a multiple of 16 up to 128; activations 0 (none) or 1 (ReLU) run specialised, the others through the generic code.
 // Refused (FVM_ERR_ARG, nothing launched): other shapes, misaligned pointers, outputs that overlap an input or each other.
 int conv_dual_launch(const void* x, const void* w1, const void* b1, const void* res, void* y, const void* w2, const void* b2,
                      void* z, long long M, int C1, int K1, int K2, long long ldx, long long ldr, long long ldy, long long ldz,
@@ -3309,7 +3312,7 @@ int conv_dual_launch(const void* x, const void* w1, const void* b1, const void* 
     if (!st) return FVM_ERR_SETUP;
     if (!x || !w1 || !y || !w2 || !z) return FVM_ERR_ARG;
     if (M <= 0 || M > 0x7fffff00ll) return FVM_ERR_ARG;
-    if ((C1 != 64 && C1 != 128) || (K1 != 128 && K1 != 256) || C1 * K1 > 64 * 256 || K2 < 16 || K2 > 64 || (K2 & 15)) return FVM_ERR_ARG;
+    if ((C1 != 64 && C1 != 128) || (K1 != 128 && K1 != 256) || C1 * K1 > 64 * 256 || K2 < 16 || K2 > 128 || (K2 & 15)) return FVM_ERR_ARG;
     if (act1 < 0 || act1 > 6 || act2 < 0 || act2 > 6) return FVM_ERR_ARG;
     if ((ldx & 7) || ldx < C1 || (ldy & 7) || ldy < K1 || (ldz & 7) || ldz < K2 || (res && ((ldr & 7) || ldr < K1))) return FVM_ERR_ARG;
     const void* ptrs[8] = {x, w1, b1, res, y, w2, b2, z};
@@ -3327,8 +3330,16 @@ int conv_dual_launch(const void* x, const void* w1, const void* b1, const void* 
     p.m_tiles = static_cast<int>((M + BM - 1) / BM);
     p.kb1 = C1 / 64;
     p.K1 = K1;
-    p.H = K1 / 128;
     p.N2 = K2;
+    // z up to 64 channels: y in units of 128 channels, three slots (3 x 128 + 2 x 64 TMEM columns); wider z: units of 64
+    // channels, four slots (4 x 64 + 2 x 128 columns) -- shared memory then still holds both weight tensors
+    p.UW = K2 <= 64 ? 128 : 64;
+    p.UP = p.UW / 64;
+    p.ys = K2 <= 64 ? 3 : 4;
+    p.H = K1 / p.UW;
+    p.acc2_col = p.ys * p.UW;
+    p.acc2_stride = K2 <= 64 ? 64 : 128;
+    p.zp = (K2 + 63) / 64;
     p.act1 = act1;
     p.act2 = act2;
     p.has_res = res != nullptr;
@@ -3345,7 +3356,7 @@ int conv_dual_launch(const void* x, const void* w1, const void* b1, const void* 
         }
     }
     const uint32_t fixed = 1024 + static_cast<uint32_t>(p.kb1 * K1) * 128u + static_cast<uint32_t>((K1 / 64) * K2) * 128u +
-                           DUAL_YSLOTS * 2 * SUB_BYTES + SUB_BYTES + 8 * DUAL_NUM_BARRIERS + DUAL_MISC_BYTES +
+                           static_cast<uint32_t>(p.ys * p.UP + p.zp) * SUB_BYTES + 8 * DUAL_NUM_BARRIERS + DUAL_MISC_BYTES +
                            ((static_cast<uint32_t>(K1 + K2) * 4 + 15u) & ~15u);
     const uint32_t a_stage = static_cast<uint32_t>(p.kb1) * A_STAGE_BYTES;
     if (fixed + 2 * a_stage > 227u * 1024) return FVM_ERR_ARG;

@@ -304,8 +304,8 @@ def pw_into(x, w, bias, res, act: int, out: torch.Tensor, force: int = 0) -> Non
 
 def pw_dual_ok(C1: int, K1: int, K2: int) -> bool:
     """Shapes fvm_conv_dual_f16 takes: (C1, K1) one of (64, 128), (64, 256), (128, 128) -- both weight tensors stay in
-    shared memory -- and K2 a multiple of 16 up to 64."""
-    return (C1, K1) in ((64, 128), (64, 256), (128, 128)) and 16 <= K2 <= 64 and K2 % 16 == 0
+    shared memory -- and K2 a multiple of 16 up to 128."""
+    return (C1, K1) in ((64, 128), (64, 256), (128, 128)) and 16 <= K2 <= 128 and K2 % 16 == 0
 
 
 def pw_dual(x, w1, b1, res, act1: int, w2, b2, act2: int):

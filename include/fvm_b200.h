@@ -127,7 +127,7 @@ int fvm_conv_chain_f16(const fvm_chain_layer* layers, int n_layers, void* stream
  *   z = act2(y * w2^T + b2)           w2 [K2][K1], z [M, K2] (row stride ldz)
  * y is written to global memory once and read by the second layer from the shared-memory tile it was stored from, so
  * the second layer costs its weights and its output only. Same bits as two fvm_conv2d_f16 calls. (C1, K1) is (64, 128),
- * (64, 256) or (128, 128) (both weight tensors stay in shared memory), K2 a multiple of 16 up to 64; returns 1 with
+ * (64, 256) or (128, 128) (both weight tensors stay in shared memory), K2 a multiple of 16 up to 128; returns 1 with
  * nothing launched for other shapes, for misaligned pointers (16 bytes) or when y or z overlaps another operand. */
 int fvm_conv_dual_f16(const void* x, const void* w1, const void* b1, const void* res, void* y, const void* w2,
                       const void* b2, void* z, long long M, int C1, int K1, int K2, long long ldx, long long ldr,

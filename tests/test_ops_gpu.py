@@ -291,6 +291,9 @@ DUAL_CASES = [
     (4, 30, 30, 128, 128, 32, 3, 5, False),    # no residual, SiLU / GELU through the generic activation code
     (1, 1, 1, 64, 256, 64, 1, 1, False),       # a single pixel
     (64, 28, 28, 128, 128, 64, 1, 1, True),    # more tiles than one wave, fewer than three
+    (64, 56, 56, 64, 256, 128, 1, 1, True),    # z wider than 64 channels (y in 64-channel units): stage 1 -> stage 2 of ResNet-50
+    (3, 17, 11, 128, 128, 128, 1, 1, True),    # the same mode with two k-blocks, ragged
+    (2, 21, 21, 64, 128, 80, 0, 1, False),     # 80 output channels, no residual
 ]
 
 
@@ -334,6 +337,7 @@ def test_pw_dual_against_the_oracle_and_refusals():
     args = lambda y_ptr, K2: (xd.data_ptr(), w1d.data_ptr(), None, None, y_ptr, w2d.data_ptr(), None, zd.data_ptr(),
                               N * H * W, 64, 256, K2, 64, 0, 256, 64, 1, 1, None)
     assert L.fvm_conv_dual_f16(*args(yd.data_ptr(), 40)) == 1           # K2 not a multiple of 16
+    assert L.fvm_conv_dual_f16(*args(yd.data_ptr(), 144)) == 1          # K2 above 128
     assert L.fvm_conv_dual_f16(*args(xd.data_ptr(), 64)) == 1           # y overlaps x
     assert L.fvm_conv_dual_f16(*args(yd.data_ptr() + 8, 64)) == 1       # misaligned y
     assert ops.launches() == before
