@@ -588,6 +588,81 @@ __global__ void up_argmax_kernel(const __half* __restrict__ s, int32_t* __restri
     out[i] = arg;
 }
 
+// The same for an upsample by a power-of-two factor SF without corner alignment (the DeepLab tail: SF = 8). The SF
+// output pixels [g*SF - SF/2, g*SF + SF/2) of a row lie between the same two source columns g - 1 and g, so one thread
+// takes such a group: it loads and converts the four source pixels once, interpolates vertically once per channel and
+// then only the horizontal lerp and the comparison are per output pixel -- about a fifth of the instructions of the
+// per-pixel kernel, which is bound by the FMA pipe. Weights come from the same index function; the sums are formed
+// in another order than in up_argmax_kernel (vertical first), so a class map can differ from it where two scores are
+// within a rounding error of each other.
+template <int SF>
+__global__ void up_argmax_group_kernel(const __half* __restrict__ s, int32_t* __restrict__ out, int h, int w, int C,
+                                       long long ld, int H, int W, float sch, float scw, long long total) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int g = static_cast<int>(i % (w + 1));
+    long long t = i / (w + 1);
+    const int oy = static_cast<int>(t % H);
+    const long long n = t / H;
+    const int ox0 = g * SF - SF / 2;
+    const int j0 = ox0 < 0 ? -ox0 : 0, j1 = ox0 + SF > W ? W - ox0 : SF;     // valid outputs of this group
+    int y0, y1, x0, x1;
+    float ly, lx[SF];
+    src_index(oy, sch, 0, h, y0, y1, ly);
+    {
+        float l;
+        src_index(ox0 + j0, scw, 0, w, x0, x1, l);
+    }
+#pragma unroll
+    for (int j = 0; j < SF; ++j) {
+        int a0, a1;
+        src_index(min(max(ox0 + j, 0), W - 1), scw, 0, w, a0, a1, lx[j]);
+    }
+    const float hy = 1.f - ly;
+    const __half* img = s + n * h * w * ld;
+    const __half* pa = img + (static_cast<long long>(y0) * w + x0) * ld;
+    const __half* pb = img + (static_cast<long long>(y0) * w + x1) * ld;
+    const __half* pc = img + (static_cast<long long>(y1) * w + x0) * ld;
+    const __half* pd = img + (static_cast<long long>(y1) * w + x1) * ld;
+    float best[SF];
+    int arg[SF];
+#pragma unroll
+    for (int j = 0; j < SF; ++j) {
+        best[j] = -INFINITY;
+        arg[j] = 0;
+    }
+    for (int c0 = 0; c0 < C; c0 += 8) {
+        float a[8], b[8], c[8], d[8];
+        to_f8(ldg16(pa + c0), a);
+        to_f8(ldg16(pb + c0), b);
+        to_f8(ldg16(pc + c0), c);
+        to_f8(ldg16(pd + c0), d);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (c0 + k < C) {
+                const float va = hy * a[k] + ly * c[k], vb = hy * b[k] + ly * d[k];
+#pragma unroll
+                for (int j = 0; j < SF; ++j) {
+                    const float val = (1.f - lx[j]) * va + lx[j] * vb;
+                    if (val > best[j]) {
+                        best[j] = val;
+                        arg[j] = c0 + k;
+                    }
+                }
+            }
+        }
+    }
+    int32_t* dst = out + (n * H + oy) * W + ox0;
+    if (SF >= 4 && j0 == 0 && j1 == SF && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < SF; j += 4) *reinterpret_cast<int4*>(dst + j) = make_int4(arg[j], arg[j + 1], arg[j + 2], arg[j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < SF; ++j)
+            if (j >= j0 && j < j1) dst[j] = arg[j];
+    }
+}
+
 // ------------------------------------------------------------------------------------------- host wrappers
 #define FVM_LAUNCH_CHECK()                                                   \
     do {                                                                     \
@@ -931,6 +1006,19 @@ extern "C" int fvm_up_argmax_f16(const void* s, int32_t* out, int N, int h, int 
     if (!s || !out || N <= 0 || h <= 0 || w <= 0 || H <= 0 || W <= 0 || C <= 0 || (ld & 7) || ld < C || !aligned16(s))
         return FVM_ERR_ARG;
     if (((C + 7) & ~7) > ld) return FVM_ERR_ARG;   // whole 16-byte vectors are read
+    // power-of-two upsample without corner alignment: one thread per group of SF output pixels between two source columns
+    static const int use_groups = [] { const char* v = getenv("FVM_B200_UP_GROUPS"); return (v && v[0] == '0') ? 0 : 1; }();
+    if (use_groups && !align && w > 0 && H % h == 0 && W % w == 0 && H / h == W / w) {
+        const int sf = W / w;
+        const long long groups = static_cast<long long>(N) * H * (w + 1);
+        const float sch = resize_scale(h, H, 0, 0.f), scw = resize_scale(w, W, 0, 0.f);
+        const __half* sp = static_cast<const __half*>(s);
+        cudaStream_t st_ = static_cast<cudaStream_t>(stream);
+        if (sf == 2) { up_argmax_group_kernel<2><<<blocks_for(groups, 256), 256, 0, st_>>>(sp, out, h, w, C, ld, H, W, sch, scw, groups); FVM_LAUNCH_CHECK(); }
+        if (sf == 4) { up_argmax_group_kernel<4><<<blocks_for(groups, 256), 256, 0, st_>>>(sp, out, h, w, C, ld, H, W, sch, scw, groups); FVM_LAUNCH_CHECK(); }
+        if (sf == 8) { up_argmax_group_kernel<8><<<blocks_for(groups, 256), 256, 0, st_>>>(sp, out, h, w, C, ld, H, W, sch, scw, groups); FVM_LAUNCH_CHECK(); }
+        if (sf == 16) { up_argmax_group_kernel<16><<<blocks_for(groups, 256), 256, 0, st_>>>(sp, out, h, w, C, ld, H, W, sch, scw, groups); FVM_LAUNCH_CHECK(); }
+    }
     const long long total = static_cast<long long>(N) * H * W;
     up_argmax_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(s), out, h, w, C, ld, H, W, align, resize_scale(h, H, align, 0.f),

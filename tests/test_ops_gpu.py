@@ -833,6 +833,26 @@ def test_input_and_elementwise_ops_match_oracle():
     close(ops.add_act(cl(y), cl(r), 1), R.add_act_ref(y, r, 1))
 
 
+@pytest.mark.parametrize("case", [(2, 19, 9, 13, 2), (1, 21, 5, 7, 4), (2, 24, 11, 6, 8), (1, 19, 3, 5, 16), (3, 8, 1, 1, 8),
+                                  (1, 150, 6, 1, 4)])
+def test_up_argmax_power_of_two_factors(case):
+    # upsample by 2 / 4 / 8 / 16 without corner alignment: one thread per group of output pixels between two source
+    # columns (vertical lerp first); against the oracle, and with duplicated channels the first maximum must win
+    N, classes, h, w, sf = case
+    C = (classes + 7) // 8 * 8
+    x = gen((N, C, h, w), 90 + sf)
+    am = ops.up_argmax(cl(x), h * sf, w * sf, False, num_classes=classes).cpu()
+    ref = R.up_argmax_ref(x, h * sf, w * sf, False, num_classes=classes)
+    assert am.dtype == torch.int32 and am.shape == ref.shape
+    assert (am == ref).float().mean() >= 0.999
+    assert int(am.max()) < classes
+    if classes >= 4:
+        x2 = x.clone()
+        x2[:, 3] = x2[:, 1]                    # channel 3 ties with channel 1 everywhere: 3 must never be reported
+        am2 = ops.up_argmax(cl(x2), h * sf, w * sf, False, num_classes=classes).cpu()
+        assert not bool((am2 == 3).any())
+
+
 @pytest.mark.parametrize("align", [False, True])
 def test_bilinear_and_up_argmax_match_oracle(align):
     x = gen((2, 256, 1, 1), 1)
