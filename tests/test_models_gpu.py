@@ -65,6 +65,28 @@ def test_resnet50_batch64_agreement_with_upstream_fp32_and_portable_on_device():
     assert (fast.argmax(1) == y32.argmax(1)).float().mean() >= 0.995
 
 
+def test_resnet50_two_layer_launches_leave_the_logits_bit_identical(monkeypatch):
+    # the trunk with a block's last 1x1 convolution and the next block's first as one launch (stage 1; with the wide form
+    # also the step into stage 2) against one launch per layer: the same logits bit for bit, and fewer launches
+    from fast_vision_models_b200 import ops
+    from fast_vision_models_b200.classification import fast
+    x = seeded_input((4, 3, 224, 224), seed=11).cuda()
+    outs, launches = [], []
+    for dual, wide in ((False, False), (True, False), (True, True)):
+        monkeypatch.setattr(fast, "DUAL_RESNET", dual)
+        monkeypatch.setattr(fast, "DUAL_WIDE", wide)
+        m = zoo.load("resnet50", "b200", device="cuda", seed=1, graphs=False)
+        with torch.inference_mode():
+            m.model(x)                      # tile tuning happens here
+            before = ops.launches()
+            outs.append(m.model(x).clone())
+            launches.append(ops.launches() - before)
+        assert len(m.model.net.trunk.dual_after) == (0 if not dual else 3 if wide else 2)
+    assert ops.last_status() == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert launches[1] == launches[0] - 2 and launches[2] == launches[0] - 3
+
+
 def test_other_batch_and_resolution_need_no_recompile():
     m = zoo.load("resnet18", "b200", device="cuda", seed=1)
     up = zoo.load("resnet18", "upstream", device="cuda", seed=1).model
