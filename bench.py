@@ -345,6 +345,7 @@ def main():
     # host memory. Every byte in and out is inside the timed region.
     runners = [m.model.runner, Fast(m.model.net).runner]
     copy_stream = torch.cuda.Stream(device=dev)
+    out_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream()
 
     def e2e_windows(dtype):
@@ -353,8 +354,10 @@ def main():
         bufs = [r.static_buffers(hx[0].to(dev)) for r in runners]         # (graph, static_in, static_out) per runner
         ready = [torch.cuda.Event() for _ in range(2)]
         consumed = [torch.cuda.Event() for _ in range(2)]
+        drained = [torch.cuda.Event() for _ in range(2)]
         for b in range(2):
             consumed[b].record(main_stream)
+            drained[b].record(main_stream)
 
         def step(i):
             b = i % 2
@@ -364,9 +367,13 @@ def main():
                 static_in.copy_(hx[b], non_blocking=True)    # host -> device, straight into the graph's input
                 ready[b].record(copy_stream)
             main_stream.wait_event(ready[b])
+            main_stream.wait_event(drained[b])               # the logits this replica wrote two steps ago have left
             graph.replay()
             consumed[b].record(main_stream)
-            hy[b].copy_(static_out, non_blocking=True)       # device -> host
+            with torch.cuda.stream(out_stream):              # device -> host under the next forward
+                out_stream.wait_event(consumed[b])
+                hy[b].copy_(static_out, non_blocking=True)
+                drained[b].record(out_stream)
 
         for i in range(warmup):
             step(i)
