@@ -269,7 +269,6 @@ def main():
     import torch.distributed as dist
     from fast_vision_models_b200 import ops, parallel
     from fast_vision_models_b200.classification import zoo
-    from fast_vision_models_b200.classification.fast import Fast
     from fast_vision_models_b200.weights import seeded_input
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device: the b200 tier has no CPU path"
@@ -340,40 +339,16 @@ def main():
     assert torch.isfinite(y).all()
 
     # ---------------------------------------------------------------- e2e: pinned host buffers in, logits out
-    # Two graph runners over the same network (ping-pong): the copy stream writes batch i+1 from pinned host memory
-    # straight into one runner's static input while the other runner's graph computes batch i; logits go back to pinned
-    # host memory. Every byte in and out is inside the timed region.
-    runners = [m.model.runner, Fast(m.model.net).runner]
-    copy_stream = torch.cuda.Stream(device=dev)
-    out_stream = torch.cuda.Stream(device=dev)
-    main_stream = torch.cuda.current_stream()
-
+    # The library's serving loop for host batches (Fast.host_pipeline -> runtime.HostPipeline): two graph replicas of the
+    # network in rotation; the copy stream writes batch i+1 from pinned host memory straight into one replica's static
+    # input while the other replica's graph computes batch i, and the logits of batch i-1 leave on a third stream into
+    # pinned host memory. Every byte in and out is inside the timed region.
     def e2e_windows(dtype):
         hx = [seeded_input((BATCH, 3, size, size), seed=200 + 100 * rank + i).to(dtype).pin_memory() for i in range(2)]
-        hy = [torch.empty((BATCH, 1000), dtype=torch.float32).pin_memory() for _ in range(2)]
-        bufs = [r.static_buffers(hx[0].to(dev)) for r in runners]         # (graph, static_in, static_out) per runner
-        ready = [torch.cuda.Event() for _ in range(2)]
-        consumed = [torch.cuda.Event() for _ in range(2)]
-        drained = [torch.cuda.Event() for _ in range(2)]
-        for b in range(2):
-            consumed[b].record(main_stream)
-            drained[b].record(main_stream)
+        pipe = m.model.host_pipeline(hx[0], replicas=2)
 
         def step(i):
-            b = i % 2
-            graph, static_in, static_out = bufs[b]
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(consumed[b])          # the replay that last read this static input is done
-                static_in.copy_(hx[b], non_blocking=True)    # host -> device, straight into the graph's input
-                ready[b].record(copy_stream)
-            main_stream.wait_event(ready[b])
-            main_stream.wait_event(drained[b])               # the logits this replica wrote two steps ago have left
-            graph.replay()
-            consumed[b].record(main_stream)
-            with torch.cuda.stream(out_stream):              # device -> host under the next forward
-                out_stream.wait_event(consumed[b])
-                hy[b].copy_(static_out, non_blocking=True)
-                drained[b].record(out_stream)
+            return pipe.submit(hx[i % 2])
 
         for i in range(warmup):
             step(i)
@@ -389,8 +364,9 @@ def main():
             torch.cuda.synchronize()
             wins.append((time.perf_counter() - t0) * 1e3)
             barrier()
-        assert torch.isfinite(hy[0]).all() and torch.isfinite(hy[1]).all()
-        return wins, hx[0].numel() * hx[0].element_size()
+        assert torch.isfinite(pipe.result(0)).all() and torch.isfinite(pipe.result(1)).all()
+        assert pipe.out_bytes == BATCH * 1000 * 4
+        return wins, pipe.in_bytes
 
     win_e2e, h2d_bytes = e2e_windows(torch.float32)
     win_e2e16, h2d_bytes16 = e2e_windows(torch.float16)

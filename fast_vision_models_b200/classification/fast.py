@@ -30,7 +30,7 @@ from torch import nn
 
 from .. import fold, ops
 from ..layers import GATE_IN_WEIGHTS, DepthwiseConv, FusedConv, LayerNormCL, SqueezeExcite, act_code
-from ..runtime import GraphRunner
+from ..runtime import GraphRunner, HostPipeline
 
 # Bottleneck stages as chain launches (ops.chain_begin): measured on B200 at batch 64, one launch per layer is as fast
 # (stage 4 only: 1.127 against 1.129 ms per forward) or faster (from stage 3: 1.16 ms, from stage 2: 1.17-1.19 ms),
@@ -306,6 +306,13 @@ class Fast(nn.Module):
     @property
     def runner(self) -> GraphRunner:
         return self._runner
+
+    def host_pipeline(self, example: torch.Tensor, replicas: int = 2) -> HostPipeline:
+        """A serving loop for batches that arrive in pinned host memory: `replicas` graph replicas of this network in
+        rotation, host -> device and device -> host copies on their own streams (runtime.HostPipeline). `example` is a
+        batch of the shape and dtype (fp32 or fp16 NCHW image batch) that will be submitted."""
+        runners = [self._runner] + [Fast(self.net).runner for _ in range(max(2, replicas) - 1)]
+        return HostPipeline(runners, as_image(example))
 
 
 class Portable(nn.Module):

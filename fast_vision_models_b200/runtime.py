@@ -14,7 +14,7 @@ from __future__ import annotations
 import os
 import time
 from collections import OrderedDict
-from typing import Callable
+from typing import Callable, Sequence
 
 import torch
 
@@ -101,3 +101,60 @@ class GraphRunner:
         code = ops.last_status()
         if code:
             raise ops.FvmError(f"device status {code:#x}: a bounded wait inside a kernel ran out")
+
+
+class HostPipeline:
+    """Batches from pinned host memory in, results in pinned host memory out, with both copies under the forwards.
+
+    `runners` are graph runners over the same network (two or more: while one replica's graph computes batch i, the copy
+    stream writes batch i+1 straight into another replica's static input, and the results of batch i-1 leave on a third
+    stream). `submit(x_host)` enqueues one batch and returns its slot; `result(slot)` waits for that batch's results
+    only. A slot's host buffer is rewritten when the slot comes round again, len(runners) submissions later.
+    The reference serves through `Fast.__call__` on device tensors (classification/fast/__init__.py:81-95); this is the
+    same call with the host <-> device copies taken off the compute stream."""
+
+    def __init__(self, runners: Sequence[GraphRunner], example: torch.Tensor, device=None):
+        if len(runners) < 2:
+            raise ValueError("HostPipeline needs at least two runners (replicas of one network)")
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        x0 = example.to(dev)
+        self._bufs = [r.static_buffers(x0) for r in runners]          # (graph, static_in, static_out) per replica
+        self._main = torch.cuda.current_stream(dev)
+        self._in_stream = torch.cuda.Stream(device=dev)
+        self._out_stream = torch.cuda.Stream(device=dev)
+        n = len(runners)
+        self._ready = [torch.cuda.Event() for _ in range(n)]
+        self._consumed = [torch.cuda.Event() for _ in range(n)]
+        self._drained = [torch.cuda.Event() for _ in range(n)]
+        self._host_out = [torch.empty(tuple(b[2].shape), dtype=b[2].dtype).pin_memory() for b in self._bufs]
+        for b in range(n):
+            self._consumed[b].record(self._main)
+            self._drained[b].record(self._main)
+        self._next = 0
+        self.in_bytes = x0.numel() * x0.element_size()
+        self.out_bytes = self._host_out[0].numel() * self._host_out[0].element_size()
+
+    def submit(self, x_host: torch.Tensor) -> int:
+        b = self._next
+        self._next = (b + 1) % len(self._bufs)
+        graph, static_in, static_out = self._bufs[b]
+        if tuple(x_host.shape) != tuple(static_in.shape) or x_host.dtype != static_in.dtype:
+            raise ops.FvmError("HostPipeline.submit: batch shape / dtype differs from the example the pipeline was built for")
+        with torch.cuda.stream(self._in_stream):
+            self._in_stream.wait_event(self._consumed[b])      # the replay that last read this static input is done
+            static_in.copy_(x_host, non_blocking=True)         # host -> device, straight into the graph's input
+            self._ready[b].record(self._in_stream)
+        self._main.wait_event(self._ready[b])
+        self._main.wait_event(self._drained[b])                # the results this replica wrote last time have left
+        with torch.cuda.stream(self._main):
+            graph.replay()
+        self._consumed[b].record(self._main)
+        with torch.cuda.stream(self._out_stream):              # device -> host under the next forward
+            self._out_stream.wait_event(self._consumed[b])
+            self._host_out[b].copy_(static_out, non_blocking=True)
+            self._drained[b].record(self._out_stream)
+        return b
+
+    def result(self, slot: int) -> torch.Tensor:
+        self._drained[slot].synchronize()
+        return self._host_out[slot]

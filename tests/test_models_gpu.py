@@ -87,6 +87,27 @@ def test_resnet50_two_layer_launches_leave_the_logits_bit_identical(monkeypatch)
     assert launches[1] == launches[0] - 2 and launches[2] == launches[0] - 3
 
 
+def test_host_pipeline_returns_each_batch_its_own_result():
+    # the serving loop for pinned host batches (two graph replicas, copies on their own streams): every submitted batch
+    # comes back with the logits a direct call gives, also when results are collected late and slots are reused
+    m = zoo.load("resnet18", "b200", device="cuda", seed=1)
+    xs = [seeded_input((3, 3, 96, 128), seed=40 + i).pin_memory() for i in range(5)]
+    with torch.inference_mode():
+        want = [m.model(x.cuda()).cpu() for x in xs]
+        pipe = m.model.host_pipeline(xs[0], replicas=2)
+        got = []
+        slot_prev = pipe.submit(xs[0])
+        for i in range(1, 5):
+            slot = pipe.submit(xs[i])
+            got.append(pipe.result(slot_prev).clone())      # collected while the next batch is in flight
+            slot_prev = slot
+        got.append(pipe.result(slot_prev).clone())
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    with pytest.raises(Exception):
+        pipe.submit(xs[0][:2])                              # another batch size than the pipeline was built for
+
+
 def test_other_batch_and_resolution_need_no_recompile():
     m = zoo.load("resnet18", "b200", device="cuda", seed=1)
     up = zoo.load("resnet18", "upstream", device="cuda", seed=1).model
