@@ -84,7 +84,8 @@ class GraphRunner:
         code = ops.poll_status()          # a fault reported by an earlier replay (no synchronisation here)
         if code:
             raise ops.FvmError(f"device status {code:#x}: a bounded wait inside a kernel ran out in an earlier launch")
-        ent.static_in.copy_(x, non_blocking=True)
+        if x.data_ptr() != ent.static_in.data_ptr():     # a caller may fill the static input itself (static_buffers)
+            ent.static_in.copy_(x, non_blocking=True)
         ent.graph.replay()
         out = ent.static_out
         return out.clone() if isinstance(out, torch.Tensor) else out
