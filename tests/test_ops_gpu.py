@@ -174,6 +174,41 @@ def test_conv_stream_k_is_refused_where_it_does_not_apply():
         ops.conv_fused(x8, w8, None, None, (3, 3), (2, 2), 0, tile_n=1 << 28)        # tap-packed stem
 
 
+def _random_conv_cases(n, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < n:
+        R_ = rng.choice([1, 1, 3, 3, 5])
+        stride = rng.choice([1, 1, 2])
+        dil = rng.choice([1, 1, 2]) if R_ > 1 else 1
+        pad = rng.choice([0, (R_ // 2) * dil, R_ // 2]) if R_ > 1 else 0
+        C = 8 * rng.randint(1, 40)
+        K = 8 * rng.randint(1, 40)
+        N = rng.randint(1, 9)
+        H, W = rng.randint(1, 40), rng.randint(1, 40)
+        if (H + 2 * pad - dil * (R_ - 1) - 1) // stride + 1 <= 0 or (W + 2 * pad - dil * (R_ - 1) - 1) // stride + 1 <= 0:
+            continue
+        cases.append((N, H, W, C, K, R_, pad, stride, dil, rng.random() < 0.4, rng.choice([0, 1, 1, 3, 5]), rng.random() < 0.8))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_conv_cases(40, 2024))
+def test_conv_random_shapes_with_the_library_s_own_tile_choice(case):
+    # shapes drawn at random (seeded): whatever mode and tile the library picks for them (single CTA or pair, staged
+    # patches, resident weights, tap-packed 8 / 16-channel inputs, reverse tile order) must agree with the oracle
+    N, H, W, C, K, R_, pad, stride, dil, res, act, has_bias = case
+    x, w = gen((N, C, H, W), 61), gen((K, C, R_, R_), 62, 1.0 / (C * R_ * R_) ** 0.5)
+    b = gen((K,), 63, 0.1) if has_bias else None
+    P = (H + 2 * pad - dil * (R_ - 1) - 1) // stride + 1
+    Q = (W + 2 * pad - dil * (R_ - 1) - 1) // stride + 1
+    r = gen((N, K, P, Q), 64) if res else None
+    y = ops.conv_fused(cl(x), cl(w), None if b is None else b.to(DEV), None if r is None else cl(r), (pad, pad),
+                       (stride, stride), act, dilation=(dil, dil))
+    assert ops.last_status() == 0
+    close(y, R.conv_fused_ref(x, w, b, r, (pad, pad), (stride, stride), act, dilation=(dil, dil)))
+
+
 PAIR_CASES = [
     # N, H, W, C, K, R, pad, stride, res, act, tile width (0 = library's choice)
     (64, 14, 14, 1024, 256, 1, 0, 1, False, 1, 256),   # 49 tiles of 256 pixels x 256 channels, 16 k-blocks
