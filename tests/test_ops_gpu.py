@@ -743,6 +743,35 @@ def test_dwconv_matches_oracle(case):
     close(y, ref)
 
 
+def _random_dw_cases(n, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < n:
+        k = rng.choice([3, 3, 5, 7, rng.choice([1, 2, 4, 9])])
+        stride = rng.choice([1, 1, 2])
+        dil = rng.choice([1, 1, 1, 2])
+        pad = rng.choice([(k // 2) * dil, k // 2, 0])
+        C = 8 * rng.randint(1, 50)
+        N, H, W = rng.randint(1, 5), rng.randint(1, 45), rng.randint(1, 45)
+        if (H + 2 * pad - dil * (k - 1) - 1) // stride + 1 <= 0 or (W + 2 * pad - dil * (k - 1) - 1) // stride + 1 <= 0:
+            continue
+        cases.append((N, H, W, C, k, stride, pad, dil, rng.choice([0, 1, 3, 3, 5]), rng.random() < 0.8))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_dw_cases(30, 7))
+def test_dwconv_random_shapes(case):
+    # seeded random depthwise shapes: whichever kernel the library routes them to (tiled 3 / 5 / 7, general) vs the oracle
+    N, H, W, C, k, stride, pad, dil, act, has_bias = case
+    x, w = gen((N, C, H, W), 1), gen((k, k, C), 2, 1.0 / k)
+    b = gen((C,), 3, 0.1) if has_bias else None
+    ref = R.dwconv_ref(x, w, b, (stride, stride), (pad, pad), act, (dil, dil))
+    y = ops.dwconv(cl(x), w.to(DEV), None if b is None else b.to(DEV), (stride, stride), (pad, pad), act, dilation=(dil, dil))
+    assert ops.last_status() == 0
+    close(y, ref)
+
+
 DW_ANY_CASES = [
     # N, H, W, C, R, S, stride, pad, dil, act: every shape the tiled 3/5/7 kernel does not take
     (2, 20, 24, 64, 3, 3, 1, 2, 2, 5), (1, 40, 40, 32, 3, 3, 1, 12, 12, 0), (2, 9, 9, 24, 1, 5, 1, 2, 1, 1),
