@@ -931,3 +931,29 @@ def test_bilinear_and_up_argmax_match_oracle(align):
     assert am.dtype == torch.int32 and am.shape == ref.shape
     # near-ties between channels may resolve differently where the fp32 lerp is contracted into FMAs
     assert (am == ref).float().mean() >= 0.999
+
+
+def _random_misc_cases(n, seed):
+    import random
+    rng = random.Random(seed)
+    return [(rng.randint(1, 4), 8 * rng.randint(1, 60), rng.randint(1, 33), rng.randint(1, 33), rng.choice([2, 3, 3, 5]),
+             rng.choice([1, 2, 2, 3]), rng.random() < 0.5, rng.random() < 0.5, rng.randint(1, 70), rng.randint(1, 70),
+             rng.random() < 0.5) for _ in range(n)]
+
+
+@pytest.mark.parametrize("case", _random_misc_cases(20, 5))
+def test_pools_layernorm_resize_random_shapes(case):
+    # seeded random shapes for the bandwidth-bound operators: max / average pool (both divisor rules, ceil mode),
+    # channels-last LayerNorm, bilinear resize and the fused upsample + argmax, each against the oracle
+    N, C, H, W, k, st, ceil, cip, OH, OW, align = case
+    x = gen((N, C, H, W), 17)
+    pad = (k // 2) if H + 2 * (k // 2) >= k and W + 2 * (k // 2) >= k else 0
+    if H + 2 * pad >= k and W + 2 * pad >= k:
+        assert torch.equal(ops.maxpool(cl(x), k, st, pad, ceil).cpu().float(), R.maxpool_ref(x, k, st, pad, ceil).float())
+        close(ops.avgpool(cl(x), k, st, pad, cip, ceil=ceil), R.avgpool_ref(x, k, st, pad, ceil, cip))
+    g, b = gen((C,), 18, 0.5) + 1.0, gen((C,), 19, 0.2)
+    close(ops.layernorm_cl(cl(x), g.to(DEV), b.to(DEV), 1e-6), R.layernorm_cl_ref(x, g, b, 1e-6), 2e-3)
+    close(ops.upsample_bilinear(cl(x), OH, OW, align=align), R.bilinear_ref(x, OH, OW, align))
+    am = ops.up_argmax(cl(x), OH, OW, align, num_classes=C).cpu()
+    assert (am == R.up_argmax_ref(x, OH, OW, align, num_classes=C)).float().mean() >= 0.999
+    assert ops.last_status() == 0
