@@ -957,3 +957,21 @@ def test_pools_layernorm_resize_random_shapes(case):
     am = ops.up_argmax(cl(x), OH, OW, align, num_classes=C).cpu()
     assert (am == R.up_argmax_ref(x, OH, OW, align, num_classes=C)).float().mean() >= 0.999
     assert ops.last_status() == 0
+
+
+def _random_group_cases(n, seed):
+    import random
+    rng = random.Random(seed)
+    return [(rng.randint(1, 4), rng.randint(3, 30), rng.randint(3, 30), rng.randint(2, 12), 8 * rng.randint(1, 4),
+             8 * rng.randint(1, 4), rng.choice([1, 3, 3]), rng.choice([1, 1, 2]), rng.choice([0, 1, 3])) for _ in range(n)]
+
+
+@pytest.mark.parametrize("case", _random_group_cases(16, 11))
+def test_gconv2_random_shapes(case):
+    # seeded random grouped convolutions (2-12 groups of 8-32 channels on either side) against the oracle
+    N, H, W, G, cg, kg, Rr, stride, act = case
+    C, K, pad = G * cg, G * kg, Rr // 2
+    x, w, b = gen((N, C, H, W), 21), gen((K, cg, Rr, Rr), 22, 1.0 / (cg * Rr * Rr) ** 0.5), gen((K,), 23, 0.1)
+    y = ops.gconv2(cl(x), cl(w), b.to(DEV), (stride, stride), (pad, pad), G, act)
+    assert ops.last_status() == 0
+    close(y, R.gconv2_ref(x, w, b, (stride, stride), (pad, pad), G, act))
